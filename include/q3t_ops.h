@@ -1,0 +1,226 @@
+/*
+ * Operator-level C ABI of libqwen3_tts_cuda.so (additive to qwen3_tts_native.h).
+ *
+ * The reference keeps its kernel launchers C++-internal (namespace qwen3_tts,
+ * native/qwen3-tts-native/native/src/talker_internal.cuh); these entry points expose the
+ * sm_100a replacements one by one with the same names, argument order and meaning, so that
+ * each operator can be driven, checked and timed on its own.  Differences from the
+ * reference's launchers: C linkage and a q3t_ prefix; bf16 tensors are passed as
+ * uint16_t bit patterns; `stream` is a cudaStream_t passed as void*; `rows` may go up to
+ * Q3T_MAX_ROWS (the reference stops at 8); the return value is the cudaError_t of the
+ * launch as int32_t (0 = cudaSuccess, 1 = cudaErrorInvalidValue for rejected arguments).
+ * All pointers are DEVICE pointers unless the name says host.  Nothing here allocates
+ * device memory except q3t_benchmark_int8_gemv.
+ */
+#ifndef Q3T_OPS_H_
+#define Q3T_OPS_H_
+
+#include "qwen3_tts_native.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define Q3T_MAX_ROWS 64
+#define Q3T_KV_PAGE_TOKENS 16
+#define Q3T_ATTENTION_CHUNK 64
+
+/* ---- int8 weight-only GEMV / skinny GEMM --------------------------------------------- */
+
+/* talker_internal.cuh launch_int8_gemm_rows (int8_gemv.cu:319-368):
+ * y[r][n] = bf16(scales[n] * sum_k w[n][k] * x[r][k]); w int8 [out][in] row-major. */
+QWEN3_TTS_API int32_t q3t_launch_int8_gemm_rows(const int8_t* weight, const float* scales,
+                                                const uint16_t* input, uint16_t* output,
+                                                int32_t in_features, int32_t out_features,
+                                                int32_t rows, void* stream);
+
+/* launch_int8_gemm_rows_add (int8_gemv.cu:370-395): output += result (residual epilogue) */
+QWEN3_TTS_API int32_t q3t_launch_int8_gemm_rows_add(const int8_t* weight, const float* scales,
+                                                    const uint16_t* input, uint16_t* output,
+                                                    int32_t in_features, int32_t out_features,
+                                                    int32_t rows, void* stream);
+
+/* launch_int8_gate_up_silu_rows (int8_gemv.cu:397-422): weight [2*out][in], gate rows first;
+ * output = bf16(silu(gate) * up) */
+QWEN3_TTS_API int32_t q3t_launch_int8_gate_up_silu_rows(const int8_t* weight, const float* scales,
+                                                        const uint16_t* input, uint16_t* output,
+                                                        int32_t in_features, int32_t out_features,
+                                                        int32_t rows, void* stream);
+
+/* Fused form used by the frame engine.  No counterpart in the reference, which launches the
+ * RMSNorm (talker_kernels.cu:27-48), the GEMM and the bias/activation/add kernels
+ * (talker_kernels.cu:660-678, 359-371) separately. */
+enum {
+    Q3T_EPI_PLAIN = 0,
+    Q3T_EPI_ADD = 1,
+    Q3T_EPI_BIAS = 2,        /* y = bf16(bf16(acc*scale) + bias) */
+    Q3T_EPI_BIAS_SILU = 3,   /* v = bf16(acc*scale) + bias; y = bf16(v * 1/(1+exp(-v))) */
+    Q3T_EPI_BIAS_ADD = 4,    /* t = bf16(bf16(acc*scale) + bias); residual = bf16(residual + t) */
+    Q3T_EPI_GATE_UP_SILU = 5
+};
+typedef struct Q3tGemmDesc {
+    uint32_t struct_size;        /* sizeof(Q3tGemmDesc) */
+    int32_t epilogue;
+    const int8_t* weight;
+    const float* scales;
+    const uint16_t* input;       /* [rows][in_features] */
+    uint16_t* output;            /* [rows][out_features] */
+    float* output_f32;           /* optional: the fp32 value before the last bf16 round */
+    const uint16_t* norm_weight; /* optional: RMSNorm(input) * norm_weight feeds the GEMM */
+    uint16_t* norm_output;       /* optional: the normalized rows */
+    const uint16_t* bias;        /* bias epilogues */
+    uint16_t* residual;          /* Q3T_EPI_BIAS_ADD */
+    int32_t in_features;
+    int32_t out_features;
+    int32_t rows;
+    float epsilon;
+} Q3tGemmDesc;
+QWEN3_TTS_API int32_t q3t_launch_int8_gemm_ex(const Q3tGemmDesc* desc, void* stream);
+
+/* launch_quantize_weight_rows (int8_gemv.cu:302-317) */
+QWEN3_TTS_API int32_t q3t_launch_quantize_weight_rows(const uint16_t* weight, int8_t* quantized,
+                                                      float* scales, int32_t in_features,
+                                                      int32_t out_features, void* stream);
+
+/* Mirrors qwen3_tts_benchmark_bf16_gemv (gemv.cu) for the int8 kernel: `buffers` distinct
+ * weight images (choose buffers*in*out > L2) are streamed round-robin for `iterations`
+ * launches; tera_operations_per_second counts 2*in*out*rows per launch. */
+QWEN3_TTS_API int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t input_features,
+                                              int32_t output_features, int32_t rows,
+                                              int32_t buffers, int32_t iterations,
+                                              Qwen3TtsGemvBenchmark* output, char* error,
+                                              size_t error_capacity);
+
+/* ---- norms, RoPE, KV append, glue (talker_kernels.cu) --------------------------------- */
+
+QWEN3_TTS_API int32_t q3t_launch_rms_norm_rows(const uint16_t* input, const uint16_t* weight,
+                                               uint16_t* output, int32_t rows, int32_t width,
+                                               float epsilon, void* stream);              /* :27-48 */
+QWEN3_TTS_API int32_t q3t_launch_head_rms_norm_rows(uint16_t* values, const uint16_t* weight,
+                                                    int32_t rows, int32_t heads,
+                                                    int32_t head_dimension, float epsilon,
+                                                    void* stream);                          /* :50-70 */
+QWEN3_TTS_API int32_t q3t_launch_rope_rows_at(uint16_t* values, int32_t rows, int32_t heads,
+                                              int32_t head_dimension, const int32_t* positions,
+                                              float theta, void* stream);                  /* :597-639 */
+QWEN3_TTS_API int32_t q3t_launch_kv_scatter_rows(const uint16_t* rows_data,
+                                                 uint16_t* const* cache_bases,
+                                                 const int32_t* positions, int32_t rows,
+                                                 int32_t width, void* stream);             /* :641-658 */
+QWEN3_TTS_API int32_t q3t_launch_bias_activation_rows(uint16_t* values, const uint16_t* bias,
+                                                      int32_t rows, int32_t width, int32_t silu,
+                                                      void* stream);                       /* :660-678 */
+QWEN3_TTS_API int32_t q3t_launch_add_in_place(uint16_t* destination, const uint16_t* source,
+                                              int32_t width, void* stream);                /* :359-371 */
+QWEN3_TTS_API int32_t q3t_launch_silu_gate(uint16_t* gate, const uint16_t* up, int32_t width,
+                                           void* stream);                                  /* :405-421 */
+QWEN3_TTS_API int32_t q3t_launch_gather_embedding_rows(const uint16_t* table, int32_t vocabulary,
+                                                       int32_t width, const int32_t* const* tokens,
+                                                       int32_t token_offset, uint16_t* output,
+                                                       int32_t rows, void* stream);        /* :680-709 */
+QWEN3_TTS_API int32_t q3t_launch_add_embedding_rows(const uint16_t* table, int32_t vocabulary,
+                                                    int32_t width, const int32_t* const* tokens,
+                                                    int32_t token_offset, uint16_t* output,
+                                                    int32_t rows, void* stream);           /* :680-709 */
+
+/* ---- decode attention ------------------------------------------------------------------ */
+
+/* Bytes of scratch a decode-attention launch needs for rows whose lengths do not exceed
+ * max_sequence_length (ticket counters followed by split-KV partials). */
+QWEN3_TTS_API size_t q3t_attention_scratch_bytes(int32_t rows, int32_t query_heads,
+                                                 int32_t key_value_heads, int32_t head_dimension,
+                                                 int32_t max_sequence_length);
+
+/* launch_batch_causal_gqa_attention_fast (talker_kernels.cu:506-595, 1024-1044): per-row
+ * contiguous caches [position][kv_heads][head_dim]; row r attends positions 0..positions[r].
+ * Extra arguments: the scratch buffer above (the reference kernel needs none). */
+QWEN3_TTS_API int32_t q3t_launch_batch_causal_gqa_attention_fast(
+    const uint16_t* query, uint16_t* const* key_bases, uint16_t* const* value_bases,
+    const int32_t* positions, uint16_t* output, int32_t rows, int32_t query_heads,
+    int32_t key_value_heads, int32_t head_dimension, int32_t max_sequence_length, void* scratch,
+    size_t scratch_bytes, void* stream);
+
+/* Full form: paged KV and/or the fused per-head RMSNorm + RoPE + KV append, which the reference
+ * issues as launch_head_rms_norm_rows x2, launch_rope_rows_at x2, launch_kv_scatter_rows x2
+ * (talker.cu:2101-2175) before the attention launch. */
+typedef struct Q3tAttentionDesc {
+    uint32_t struct_size;        /* sizeof(Q3tAttentionDesc) */
+    int32_t fused;               /* 1: q/key_new are raw projections; normalize, rotate, append */
+    const uint16_t* query;       /* [rows][query_stride] */
+    const uint16_t* key_new;     /* fused: [rows][new_stride] */
+    const uint16_t* value_new;
+    const uint16_t* query_norm_weight;   /* fused: [head_dimension] */
+    const uint16_t* key_norm_weight;
+    const int32_t* positions;    /* [rows] */
+    uint16_t* output;            /* [rows][query_heads*head_dimension] */
+    float* output_f32;           /* optional fp32 value before the last bf16 round */
+    uint16_t* const* key_bases;  /* contiguous caches, or NULL when paged */
+    uint16_t* const* value_bases;
+    const int32_t* page_table;   /* paged: [rows][page_table_stride] page ids */
+    uint16_t* const* slabs;      /* paged: slab base pointers */
+    int64_t page_elements;       /* paged: elements between consecutive pages of a plane */
+    int64_t key_offset;          /* paged: element offset of the K plane inside a slab */
+    int64_t value_offset;
+    int32_t page_table_stride;
+    int32_t slab_shift;          /* paged: page id >> slab_shift selects the slab */
+    int32_t query_stride;        /* 0: query_heads*head_dimension */
+    int32_t new_stride;          /* 0: key_value_heads*head_dimension */
+    int32_t rows;
+    int32_t query_heads;
+    int32_t key_value_heads;
+    int32_t head_dimension;      /* 32 (not fused), 64, 128 */
+    int32_t max_sequence_length;
+    float epsilon;
+    float theta;
+    void* scratch;
+    size_t scratch_bytes;
+} Q3tAttentionDesc;
+QWEN3_TTS_API int32_t q3t_launch_decode_attention_ex(const Q3tAttentionDesc* desc, void* stream);
+
+/* ---- sampler (sampling_kernels.cu) ------------------------------------------------------- */
+
+/* launch_sample_logits (sampling_kernels.cu:460-498) */
+QWEN3_TTS_API int32_t q3t_launch_sample_logits(
+    const uint16_t* logits, int32_t vocabulary, int32_t suppress_talker_reserved,
+    int32_t codec_eos_token, const int32_t* semantic_history, int32_t semantic_history_count,
+    int32_t do_sample, int32_t top_k, float top_p, float temperature, float repetition_penalty,
+    uint64_t* random_state, int32_t* selected_token, void* stream);
+
+/* launch_sample_logits_at (sampling_kernels.cu:500-538): the history count is read from device */
+QWEN3_TTS_API int32_t q3t_launch_sample_logits_at(
+    const uint16_t* logits, int32_t vocabulary, int32_t suppress_talker_reserved,
+    int32_t codec_eos_token, const int32_t* semantic_history, const int32_t* semantic_history_count,
+    int32_t do_sample, int32_t top_k, float top_p, float temperature, float repetition_penalty,
+    uint64_t* random_state, int32_t* selected_token, void* stream);
+
+/* ---- engine extras --------------------------------------------------------------------- */
+
+/* Options: "mask_eos" (1: the talker sampler also masks EOS, for synthetic weights whose
+ * logits would otherwise end a run at random), "use_graphs" (0: launch kernels one by one). */
+QWEN3_TTS_API int32_t q3t_model_set_option(Qwen3TtsModelHandle model, const char* key,
+                                           int32_t value, char* error, size_t error_capacity);
+
+/* Frame loop without a host round trip per frame: `frames` codec frames for each of the
+ * `session_count` prefilled sessions, enqueued back to back; returns after the last one.
+ * frame_milliseconds (host, [frames], optional) receives each frame's GPU time,
+ * total_milliseconds (host, optional) the whole loop's.  Session state afterwards is as if
+ * begin/finish had been called `frames` times (an EOS inside the loop is not acted on). */
+QWEN3_TTS_API int32_t q3t_model_run_frames(Qwen3TtsModelHandle model,
+                                           Qwen3TtsSessionHandle* sessions, int32_t session_count,
+                                           int32_t frames, int32_t trailing_text_token_id,
+                                           Qwen3TtsSamplingConfig talker_sampling,
+                                           Qwen3TtsSamplingConfig predictor_sampling,
+                                           float* frame_milliseconds, float* total_milliseconds,
+                                           char* error, size_t error_capacity);
+
+/* Test hook: host copies of a session's device state (any pointer may be NULL):
+ * last_hidden [2048] bf16, frame_tokens [16], random_state [1]. */
+QWEN3_TTS_API int32_t q3t_session_read_state(Qwen3TtsSessionHandle session, uint16_t* last_hidden,
+                                             int32_t* frame_tokens, uint64_t* random_state,
+                                             char* error, size_t error_capacity);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* Q3T_OPS_H_ */

@@ -1,0 +1,1110 @@
+// Model / session / frame engine (see engine.hpp).
+
+#include "engine.hpp"
+
+#include <algorithm>
+#include <cstddef>
+#include <cstdlib>
+#include <cstring>
+#include <limits>
+
+namespace q3t {
+
+namespace {
+constexpr int kTalkerLayers = 28;
+constexpr int kPredictorLayers = 5;
+constexpr int kResidualCodebooks = 15;
+constexpr int kTalkerVocab = 3072;
+constexpr int kTextVocab = 151936;
+constexpr int kPredictorSequence = 16;
+constexpr int kEos = 2150;
+constexpr uint32_t kPhaseCreated = 0, kPhaseReady = 1, kPhasePrefilled = 2, kPhaseEnded = 3;
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int env_int(const char* name, int fallback) {
+    const char* v = std::getenv(name);
+    return v != nullptr && *v != '\0' ? std::atoi(v) : fallback;
+}
+}  // namespace
+
+void check_cuda(cudaError_t status, const char* what) {
+    if (status != cudaSuccess) {
+        throw CudaFailure(std::string(what) + " failed: " + cudaGetErrorString(status));
+    }
+}
+
+// ------------------------------------------------------------------ DeviceBuffer
+
+DeviceBuffer::DeviceBuffer(size_t bytes) : bytes_(bytes) {
+    if (bytes != 0) check_cuda(cudaMalloc(&ptr_, bytes), "cudaMalloc");
+}
+DeviceBuffer::DeviceBuffer(DeviceBuffer&& o) noexcept : ptr_(o.ptr_), bytes_(o.bytes_) {
+    o.ptr_ = nullptr;
+    o.bytes_ = 0;
+}
+DeviceBuffer& DeviceBuffer::operator=(DeviceBuffer&& o) noexcept {
+    if (this != &o) {
+        if (ptr_ != nullptr) cudaFree(ptr_);
+        ptr_ = o.ptr_;
+        bytes_ = o.bytes_;
+        o.ptr_ = nullptr;
+        o.bytes_ = 0;
+    }
+    return *this;
+}
+DeviceBuffer::~DeviceBuffer() {
+    if (ptr_ != nullptr) cudaFree(ptr_);
+}
+
+// ------------------------------------------------------------------ KvPool
+
+KvPool::KvPool(int layers, int kv_width, int slab_shift)
+    : layers_(layers), kv_width_(kv_width), slab_shift_(slab_shift),
+      page_elems_((long long)kPageTokens * kv_width),
+      plane_elems_(((long long)1 << slab_shift) * kPageTokens * kv_width),
+      slab_table_(kMaxSlabs * sizeof(bf16*)) {
+    check_cuda(cudaMemset(slab_table_.as<void>(), 0, kMaxSlabs * sizeof(bf16*)), "cudaMemset(slab table)");
+}
+
+void KvPool::add_slab() {
+    if (static_cast<int>(slabs_.size()) >= kMaxSlabs) throw std::bad_alloc();
+    const size_t bytes = (size_t)layers_ * 2 * plane_elems_ * sizeof(bf16);
+    DeviceBuffer slab(bytes);
+    bf16* base = slab.as<bf16>();
+    const int index = static_cast<int>(slabs_.size());
+    check_cuda(cudaMemcpy(slab_table_.as<bf16*>() + index, &base, sizeof(base), cudaMemcpyHostToDevice),
+               "cudaMemcpy(slab table)");
+    slabs_.push_back(std::move(slab));
+    const int per = 1 << slab_shift_;
+    for (int i = per - 1; i >= 0; --i) free_.push_back(index * per + i);
+}
+
+int KvPool::allocate() {
+    if (free_.empty()) add_slab();
+    const int page = free_.back();
+    free_.pop_back();
+    return page;
+}
+
+void KvPool::release(int page) { free_.push_back(page); }
+
+KvLayout KvPool::layout(int layer, const int* page_table, int table_stride) const {
+    KvLayout l;
+    l.page_table = page_table;
+    l.table_stride = table_stride;
+    l.slabs = slab_table_.as<bf16*>();
+    l.slab_shift = slab_shift_;
+    l.page_elems = page_elems_;
+    l.k_offset = (long long)(layer * 2) * plane_elems_;
+    l.v_offset = (long long)(layer * 2 + 1) * plane_elems_;
+    return l;
+}
+
+uint64_t KvPool::page_bytes() const { return (uint64_t)layers_ * 2 * page_elems_ * sizeof(bf16); }
+
+// ------------------------------------------------------------------ Workspace
+
+Workspace::Workspace(int capacity_, int device_) : capacity(capacity_), device(device_) {
+    check_cuda(cudaSetDevice(device), "cudaSetDevice(workspace)");
+    const size_t e = sizeof(bf16);
+    const size_t c = capacity;
+    hidden = DeviceBuffer(c * 2048 * e);
+    qkv = DeviceBuffer(c * 4096 * e);
+    attention = DeviceBuffer(c * 2048 * e);
+    gate = DeviceBuffer(c * 6144 * e);
+    logits = DeviceBuffer(c * kTalkerVocab * e);
+    x_in = DeviceBuffer(c * 2048 * e);
+    projection = DeviceBuffer(c * 2048 * e);
+    normalized = DeviceBuffer(c * 2048 * e);
+    table = DeviceBuffer(sizeof(FrameTable));
+    talker_pages = DeviceBuffer(c * kMaxPagesPerRow * sizeof(int));
+    predictor_pages = DeviceBuffer(c * sizeof(int));
+    predictor_positions = DeviceBuffer((size_t)kPredictorSequence * kMaxRows * sizeof(int));
+    counters = DeviceBuffer(c * 16 * sizeof(unsigned int));
+    try {
+        check_cuda(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        check_cuda(cudaHostAlloc(reinterpret_cast<void**>(&host_table), sizeof(FrameTable),
+                                 cudaHostAllocDefault), "cudaHostAlloc(frame table)");
+        std::memset(host_table, 0, sizeof(FrameTable));
+        check_cuda(cudaHostAlloc(reinterpret_cast<void**>(&host_pages),
+                                 c * (kMaxPagesPerRow + 1) * sizeof(int), cudaHostAllocDefault),
+                   "cudaHostAlloc(page tables)");
+        check_cuda(cudaMemset(table.as<void>(), 0, sizeof(FrameTable)), "cudaMemset(frame table)");
+        check_cuda(cudaMemset(counters.as<void>(), 0, counters.bytes()), "cudaMemset(counters)");
+        std::vector<int> positions((size_t)kPredictorSequence * kMaxRows);
+        for (int p = 0; p < kPredictorSequence; ++p)
+            for (int r = 0; r < kMaxRows; ++r) positions[(size_t)p * kMaxRows + r] = p;
+        check_cuda(cudaMemcpy(predictor_positions.as<void>(), positions.data(),
+                              positions.size() * sizeof(int), cudaMemcpyHostToDevice),
+                   "cudaMemcpy(predictor positions)");
+        check_cuda(cudaEventCreate(&predictor_start), "cudaEventCreate");
+        check_cuda(cudaEventCreate(&predictor_stop), "cudaEventCreate");
+        check_cuda(cudaEventCreate(&talker_start), "cudaEventCreate");
+        check_cuda(cudaEventCreate(&talker_stop), "cudaEventCreate");
+        check_cuda(cudaEventCreateWithFlags(&table_uploaded, cudaEventDisableTiming), "cudaEventCreate");
+        for (int i = 0; i < capacity && i < kMaxRows; ++i) {
+            check_cuda(cudaEventCreateWithFlags(&join_events[i], cudaEventDisableTiming),
+                       "cudaEventCreate(join)");
+        }
+    } catch (...) {
+        release();
+        throw;
+    }
+}
+
+void Workspace::release() noexcept {
+    destroy_graphs();
+    for (cudaEvent_t& ev : join_events) {
+        if (ev != nullptr) cudaEventDestroy(ev);
+        ev = nullptr;
+    }
+    for (cudaEvent_t* ev : {&predictor_start, &predictor_stop, &talker_start, &talker_stop,
+                            &table_uploaded}) {
+        if (*ev != nullptr) cudaEventDestroy(*ev);
+        *ev = nullptr;
+    }
+    if (host_pages != nullptr) cudaFreeHost(host_pages);
+    host_pages = nullptr;
+    if (host_table != nullptr) cudaFreeHost(host_table);
+    host_table = nullptr;
+    if (stream != nullptr) cudaStreamDestroy(stream);
+    stream = nullptr;
+}
+
+Workspace::~Workspace() {
+    cudaSetDevice(device);
+    if (stream != nullptr) cudaStreamSynchronize(stream);
+    release();
+}
+
+void Workspace::destroy_graphs() noexcept {
+    for (auto& kv : graphs) {
+        if (kv.second.predictor != nullptr) cudaGraphExecDestroy(kv.second.predictor);
+        if (kv.second.talker != nullptr) cudaGraphExecDestroy(kv.second.talker);
+    }
+    graphs.clear();
+}
+
+void Workspace::ensure_scratch(int splits) {
+    if (splits <= scratch_splits) return;
+    check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize(scratch)");
+    destroy_graphs();   // captured launches hold the old scratch pointer
+    scratch = DeviceBuffer();
+    scratch = DeviceBuffer(attention_scratch_floats(capacity, 16, 128, splits) * sizeof(float));
+    scratch_splits = splits;
+}
+
+uint64_t Workspace::bytes() const {
+    return hidden.bytes() + qkv.bytes() + attention.bytes() + gate.bytes() + logits.bytes()
+        + x_in.bytes() + projection.bytes() + normalized.bytes() + table.bytes()
+        + talker_pages.bytes() + predictor_pages.bytes() + predictor_positions.bytes()
+        + counters.bytes() + scratch.bytes();
+}
+
+// ------------------------------------------------------------------ Model
+
+Model::Model(int device) : device_(device) {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(model)");
+    check_cuda(cudaStreamCreateWithFlags(&upload_stream_, cudaStreamNonBlocking),
+               "cudaStreamCreate(upload)");
+    talker = {2048, 6144, 16, 8, 128, 2048, 1024, kTalkerLayers};
+    // The checkpoint's code predictor has head_dim 128 (q 2048 wide, k/v 1024 wide);
+    // QWEN3_TTS_PREDICTOR_HEAD_DIM=64 selects the 64-wide variant for experiments.
+    const int phd = env_int("QWEN3_TTS_PREDICTOR_HEAD_DIM", 128) == 64 ? 64 : 128;
+    predictor = {1024, 3072, 16, 8, phd, 16 * phd, 8 * phd, kPredictorLayers};
+    mask_eos = env_int("QWEN3_TTS_MASK_EOS", 0) != 0;
+    use_graphs = env_int("QWEN3_TTS_DISABLE_GRAPHS", 0) == 0;
+
+    const uint64_t H = talker.hidden, PH = predictor.hidden;
+    add_keep("talker.model.codec_embedding.weight", {kTalkerVocab, H}, &codec_embedding);
+    add_keep("talker.model.text_embedding.weight", {kTextVocab, H}, &text_embedding);
+    text_fc1 = add_quant_matrix("talker.text_projection.linear_fc1.weight", H, H);
+    add_keep("talker.text_projection.linear_fc1.bias", {H}, &text_fc1_bias);
+    text_fc2 = add_quant_matrix("talker.text_projection.linear_fc2.weight", H, H);
+    add_keep("talker.text_projection.linear_fc2.bias", {H}, &text_fc2_bias);
+    add_keep("talker.model.norm.weight", {H}, &talker_norm);
+    codec_head = add_quant_matrix("talker.codec_head.weight", kTalkerVocab, H);
+    plan_layers("talker.model.layers.", talker, talker_layers);
+    small_to_mtp = add_quant_matrix("talker.code_predictor.small_to_mtp_projection.weight", PH, H);
+    add_keep("talker.code_predictor.small_to_mtp_projection.bias", {PH}, &small_to_mtp_bias);
+    add_keep("talker.code_predictor.model.norm.weight", {PH}, &predictor_norm);
+    plan_layers("talker.code_predictor.model.layers.", predictor, predictor_layers);
+    for (int g = 0; g < kResidualCodebooks; ++g) {
+        add_keep("talker.code_predictor.model.codec_embedding." + std::to_string(g) + ".weight",
+                 {(uint64_t)kPredictorVocab, H}, &predictor_embeddings[g]);
+        predictor_heads[g] = add_quant_matrix(
+            "talker.code_predictor.lm_head." + std::to_string(g) + ".weight", kPredictorVocab, PH);
+    }
+}
+
+Model::~Model() {
+    cudaSetDevice(device_);
+    batch_.reset();
+    if (upload_stream_ != nullptr) {
+        cudaStreamSynchronize(upload_stream_);
+        cudaStreamDestroy(upload_stream_);
+    }
+}
+
+void Model::add_keep(const std::string& name, std::vector<uint64_t> shape, const bf16** slot) {
+    size_t elements = 1;
+    for (uint64_t d : shape) elements *= d;
+    storage_.emplace_back(elements * sizeof(bf16));
+    Spec s;
+    s.shape = std::move(shape);
+    s.destination = storage_.back().as<void>();
+    *slot = storage_.back().as<bf16>();
+    specs_.emplace(name, std::move(s));
+}
+
+void Model::add_quant_rows(const std::string& name, uint64_t rows, uint64_t cols, int8_t* data,
+                           float* scales) {
+    Spec s;
+    s.shape = {rows, cols};
+    s.quantize = true;
+    s.destination = data;
+    s.scales = scales;
+    specs_.emplace(name, std::move(s));
+    staging_bytes_ = std::max(staging_bytes_, (size_t)(rows * cols * sizeof(bf16)));
+}
+
+Quantized Model::allocate_quantized(uint64_t rows, uint64_t cols) {
+    storage_.emplace_back(rows * cols);
+    int8_t* data = storage_.back().as<int8_t>();
+    storage_.emplace_back(rows * sizeof(float));
+    float* scales = storage_.back().as<float>();
+    return Quantized{data, scales};
+}
+
+Quantized Model::add_quant_matrix(const std::string& name, uint64_t rows, uint64_t cols) {
+    const Quantized q = allocate_quantized(rows, cols);
+    add_quant_rows(name, rows, cols, const_cast<int8_t*>(q.data), const_cast<float*>(q.scales));
+    return q;
+}
+
+void Model::plan_layers(const std::string& prefix, const ModelDims& d, std::vector<LayerWeights>& out) {
+    const uint64_t H = d.hidden, I = d.intermediate, QW = d.q_width, KW = d.kv_width, HD = d.head_dim;
+    out.resize(d.layers);
+    for (int l = 0; l < d.layers; ++l) {
+        LayerWeights& w = out[l];
+        const std::string p = prefix + std::to_string(l);
+        add_keep(p + ".input_layernorm.weight", {H}, &w.input_norm);
+        w.qkv = allocate_quantized(QW + 2 * KW, H);
+        int8_t* qd = const_cast<int8_t*>(w.qkv.data);
+        float* qs = const_cast<float*>(w.qkv.scales);
+        add_quant_rows(p + ".self_attn.q_proj.weight", QW, H, qd, qs);
+        add_quant_rows(p + ".self_attn.k_proj.weight", KW, H, qd + QW * H, qs + QW);
+        add_quant_rows(p + ".self_attn.v_proj.weight", KW, H, qd + (QW + KW) * H, qs + QW + KW);
+        w.o = add_quant_matrix(p + ".self_attn.o_proj.weight", H, QW);
+        add_keep(p + ".self_attn.q_norm.weight", {HD}, &w.q_norm);
+        add_keep(p + ".self_attn.k_norm.weight", {HD}, &w.k_norm);
+        add_keep(p + ".post_attention_layernorm.weight", {H}, &w.post_norm);
+        w.gate_up = allocate_quantized(2 * I, H);
+        int8_t* gd = const_cast<int8_t*>(w.gate_up.data);
+        float* gs = const_cast<float*>(w.gate_up.scales);
+        add_quant_rows(p + ".mlp.gate_proj.weight", I, H, gd, gs);
+        add_quant_rows(p + ".mlp.up_proj.weight", I, H, gd + I * H, gs + I);
+        w.down = add_quant_matrix(p + ".mlp.down_proj.weight", H, I);
+    }
+}
+
+void Model::upload_tensor(const char* name, const void* data, uint64_t bytes, int rank,
+                          const uint64_t* shape) {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(upload)");
+    if (finalized_) throw std::runtime_error("model weights are already finalized");
+    if (name == nullptr || *name == '\0' || data == nullptr || shape == nullptr) {
+        throw std::runtime_error("tensor upload received a null argument");
+    }
+    if (rank <= 0 || rank > 4 || bytes == 0) {
+        throw std::runtime_error("tensor upload has an invalid rank or byte size");
+    }
+    uint64_t elements = 1;
+    std::vector<uint64_t> dims;
+    for (int i = 0; i < rank; ++i) {
+        if (shape[i] == 0 || elements > std::numeric_limits<uint64_t>::max() / shape[i]) {
+            throw std::runtime_error("tensor shape is empty or overflows");
+        }
+        elements *= shape[i];
+        dims.push_back(shape[i]);
+    }
+    if (elements > std::numeric_limits<uint64_t>::max() / sizeof(bf16)
+        || elements * sizeof(bf16) != bytes) {
+        throw std::runtime_error("tensor byte size does not match BF16 shape");
+    }
+    const auto found = specs_.find(name);
+    if (found == specs_.end()) {
+        throw std::runtime_error(std::string("tensor is not part of the talker checkpoint: ") + name);
+    }
+    Spec& spec = found->second;
+    if (spec.seen) throw std::runtime_error(std::string("duplicate tensor upload: ") + name);
+    if (spec.shape != dims) throw std::runtime_error(std::string("unexpected shape for tensor ") + name);
+    if (spec.quantize) {
+        if (staging_.bytes() < staging_bytes_) staging_ = DeviceBuffer(staging_bytes_);
+        check_cuda(cudaMemcpyAsync(staging_.as<void>(), data, bytes, cudaMemcpyHostToDevice,
+                                   upload_stream_), "cudaMemcpyAsync(weight H2D)");
+        check_cuda(launch_quantize_weight_rows(staging_.as<bf16>(),
+                                               static_cast<int8_t*>(spec.destination), spec.scales,
+                                               static_cast<int>(dims[1]), static_cast<int>(dims[0]),
+                                               upload_stream_), "quantize decode weight");
+        // the staging buffer is reused by the next upload; the host copy above has already
+        // left the caller's buffer when cudaMemcpyAsync returns for pageable memory, but a
+        // pinned source is read asynchronously, so wait before handing control back
+        check_cuda(cudaStreamSynchronize(upload_stream_), "cudaStreamSynchronize(upload)");
+    } else {
+        check_cuda(cudaMemcpyAsync(spec.destination, data, bytes, cudaMemcpyHostToDevice,
+                                   upload_stream_), "cudaMemcpyAsync(weight H2D)");
+        check_cuda(cudaStreamSynchronize(upload_stream_), "cudaStreamSynchronize(upload)");
+    }
+    spec.seen = true;
+    weight_bytes_ += bytes;
+    ++tensor_count_;
+}
+
+void Model::finalize(uint64_t* weight_bytes, uint32_t* tensor_count) {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(finalize)");
+    if (finalized_) throw std::runtime_error("model weights are already finalized");
+    if (tensor_count_ != 404 || specs_.size() != 404) {
+        for (const auto& kv : specs_) {
+            if (!kv.second.seen) {
+                throw std::runtime_error("checkpoint is missing required tensor " + kv.first);
+            }
+        }
+        throw std::runtime_error("expected exactly 404 VoiceDesign tensors, found "
+                                 + std::to_string(tensor_count_));
+    }
+    check_cuda(cudaStreamSynchronize(upload_stream_), "cudaStreamSynchronize(upload)");
+    staging_ = DeviceBuffer();
+    embedding_ptrs_ = DeviceBuffer(kResidualCodebooks * sizeof(const bf16*));
+    check_cuda(cudaMemcpy(embedding_ptrs_.as<void>(), predictor_embeddings.data(),
+                          kResidualCodebooks * sizeof(const bf16*), cudaMemcpyHostToDevice),
+               "cudaMemcpy(embedding table)");
+    predictor_embedding_table = embedding_ptrs_.as<const bf16*>();
+    talker_pool.reset(new KvPool(talker.layers, talker.kv_width, 8));
+    predictor_pool.reset(new KvPool(predictor.layers, predictor.kv_width, 6));
+    finalized_ = true;
+    *weight_bytes = weight_bytes_;
+    *tensor_count = tensor_count_;
+}
+
+Workspace& Model::batch_workspace() {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!batch_) batch_.reset(new Workspace(kMaxRows, device_));
+    return *batch_;
+}
+
+// ------------------------------------------------------------------ frame enqueue
+
+namespace {
+
+void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWeights>& layers,
+                    const KvPool& pool, const int* page_table, int table_stride,
+                    const int* positions, int n, int splits, cudaStream_t s) {
+    const int qkv_width = d.q_width + 2 * d.kv_width;
+    for (size_t l = 0; l < layers.size(); ++l) {
+        const LayerWeights& lw = layers[l];
+        GemvArgs g;
+        g.w = lw.qkv.data; g.scales = lw.qkv.scales;
+        g.x = w.hidden.as<bf16>(); g.y = w.qkv.as<bf16>();
+        g.norm_w = lw.input_norm;
+        g.in_features = d.hidden; g.out_features = qkv_width; g.rows = n; g.epilogue = EPI_PLAIN;
+        check_cuda(launch_int8_gemm(g, s), "qkv projection");
+
+        AttentionArgs a;
+        a.q = w.qkv.as<bf16>();
+        a.k_new = w.qkv.as<bf16>() + d.q_width;
+        a.v_new = w.qkv.as<bf16>() + d.q_width + d.kv_width;
+        a.q_stride = qkv_width; a.kv_new_stride = qkv_width;
+        a.q_norm_w = lw.q_norm; a.k_norm_w = lw.k_norm;
+        a.positions = positions;
+        a.out = w.attention.as<bf16>();
+        a.kv = pool.layout(static_cast<int>(l), page_table, table_stride);
+        a.scratch = w.scratch.as<float>();
+        a.counters = w.counters.as<unsigned int>();
+        a.rows = n; a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.head_dim = d.head_dim;
+        a.max_splits = splits; a.fused = 1;
+        check_cuda(launch_decode_attention(a, s), "decode attention");
+
+        GemvArgs o;
+        o.w = lw.o.data; o.scales = lw.o.scales;
+        o.x = w.attention.as<bf16>(); o.y = w.hidden.as<bf16>();
+        o.in_features = d.q_width; o.out_features = d.hidden; o.rows = n; o.epilogue = EPI_ADD;
+        check_cuda(launch_int8_gemm(o, s), "attention output projection");
+
+        GemvArgs u;
+        u.w = lw.gate_up.data; u.scales = lw.gate_up.scales;
+        u.x = w.hidden.as<bf16>(); u.y = w.gate.as<bf16>();
+        u.norm_w = lw.post_norm;
+        u.in_features = d.hidden; u.out_features = d.intermediate; u.rows = n;
+        u.epilogue = EPI_GATE_UP_SILU;
+        check_cuda(launch_int8_gemm(u, s), "gate/up projection");
+
+        GemvArgs dn;
+        dn.w = lw.down.data; dn.scales = lw.down.scales;
+        dn.x = w.gate.as<bf16>(); dn.y = w.hidden.as<bf16>();
+        dn.in_features = d.intermediate; dn.out_features = d.hidden; dn.rows = n;
+        dn.epilogue = EPI_ADD;
+        check_cuda(launch_int8_gemm(dn, s), "down projection");
+    }
+}
+
+// 16 predictor positions, 15 sampled codebooks, packed codes (talker.cu:1549-1701)
+void enqueue_predictor(Workspace& w, Model& m, int n, cudaStream_t s) {
+    const FrameTable* table = w.table.as<FrameTable>();
+    const int H = m.talker.hidden, PH = m.predictor.hidden;
+    check_cuda(launch_frame_begin(table, n, s), "frame begin");
+    for (int p = 0; p < kPredictorSequence; ++p) {
+        check_cuda(launch_predictor_input(table, p, m.codec_embedding, m.predictor_embedding_table,
+                                          w.x_in.as<bf16>(), H, n, s), "predictor input");
+        GemvArgs g;
+        g.w = m.small_to_mtp.data; g.scales = m.small_to_mtp.scales;
+        g.x = w.x_in.as<bf16>(); g.y = w.hidden.as<bf16>(); g.bias = m.small_to_mtp_bias;
+        g.in_features = H; g.out_features = PH; g.rows = n; g.epilogue = EPI_BIAS;
+        check_cuda(launch_int8_gemm(g, s), "predictor input projection");
+        enqueue_layers(w, m.predictor, m.predictor_layers, *m.predictor_pool,
+                       w.predictor_pages.as<int>(), 1,
+                       w.predictor_positions.as<int>() + (size_t)p * kMaxRows, n, 1, s);
+        if (p >= 1) {
+            GemvArgs h;
+            h.w = m.predictor_heads[p - 1].data; h.scales = m.predictor_heads[p - 1].scales;
+            h.x = w.hidden.as<bf16>(); h.y = w.logits.as<bf16>(); h.norm_w = m.predictor_norm;
+            h.in_features = PH; h.out_features = kPredictorVocab; h.rows = n; h.epilogue = EPI_PLAIN;
+            check_cuda(launch_int8_gemm(h, s), "predictor head");
+            check_cuda(launch_sample_table(table, w.logits.as<bf16>(), kPredictorVocab,
+                                           kPredictorVocab, 0, p, 0, kEos, n, s),
+                       "sample predictor logits");
+        }
+    }
+    check_cuda(launch_pack_codes(table, n, s), "pack codec frame");
+}
+
+void enqueue_text_projection(Workspace& w, Model& m, int n, bool residual, cudaStream_t s) {
+    const int H = m.talker.hidden;
+    GemvArgs f1;
+    f1.w = m.text_fc1.data; f1.scales = m.text_fc1.scales;
+    f1.x = w.x_in.as<bf16>(); f1.y = w.projection.as<bf16>(); f1.bias = m.text_fc1_bias;
+    f1.in_features = H; f1.out_features = H; f1.rows = n; f1.epilogue = EPI_BIAS_SILU;
+    check_cuda(launch_int8_gemm(f1, s), "text projection fc1");
+    GemvArgs f2;
+    f2.w = m.text_fc2.data; f2.scales = m.text_fc2.scales;
+    f2.x = w.projection.as<bf16>(); f2.bias = m.text_fc2_bias;
+    f2.in_features = H; f2.out_features = H; f2.rows = n;
+    if (residual) {
+        f2.resid = w.hidden.as<bf16>(); f2.epilogue = EPI_BIAS_ADD;
+    } else {
+        f2.y = w.hidden.as<bf16>(); f2.epilogue = EPI_BIAS;
+    }
+    check_cuda(launch_int8_gemm(f2, s), "text projection fc2");
+}
+
+void enqueue_talker_head(Workspace& w, Model& m, int n, int advance, cudaStream_t s) {
+    FrameTable* table = w.table.as<FrameTable>();
+    const int H = m.talker.hidden;
+    GemvArgs h;
+    h.w = m.codec_head.data; h.scales = m.codec_head.scales;
+    h.x = w.hidden.as<bf16>(); h.y = w.logits.as<bf16>();
+    h.norm_w = m.talker_norm; h.norm_out = w.normalized.as<bf16>();
+    h.in_features = H; h.out_features = kTalkerVocab; h.rows = n; h.epilogue = EPI_PLAIN;
+    check_cuda(launch_int8_gemm(h, s), "codec head");
+    check_cuda(launch_sample_table(table, w.logits.as<bf16>(), kTalkerVocab, kTalkerVocab, 1, 0,
+                                   m.mask_eos, kEos, n, s), "sample talker logits");
+    check_cuda(launch_frame_end(table, w.normalized.as<bf16>(), H, n, advance, s), "frame end");
+}
+
+// next talker input, 28 layers, head, sample (talker.cu:1703-1880)
+void enqueue_talker(Workspace& w, Model& m, int n, int splits, cudaStream_t s) {
+    FrameTable* table = w.table.as<FrameTable>();
+    const int H = m.talker.hidden;
+    check_cuda(launch_talker_input(table, m.codec_embedding, m.predictor_embedding_table,
+                                   m.text_embedding, kTextVocab, w.hidden.as<bf16>(),
+                                   w.x_in.as<bf16>(), H, n, s), "talker input");
+    enqueue_text_projection(w, m, n, true, s);
+    enqueue_layers(w, m.talker, m.talker_layers, *m.talker_pool, w.talker_pages.as<int>(),
+                   Workspace::kMaxPagesPerRow, table->position, n, splits, s);
+    enqueue_talker_head(w, m, n, 1, s);
+}
+
+// one prompt position of row 0 (talker.cu:1058-1064 + one decoder pass)
+void enqueue_prompt_step(Workspace& w, Model& m, const int* text_ids, const int* codec_ids,
+                         int splits, cudaStream_t s) {
+    FrameTable* table = w.table.as<FrameTable>();
+    const int H = m.talker.hidden;
+    check_cuda(launch_prompt_gather(table, text_ids, m.text_embedding, kTextVocab,
+                                    w.x_in.as<bf16>(), H, s), "prompt gather");
+    enqueue_text_projection(w, m, 1, false, s);
+    check_cuda(launch_prompt_combine(table, text_ids, codec_ids, m.codec_embedding, kTalkerVocab,
+                                     w.hidden.as<bf16>(), H, s), "prompt combine");
+    enqueue_layers(w, m.talker, m.talker_layers, *m.talker_pool, w.talker_pages.as<int>(),
+                   Workspace::kMaxPagesPerRow, table->position, 1, splits, s);
+    check_cuda(launch_advance_position(table, s), "advance position");
+}
+
+template <class Enqueue>
+cudaGraphExec_t capture(cudaStream_t s, Enqueue&& enqueue) {
+    check_cuda(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    cudaGraph_t graph = nullptr;
+    try {
+        enqueue();
+    } catch (...) {
+        cudaStreamEndCapture(s, &graph);
+        if (graph != nullptr) cudaGraphDestroy(graph);
+        throw;
+    }
+    check_cuda(cudaStreamEndCapture(s, &graph), "cudaStreamEndCapture");
+    cudaGraphExec_t exec = nullptr;
+    const cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    check_cuda(e, "cudaGraphInstantiate");
+    return exec;
+}
+
+int split_bucket(int max_length) {
+    const int splits = (max_length + kAttnChunk - 1) / kAttnChunk;
+    return (splits + 7) / 8 * 8;
+}
+
+void validate_sampling_params(const SamplingParams& p) {
+    if (p.top_k < 0 || !(p.top_p > 0.0f) || p.top_p > 1.0f || !(p.temperature > 0.0f)
+        || !(p.penalty > 0.0f)) {
+        throw std::runtime_error("invalid sampling configuration");
+    }
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ Session
+
+Session::Session(std::shared_ptr<Model> model, int max_sequence_length, uint64_t seed)
+    : model_(std::move(model)), device_(model_->device()), max_seq_(max_sequence_length) {
+    if (max_sequence_length < 16 || max_sequence_length > 8192) {
+        throw std::runtime_error("max sequence length must be in [16, 8192]");
+    }
+    if (!model_->finalized()) {
+        throw std::runtime_error("model weights must be finalized before creating a session");
+    }
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(session)");
+    solo_.reset(new Workspace(1, device_));
+    stream_ = solo_->stream;
+    try {
+        check_cuda(cudaEventCreateWithFlags(&codes_ready_, cudaEventDisableTiming), "cudaEventCreate");
+        check_cuda(cudaEventCreateWithFlags(&semantic_ready_, cudaEventDisableTiming), "cudaEventCreate");
+        const size_t off_tokens = 0;
+        const size_t off_codes = align_up(off_tokens + kCodebooks * sizeof(int), 256);
+        const size_t off_sampled = align_up(off_codes + kCodebooks * sizeof(unsigned short), 256);
+        const size_t off_rng = align_up(off_sampled + sizeof(int), 256);
+        const size_t off_hidden = align_up(off_rng + sizeof(unsigned long long), 256);
+        const size_t off_history = align_up(off_hidden + 2048 * sizeof(bf16), 256);
+        const size_t total = off_history + (size_t)max_seq_ * sizeof(int);
+        state_ = DeviceBuffer(total);
+        check_cuda(cudaMemset(state_.as<void>(), 0, total), "cudaMemset(session state)");
+        char* base = state_.as<char>();
+        d_frame_tokens_ = reinterpret_cast<int*>(base + off_tokens);
+        d_frame_codes_ = reinterpret_cast<unsigned short*>(base + off_codes);
+        d_sampled_ = reinterpret_cast<int*>(base + off_sampled);
+        d_rng_ = reinterpret_cast<unsigned long long*>(base + off_rng);
+        d_last_hidden_ = reinterpret_cast<bf16*>(base + off_hidden);
+        d_history_ = reinterpret_cast<int*>(base + off_history);
+        check_cuda(cudaHostAlloc(reinterpret_cast<void**>(&h_token_), sizeof(int), cudaHostAllocMapped),
+                   "cudaHostAlloc(sampled token)");
+        check_cuda(cudaHostAlloc(reinterpret_cast<void**>(&h_codes_), kCodebooks * sizeof(unsigned short),
+                                 cudaHostAllocMapped), "cudaHostAlloc(frame codes)");
+        *h_token_ = -1;
+        {
+            std::lock_guard<std::mutex> lock(model_->mutex);
+            const int pages = (max_seq_ + kPageTokens - 1) / kPageTokens;
+            for (int i = 0; i < pages; ++i) talker_pages_.push_back(model_->talker_pool->allocate());
+            predictor_page_ = model_->predictor_pool->allocate();
+            talker_kv_bytes = (uint64_t)pages * model_->talker_pool->page_bytes();
+            predictor_kv_bytes = model_->predictor_pool->page_bytes();
+        }
+        solo_->ensure_scratch(split_bucket(max_seq_ < 512 ? max_seq_ : 512));
+        workspace_bytes = solo_->bytes() + state_.bytes();
+        reset(seed);
+    } catch (...) {
+        release();
+        throw;
+    }
+}
+
+void Session::release() noexcept {
+    if (model_) {
+        std::lock_guard<std::mutex> lock(model_->mutex);
+        for (int page : talker_pages_) model_->talker_pool->release(page);
+        talker_pages_.clear();
+        if (predictor_page_ >= 0) model_->predictor_pool->release(predictor_page_);
+        predictor_page_ = -1;
+    }
+    if (h_codes_ != nullptr) cudaFreeHost(h_codes_);
+    h_codes_ = nullptr;
+    if (h_token_ != nullptr) cudaFreeHost(h_token_);
+    h_token_ = nullptr;
+    if (semantic_ready_ != nullptr) cudaEventDestroy(semantic_ready_);
+    semantic_ready_ = nullptr;
+    if (codes_ready_ != nullptr) cudaEventDestroy(codes_ready_);
+    codes_ready_ = nullptr;
+}
+
+Session::~Session() {
+    cudaSetDevice(device_);
+    if (stream_ != nullptr) cudaStreamSynchronize(stream_);
+    // a batch workspace may still hold this session's page ids
+    if (model_) {
+        Workspace* batch = model_->batch_workspace_if_any();
+        if (batch != nullptr) {
+            cudaStreamSynchronize(batch->stream);
+            batch->bound.clear();
+        }
+    }
+    release();
+    solo_.reset();
+}
+
+void Session::reset(uint64_t seed) {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(reset)");
+    if (frame_in_flight_) throw std::runtime_error("cannot reset while a device frame lease is in flight");
+    position_ = 0;
+    generated_ = 0;
+    frames_generated = 0;
+    device_sample_count = 0;
+    host_sync_count = 0;
+    current_token_ = 0;
+    phase_ = model_->finalized() ? kPhaseReady : kPhaseCreated;
+    const unsigned long long state = seed == 0 ? 0x9e3779b97f4a7c15ULL : seed;
+    check_cuda(cudaMemcpyAsync(d_rng_, &state, sizeof(state), cudaMemcpyHostToDevice, stream_),
+               "reset device random state");
+    check_cuda(cudaStreamSynchronize(stream_), "synchronize reset random state");
+}
+
+void Session::fill_row(FrameTable& t, int row, int trailing_text, const SamplingParams& talker,
+                       const SamplingParams& predictor, bool host_codes) const {
+    t.position[row] = position_;
+    t.history_count[row] = generated_;
+    t.trailing_text[row] = trailing_text;
+    t.frame_tokens[row] = d_frame_tokens_;
+    t.frame_codes[row] = d_frame_codes_;
+    t.history[row] = d_history_;
+    t.rng[row] = d_rng_;
+    t.sampled[row] = d_sampled_;
+    t.last_hidden[row] = d_last_hidden_;
+    t.host_token[row] = h_token_;
+    t.host_codes[row] = host_codes ? h_codes_ : nullptr;
+    t.talker[row] = talker;
+    t.predictor[row] = predictor;
+}
+
+// the checks of the reference's begin_frame, in its order (talker.cu:1103-1127)
+void Session::validate_begin(int semantic_token, int trailing_text, const SamplingParams& talker,
+                             const SamplingParams& predictor) const {
+    if (poisoned_) throw std::runtime_error("talker session is poisoned and must be destroyed");
+    if (frame_in_flight_) throw std::runtime_error("a device frame lease is already in flight");
+    if (phase_ != kPhasePrefilled) {
+        throw std::runtime_error("talker must be prefilled before frame generation");
+    }
+    if (semantic_token == kEos) throw std::runtime_error("EOS must not be expanded into a codec frame");
+    if (semantic_token >= kTalkerVocab) {
+        throw std::runtime_error("semantic token is outside the talker vocabulary");
+    }
+    if (semantic_token != current_token_) {
+        throw std::runtime_error("semantic token does not match talker session state");
+    }
+    if (trailing_text < 0 || trailing_text >= kTextVocab) {
+        throw std::runtime_error("next-frame text token is outside the text vocabulary");
+    }
+    if (position_ >= max_seq_) throw std::runtime_error("talker KV cache is full");
+    if (generated_ >= max_seq_) {
+        throw std::runtime_error("semantic history exceeds configured sequence capacity");
+    }
+    validate_sampling_params(talker);
+    validate_sampling_params(predictor);
+}
+
+// Makes the page lists of s[0..n) resident in the workspace's page tables.
+void Session::bind_rows(Workspace& w, Session** s, int n) {
+    bool same = static_cast<int>(w.bound.size()) == n;
+    for (int i = 0; same && i < n; ++i) same = w.bound[i] == s[i];
+    if (same) return;
+    check_cuda(cudaStreamSynchronize(w.stream), "cudaStreamSynchronize(rebind)");
+    const int stride = Workspace::kMaxPagesPerRow;
+    int* talker_rows = w.host_pages;
+    int* predictor_rows = w.host_pages + (size_t)w.capacity * stride;
+    for (int i = 0; i < n; ++i) {
+        const std::vector<int>& pages = s[i]->talker_pages_;
+        std::copy(pages.begin(), pages.end(), talker_rows + (size_t)i * stride);
+        predictor_rows[i] = s[i]->predictor_page_;
+    }
+    check_cuda(cudaMemcpyAsync(w.talker_pages.as<void>(), talker_rows,
+                               (size_t)n * stride * sizeof(int), cudaMemcpyHostToDevice, w.stream),
+               "upload talker page table");
+    check_cuda(cudaMemcpyAsync(w.predictor_pages.as<void>(), predictor_rows, (size_t)n * sizeof(int),
+                               cudaMemcpyHostToDevice, w.stream), "upload predictor page table");
+    w.bound.assign(s, s + n);
+}
+
+Workspace::Graphs& Session::frame_graphs(Workspace& w, Model& m, int n, int splits) {
+    const auto key = std::make_pair(n, splits);
+    auto found = w.graphs.find(key);
+    if (found != w.graphs.end()) return found->second;
+    Workspace::Graphs g;
+    g.predictor = capture(w.stream, [&] { enqueue_predictor(w, m, n, w.stream); });
+    try {
+        g.talker = capture(w.stream, [&] { enqueue_talker(w, m, n, splits, w.stream); });
+    } catch (...) {
+        cudaGraphExecDestroy(g.predictor);
+        throw;
+    }
+    return w.graphs.emplace(key, g).first->second;
+}
+
+// Enqueues one frame for rows s[0..n) on w.stream.  The host table must be filled.
+void Session::launch_frame(Workspace& w, Model& m, Session** s, int n, bool upload_table,
+                           bool record_session_events) {
+    int max_length = 1;
+    for (int i = 0; i < n; ++i) max_length = std::max(max_length, w.host_table->position[i] + 1);
+    const int splits = split_bucket(max_length);
+    if (w.option_epoch != m.option_epoch) {
+        check_cuda(cudaStreamSynchronize(w.stream), "cudaStreamSynchronize(options)");
+        w.destroy_graphs();
+        w.option_epoch = m.option_epoch;
+    }
+    w.ensure_scratch(splits);
+    bind_rows(w, s, n);
+    if (upload_table) {
+        check_cuda(cudaMemcpyAsync(w.table.as<void>(), w.host_table, sizeof(FrameTable),
+                                   cudaMemcpyHostToDevice, w.stream), "upload frame table");
+        check_cuda(cudaEventRecord(w.table_uploaded, w.stream), "cudaEventRecord(table)");
+    }
+    if (m.use_graphs) {
+        Workspace::Graphs& g = frame_graphs(w, m, n, splits);
+        check_cuda(cudaEventRecord(w.predictor_start, w.stream), "cudaEventRecord");
+        check_cuda(cudaGraphLaunch(g.predictor, w.stream), "cudaGraphLaunch(predictor)");
+        check_cuda(cudaEventRecord(w.predictor_stop, w.stream), "cudaEventRecord");
+        if (record_session_events) {
+            for (int i = 0; i < n; ++i) {
+                check_cuda(cudaEventRecord(s[i]->codes_ready_, w.stream), "cudaEventRecord(codes)");
+            }
+        }
+        check_cuda(cudaEventRecord(w.talker_start, w.stream), "cudaEventRecord");
+        check_cuda(cudaGraphLaunch(g.talker, w.stream), "cudaGraphLaunch(talker)");
+        check_cuda(cudaEventRecord(w.talker_stop, w.stream), "cudaEventRecord");
+    } else {
+        check_cuda(cudaEventRecord(w.predictor_start, w.stream), "cudaEventRecord");
+        enqueue_predictor(w, m, n, w.stream);
+        check_cuda(cudaEventRecord(w.predictor_stop, w.stream), "cudaEventRecord");
+        if (record_session_events) {
+            for (int i = 0; i < n; ++i) {
+                check_cuda(cudaEventRecord(s[i]->codes_ready_, w.stream), "cudaEventRecord(codes)");
+            }
+        }
+        check_cuda(cudaEventRecord(w.talker_start, w.stream), "cudaEventRecord");
+        enqueue_talker(w, m, n, splits, w.stream);
+        check_cuda(cudaEventRecord(w.talker_stop, w.stream), "cudaEventRecord");
+    }
+    if (record_session_events) {
+        for (int i = 0; i < n; ++i) {
+            check_cuda(cudaEventRecord(s[i]->semantic_ready_, w.stream), "cudaEventRecord(semantic)");
+        }
+    }
+}
+
+uint64_t Session::take_lease(Workspace* w, bool host_codes) {
+    const uint64_t lease = next_lease_++;
+    if (next_lease_ == 0) next_lease_ = 1;
+    frame_in_flight_ = true;
+    pending_host_codes_ = host_codes;
+    pending_lease_ = lease;
+    pending_position_ = static_cast<uint32_t>(position_);
+    pending_workspace_ = w;
+    return lease;
+}
+
+void Session::drop_lease_poisoned() noexcept {
+    poisoned_ = true;
+    frame_in_flight_ = false;
+    pending_host_codes_ = false;
+    pending_lease_ = 0;
+    pending_workspace_ = nullptr;
+}
+
+FrameView Session::begin_frame(uint16_t semantic_token, int trailing_text, const SamplingParams& talker,
+                               const SamplingParams& predictor, bool host_codes) {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(begin frame)");
+    validate_begin(semantic_token, trailing_text, talker, predictor);
+    Workspace& w = *solo_;
+    const uint64_t lease = take_lease(&w, host_codes);
+    try {
+        check_cuda(cudaEventSynchronize(w.table_uploaded), "cudaEventSynchronize(table)");
+        fill_row(*w.host_table, 0, trailing_text, talker, predictor, host_codes);
+        Session* self = this;
+        launch_frame(w, *model_, &self, 1, true, true);
+    } catch (...) {
+        cudaStreamSynchronize(stream_);
+        drop_lease_poisoned();
+        throw;
+    }
+    device_sample_count += kPredictorSequence;
+    ++generated_;
+    ++position_;
+    FrameView view;
+    view.device_codes = d_frame_codes_;
+    view.ready_event = codes_ready_;
+    view.lease_id = lease;
+    view.device = device_;
+    return view;
+}
+
+void Session::batch_begin(Model* model, Session** s, int n, const int* trailing_text,
+                          const SamplingParams* talker, const SamplingParams* predictor,
+                          FrameView* views) {
+    if (model == nullptr || s == nullptr || n <= 0 || n > kMaxRows) {
+        throw std::runtime_error("invalid batch frame arguments");
+    }
+    check_cuda(cudaSetDevice(model->device()), "cudaSetDevice(batch frame)");
+    for (int i = 0; i < n; ++i) {
+        if (s[i]->model_.get() != model) {
+            throw std::runtime_error("batched session belongs to a different model");
+        }
+        for (int j = 0; j < i; ++j) {
+            if (s[j] == s[i]) throw std::runtime_error("a session appears twice in one batch");
+        }
+        s[i]->validate_begin(s[i]->current_token_, trailing_text[i], talker[i], predictor[i]);
+    }
+    Workspace& w = model->batch_workspace();
+    for (int i = 0; i < n; ++i) s[i]->take_lease(&w, false);
+    try {
+        check_cuda(cudaEventSynchronize(w.table_uploaded), "cudaEventSynchronize(table)");
+        for (int i = 0; i < n; ++i) {
+            s[i]->fill_row(*w.host_table, i, trailing_text[i], talker[i], predictor[i], false);
+        }
+        // order the batch stream after each session's earlier work
+        for (int i = 0; i < n; ++i) {
+            check_cuda(cudaEventRecord(w.join_events[i], s[i]->stream_), "cudaEventRecord(join)");
+            check_cuda(cudaStreamWaitEvent(w.stream, w.join_events[i], 0), "cudaStreamWaitEvent(join)");
+        }
+        launch_frame(w, *model, s, n, true, true);
+        for (int i = 0; i < n; ++i) {
+            s[i]->device_sample_count += kPredictorSequence;
+            ++s[i]->generated_;
+            ++s[i]->position_;
+            check_cuda(cudaStreamWaitEvent(s[i]->stream_, s[i]->semantic_ready_, 0),
+                       "cudaStreamWaitEvent(rejoin)");
+        }
+    } catch (...) {
+        cudaStreamSynchronize(w.stream);
+        for (int i = 0; i < n; ++i) s[i]->drop_lease_poisoned();
+        w.destroy_graphs();
+        throw;
+    }
+    for (int i = 0; i < n; ++i) {
+        views[i].device_codes = s[i]->d_frame_codes_;
+        views[i].ready_event = s[i]->codes_ready_;
+        views[i].lease_id = s[i]->pending_lease_;
+        views[i].device = s[i]->device_;
+    }
+}
+
+FrameResult Session::finish_frame(uint64_t lease_id, cudaEvent_t consumer_done) {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(finish frame)");
+    if (poisoned_) throw std::runtime_error("talker session is poisoned and must be destroyed");
+    if (!frame_in_flight_) throw std::runtime_error("no device frame lease is in flight");
+    if (lease_id == 0 || lease_id != pending_lease_) {
+        throw std::runtime_error("device frame lease ID is stale or invalid");
+    }
+    if (consumer_done != nullptr) {
+        check_cuda(cudaStreamWaitEvent(stream_, consumer_done, 0), "cudaStreamWaitEvent(consumer done)");
+    }
+    check_cuda(cudaEventSynchronize(semantic_ready_), "cudaEventSynchronize(semantic ready)");
+    ++host_sync_count;
+    const int next = *h_token_;
+    if (next < 0 || next >= kTalkerVocab) {
+        throw std::runtime_error("device sampler returned an invalid token");
+    }
+    FrameResult r{};
+    r.talker_position = pending_position_;
+    Workspace* w = pending_workspace_;
+    if (w == nullptr
+        || cudaEventElapsedTime(&r.predictor_ms, w->predictor_start, w->predictor_stop) != cudaSuccess
+        || cudaEventElapsedTime(&r.talker_ms, w->talker_start, w->talker_stop) != cudaSuccess) {
+        // a later frame of a shared workspace has re-recorded the timing events
+        cudaGetLastError();
+        r.predictor_ms = 0.0f;
+        r.talker_ms = 0.0f;
+    }
+    if (pending_host_codes_) std::copy_n(h_codes_, kCodebooks, r.codes);
+    r.next_semantic = static_cast<uint16_t>(next);
+    r.ended = next == kEos ? 1u : 0u;
+    current_token_ = r.next_semantic;
+    ++frames_generated;
+    phase_ = r.ended ? kPhaseEnded : kPhasePrefilled;
+    frame_in_flight_ = false;
+    pending_host_codes_ = false;
+    pending_lease_ = 0;
+    pending_workspace_ = nullptr;
+    return r;
+}
+
+void Session::prefill(const int32_t* text_ids, const int32_t* codec_ids, int count,
+                      const SamplingParams& sampling, uint16_t* first_token, float* gpu_ms) {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(prefill)");
+    if (poisoned_) throw std::runtime_error("talker session is poisoned and must be destroyed");
+    if (frame_in_flight_) throw std::runtime_error("cannot prefill while a device frame lease is in flight");
+    if (text_ids == nullptr || codec_ids == nullptr || count <= 0) {
+        throw std::runtime_error("prefill requires non-empty text and codec ID arrays");
+    }
+    if (count > max_seq_) throw std::runtime_error("prompt exceeds the configured KV-cache capacity");
+    for (int i = 0; i < count; ++i) {
+        if (text_ids[i] < 0 && codec_ids[i] < 0) {
+            throw std::runtime_error("a prompt position must contain text or codec input");
+        }
+        if (text_ids[i] >= kTextVocab || codec_ids[i] >= kTalkerVocab) {
+            throw std::runtime_error("embedding token is outside its vocabulary");
+        }
+    }
+    validate_sampling_params(sampling);
+    Workspace& w = *solo_;
+    Model& m = *model_;
+    position_ = 0;
+    generated_ = 0;
+    try {
+        DeviceBuffer ids(2 * (size_t)count * sizeof(int));
+        int* d_text = ids.as<int>();
+        int* d_codec = d_text + count;
+        check_cuda(cudaMemcpyAsync(d_text, text_ids, (size_t)count * sizeof(int),
+                                   cudaMemcpyHostToDevice, w.stream), "upload prompt text ids");
+        check_cuda(cudaMemcpyAsync(d_codec, codec_ids, (size_t)count * sizeof(int),
+                                   cudaMemcpyHostToDevice, w.stream), "upload prompt codec ids");
+        check_cuda(cudaEventSynchronize(w.table_uploaded), "cudaEventSynchronize(table)");
+        fill_row(*w.host_table, 0, 0, sampling, sampling, false);
+        const int splits = split_bucket(count);
+        w.ensure_scratch(splits);
+        Session* self = this;
+        bind_rows(w, &self, 1);
+        check_cuda(cudaMemcpyAsync(w.table.as<void>(), w.host_table, sizeof(FrameTable),
+                                   cudaMemcpyHostToDevice, w.stream), "upload frame table");
+        check_cuda(cudaEventRecord(w.table_uploaded, w.stream), "cudaEventRecord(table)");
+        check_cuda(cudaEventRecord(w.talker_start, w.stream), "cudaEventRecord");
+        // The prompt ids live in a buffer of this call, so the captured step graph is rebuilt
+        // per prefill; capture costs far less than the steps it replays.
+        if (m.use_graphs) {
+            cudaGraphExec_t step = capture(w.stream, [&] {
+                enqueue_prompt_step(w, m, d_text, d_codec, splits, w.stream);
+            });
+            try {
+                for (int i = 0; i < count; ++i) {
+                    check_cuda(cudaGraphLaunch(step, w.stream), "cudaGraphLaunch(prompt step)");
+                }
+            } catch (...) {
+                cudaStreamSynchronize(w.stream);
+                cudaGraphExecDestroy(step);
+                throw;
+            }
+            check_cuda(cudaStreamSynchronize(w.stream), "cudaStreamSynchronize(prompt)");
+            cudaGraphExecDestroy(step);
+        } else {
+            for (int i = 0; i < count; ++i) enqueue_prompt_step(w, m, d_text, d_codec, splits, w.stream);
+        }
+        enqueue_talker_head(w, m, 1, 0, w.stream);
+        check_cuda(cudaEventRecord(w.talker_stop, w.stream), "cudaEventRecord");
+        check_cuda(cudaStreamSynchronize(w.stream), "synchronize sampled token");
+        ++host_sync_count;
+        ++device_sample_count;
+        check_cuda(cudaEventElapsedTime(gpu_ms, w.talker_start, w.talker_stop), "cudaEventElapsedTime");
+    } catch (...) {
+        cudaStreamSynchronize(w.stream);
+        poisoned_ = true;
+        throw;
+    }
+    const int first = *h_token_;
+    if (first < 0 || first >= kTalkerVocab) throw std::runtime_error("device sampler returned an invalid token");
+    position_ = count;
+    generated_ = 1;
+    current_token_ = static_cast<uint16_t>(first);
+    phase_ = first == kEos ? kPhaseEnded : kPhasePrefilled;
+    *first_token = current_token_;
+}
+
+void Session::run_frames(Model* model, Session** s, int n, int frames, int trailing_text,
+                         const SamplingParams& talker, const SamplingParams& predictor,
+                         float* frame_ms, float* total_ms) {
+    if (model == nullptr || s == nullptr || n <= 0 || n > kMaxRows || frames <= 0) {
+        throw std::runtime_error("invalid frame-loop arguments");
+    }
+    check_cuda(cudaSetDevice(model->device()), "cudaSetDevice(frame loop)");
+    for (int i = 0; i < n; ++i) {
+        if (s[i]->model_.get() != model) throw std::runtime_error("session belongs to a different model");
+        for (int j = 0; j < i; ++j) {
+            if (s[j] == s[i]) throw std::runtime_error("a session appears twice in one batch");
+        }
+        s[i]->validate_begin(s[i]->current_token_, trailing_text, talker, predictor);
+        if (s[i]->position_ + frames > s[i]->max_seq_) {
+            throw std::runtime_error("frame loop would overflow the talker KV cache");
+        }
+    }
+    Workspace& w = n == 1 ? *s[0]->solo_ : model->batch_workspace();
+    std::vector<cudaEvent_t> marks;
+    try {
+        check_cuda(cudaEventSynchronize(w.table_uploaded), "cudaEventSynchronize(table)");
+        int longest = 0;
+        for (int i = 0; i < n; ++i) {
+            s[i]->fill_row(*w.host_table, i, trailing_text, talker, predictor, false);
+            longest = std::max(longest, s[i]->position_ + frames);
+            check_cuda(cudaEventRecord(w.join_events[i], s[i]->stream_), "cudaEventRecord(join)");
+            check_cuda(cudaStreamWaitEvent(w.stream, w.join_events[i], 0), "cudaStreamWaitEvent(join)");
+        }
+        w.ensure_scratch(split_bucket(longest));
+        marks.resize(frames + 1, nullptr);
+        for (cudaEvent_t& ev : marks) check_cuda(cudaEventCreate(&ev), "cudaEventCreate(frame mark)");
+        check_cuda(cudaEventRecord(marks[0], w.stream), "cudaEventRecord(frame mark)");
+        for (int f = 0; f < frames; ++f) {
+            // the device table advances itself; the host mirror follows for the graph key
+            launch_frame(w, *model, s, n, f == 0, false);
+            for (int i = 0; i < n; ++i) w.host_table->position[i] += 1;
+            check_cuda(cudaEventRecord(marks[f + 1], w.stream), "cudaEventRecord(frame mark)");
+        }
+        check_cuda(cudaStreamSynchronize(w.stream), "cudaStreamSynchronize(frame loop)");
+        if (frame_ms != nullptr) {
+            for (int f = 0; f < frames; ++f) {
+                check_cuda(cudaEventElapsedTime(&frame_ms[f], marks[f], marks[f + 1]), "cudaEventElapsedTime");
+            }
+        }
+        if (total_ms != nullptr) {
+            check_cuda(cudaEventElapsedTime(total_ms, marks[0], marks[frames]), "cudaEventElapsedTime");
+        }
+        for (int i = 0; i < n; ++i) {
+            Session* c = s[i];
+            c->position_ += frames;
+            c->generated_ += frames;
+            c->frames_generated += frames;
+            c->device_sample_count += (uint64_t)frames * kPredictorSequence;
+            ++c->host_sync_count;
+            const int token = *c->h_token_;
+            if (token < 0 || token >= kTalkerVocab) throw std::runtime_error("device sampler returned an invalid token");
+            c->current_token_ = static_cast<uint16_t>(token);
+            c->phase_ = token == kEos ? kPhaseEnded : kPhasePrefilled;
+        }
+    } catch (...) {
+        cudaStreamSynchronize(w.stream);
+        for (cudaEvent_t ev : marks) if (ev != nullptr) cudaEventDestroy(ev);
+        for (int i = 0; i < n; ++i) s[i]->poisoned_ = true;
+        throw;
+    }
+    for (cudaEvent_t ev : marks) cudaEventDestroy(ev);
+}
+
+void Session::read_state(uint16_t* last_hidden, int* frame_tokens, unsigned long long* rng) const {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(read state)");
+    check_cuda(cudaStreamSynchronize(stream_), "cudaStreamSynchronize(read state)");
+    if (last_hidden != nullptr) {
+        check_cuda(cudaMemcpy(last_hidden, d_last_hidden_, 2048 * sizeof(bf16), cudaMemcpyDeviceToHost),
+                   "cudaMemcpy(last hidden)");
+    }
+    if (frame_tokens != nullptr) {
+        check_cuda(cudaMemcpy(frame_tokens, d_frame_tokens_, kCodebooks * sizeof(int),
+                              cudaMemcpyDeviceToHost), "cudaMemcpy(frame tokens)");
+    }
+    if (rng != nullptr) {
+        check_cuda(cudaMemcpy(rng, d_rng_, sizeof(unsigned long long), cudaMemcpyDeviceToHost),
+                   "cudaMemcpy(rng)");
+    }
+}
+
+}  // namespace q3t

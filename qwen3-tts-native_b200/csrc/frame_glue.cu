@@ -1,0 +1,195 @@
+// Row-table kernels that stitch the projections of one codec frame together: token
+// stores, embedding gathers and sums, code packing and the end-of-frame bookkeeping.
+// They replace the store_token / store_sampled_token / pack_frame_codes / gather_embedding
+// launches of the reference (native/qwen3-tts-native/native/src/sampling_kernels.cu:403-452
+// and talker_kernels.cu:680-709) -- about 40 single-purpose launches per frame there --
+// with one launch per step of the frame, all driven by the device-resident FrameTable.
+
+#include "q3t_kernels.cuh"
+
+namespace q3t {
+namespace {
+
+constexpr int kThreads = 256;
+
+__global__ void frame_begin_kernel(const FrameTable* t, int rows) {
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row < rows) t->frame_tokens[row][0] = *t->sampled[row];
+}
+
+__global__ void __launch_bounds__(kThreads)
+predictor_input_kernel(const FrameTable* t, int p, const bf16* __restrict__ codec_embedding,
+                       const bf16* const* predictor_embeddings, bf16* __restrict__ x, int width) {
+    const int row = blockIdx.x;
+    const bf16* src;
+    if (p == 0) {
+        src = t->last_hidden[row];
+    } else if (p == 1) {
+        const int token = t->frame_tokens[row][0];
+        if (token < 0 || token >= kMaxVocab) return;
+        src = codec_embedding + (size_t)token * width;
+    } else {
+        const int token = t->frame_tokens[row][p - 1];
+        if (token < 0 || token >= kPredictorVocab) return;
+        src = predictor_embeddings[p - 2] + (size_t)token * width;
+    }
+    const int4* s4 = reinterpret_cast<const int4*>(src);
+    int4* d4 = reinterpret_cast<int4*>(x + (size_t)row * width);
+    for (int i = threadIdx.x; i < width / 8; i += kThreads) d4[i] = s4[i];
+}
+
+// The reference builds the next talker input with one gather and fifteen add launches,
+// each add rounding to bf16 (talker.cu:3546-3570 / 1704-1731); the same chain runs here in
+// registers, in the same order.
+__global__ void __launch_bounds__(kThreads)
+talker_input_kernel(const FrameTable* t, const bf16* __restrict__ codec_embedding,
+                    const bf16* const* predictor_embeddings,
+                    const bf16* __restrict__ text_embedding, int text_vocabulary,
+                    bf16* __restrict__ hidden, bf16* __restrict__ text_in, int width) {
+    const int row = blockIdx.x;
+    const int* tokens = t->frame_tokens[row];
+    __shared__ int tok[kCodebooks];
+    if (threadIdx.x < kCodebooks) tok[threadIdx.x] = tokens[threadIdx.x];
+    __syncthreads();
+    for (int i = threadIdx.x; i < width; i += kThreads) {
+        // an out-of-range token leaves the previous content in place, as the reference's
+        // gather does
+        float acc = (tok[0] >= 0 && tok[0] < kMaxVocab)
+            ? bf2f(codec_embedding[(size_t)tok[0] * width + i])
+            : bf2f(hidden[(size_t)row * width + i]);
+#pragma unroll
+        for (int r = 0; r < kCodebooks - 1; ++r) {
+            const int token = tok[r + 1];
+            if (token >= 0 && token < kPredictorVocab) {
+                acc = rbf(acc + bf2f(predictor_embeddings[r][(size_t)token * width + i]));
+            }
+        }
+        hidden[(size_t)row * width + i] = f2bf(acc);
+    }
+    const int text = t->trailing_text[row];
+    if (text >= 0 && text < text_vocabulary) {
+        const int4* s4 = reinterpret_cast<const int4*>(text_embedding + (size_t)text * width);
+        int4* d4 = reinterpret_cast<int4*>(text_in + (size_t)row * width);
+        for (int i = threadIdx.x; i < width / 8; i += kThreads) d4[i] = s4[i];
+    }
+}
+
+__global__ void pack_codes_kernel(const FrameTable* t, int rows) {
+    const int row = blockIdx.x;
+    const int i = threadIdx.x;
+    if (row < rows && i < kCodebooks) {
+        const unsigned short code = static_cast<unsigned short>(t->frame_tokens[row][i]);
+        t->frame_codes[row][i] = code;
+        if (t->host_codes[row] != nullptr) t->host_codes[row][i] = code;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+frame_end_kernel(FrameTable* t, const bf16* __restrict__ normalized, int width,
+                 int advance_position) {
+    const int row = blockIdx.x;
+    const int4* s4 = reinterpret_cast<const int4*>(normalized + (size_t)row * width);
+    int4* d4 = reinterpret_cast<int4*>(t->last_hidden[row]);
+    for (int i = threadIdx.x; i < width / 8; i += kThreads) d4[i] = s4[i];
+    if (threadIdx.x == 0) {
+        if (t->host_token[row] != nullptr) {
+            *t->host_token[row] = *t->sampled[row];
+            __threadfence_system();
+        }
+        if (advance_position) t->position[row] += 1;
+        t->history_count[row] += 1;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+prompt_gather_kernel(const FrameTable* t, const int* __restrict__ text_ids,
+                     const bf16* __restrict__ text_embedding, int text_vocabulary,
+                     bf16* __restrict__ x, int width) {
+    const int text = text_ids[t->position[0]];
+    if (text < 0 || text >= text_vocabulary) return;
+    const int4* s4 = reinterpret_cast<const int4*>(text_embedding + (size_t)text * width);
+    int4* d4 = reinterpret_cast<int4*>(x);
+    for (int i = blockIdx.x * kThreads + threadIdx.x; i < width / 8; i += gridDim.x * kThreads) {
+        d4[i] = s4[i];
+    }
+}
+
+// talker.cu:2721-2748: text part (or zeros) plus the codec embedding, one rounded add
+__global__ void __launch_bounds__(kThreads)
+prompt_combine_kernel(const FrameTable* t, const int* __restrict__ text_ids,
+                      const int* __restrict__ codec_ids, const bf16* __restrict__ codec_embedding,
+                      int codec_vocabulary, bf16* __restrict__ hidden, int width) {
+    const int index = t->position[0];
+    const int text = text_ids[index];
+    const int codec = codec_ids[index];
+    for (int i = blockIdx.x * kThreads + threadIdx.x; i < width; i += gridDim.x * kThreads) {
+        float v = text >= 0 ? bf2f(hidden[i]) : 0.0f;
+        if (codec >= 0 && codec < codec_vocabulary) {
+            v = rbf(v + bf2f(codec_embedding[(size_t)codec * width + i]));
+        }
+        hidden[i] = f2bf(v);
+    }
+}
+
+__global__ void advance_position_kernel(FrameTable* t) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) t->position[0] += 1;
+}
+
+}  // namespace
+
+cudaError_t launch_frame_begin(const FrameTable* table, int rows, cudaStream_t stream) {
+    frame_begin_kernel<<<1, kMaxRows, 0, stream>>>(table, rows);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_predictor_input(const FrameTable* table, int p, const bf16* codec_embedding,
+                                   const bf16* const* predictor_embeddings, bf16* x, int width,
+                                   int rows, cudaStream_t stream) {
+    predictor_input_kernel<<<rows, kThreads, 0, stream>>>(table, p, codec_embedding,
+                                                          predictor_embeddings, x, width);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_talker_input(const FrameTable* table, const bf16* codec_embedding,
+                                const bf16* const* predictor_embeddings, const bf16* text_embedding,
+                                int text_vocabulary, bf16* hidden, bf16* text_in, int width, int rows,
+                                cudaStream_t stream) {
+    talker_input_kernel<<<rows, kThreads, 0, stream>>>(table, codec_embedding, predictor_embeddings,
+                                                       text_embedding, text_vocabulary, hidden,
+                                                       text_in, width);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_pack_codes(const FrameTable* table, int rows, cudaStream_t stream) {
+    pack_codes_kernel<<<rows, 32, 0, stream>>>(table, rows);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_frame_end(FrameTable* table, const bf16* normalized, int width, int rows,
+                             int advance_position, cudaStream_t stream) {
+    frame_end_kernel<<<rows, kThreads, 0, stream>>>(table, normalized, width, advance_position);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prompt_gather(const FrameTable* table, const int* text_ids,
+                                 const bf16* text_embedding, int text_vocabulary, bf16* x, int width,
+                                 cudaStream_t stream) {
+    prompt_gather_kernel<<<1, kThreads, 0, stream>>>(table, text_ids, text_embedding,
+                                                     text_vocabulary, x, width);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prompt_combine(const FrameTable* table, const int* text_ids, const int* codec_ids,
+                                  const bf16* codec_embedding, int codec_vocabulary, bf16* hidden,
+                                  int width, cudaStream_t stream) {
+    prompt_combine_kernel<<<4, kThreads, 0, stream>>>(table, text_ids, codec_ids, codec_embedding,
+                                                      codec_vocabulary, hidden, width);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_advance_position(FrameTable* table, cudaStream_t stream) {
+    advance_position_kernel<<<1, 32, 0, stream>>>(table);
+    return cudaGetLastError();
+}
+
+}  // namespace q3t

@@ -1,0 +1,523 @@
+"""Host-side binding of libqwen3_tts_cuda.so.
+
+Python counterpart of the reference's Rust host wrapper
+(native/qwen3-tts-native/src/native_talker.rs): the same objects and method names
+(NativeTalkerModel.load / start_prompt, NativeTalkerSession.next_frame /
+begin_device_frame / finish, SamplingConfig.official_*_defaults, NativeTalkerStatusError)
+over the same C symbols, resolved by name from the shared library exactly as the Rust
+crate does with libloading (native_talker.rs:776-821).  There is no CPU fallback: if the
+library is missing, import fails with the build command to run.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import Iterable, Optional, Sequence, Tuple
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY_NAME = "libqwen3_tts_cuda.so"
+LIBRARY_PATH = os.path.join(_HERE, LIBRARY_NAME)
+
+ABI_VERSION = 3
+MAX_BATCH_SESSIONS = 64
+CODEBOOKS = 16
+EOS = 2150
+TALKER_VOCAB = 3072
+TEXT_VOCAB = 151936
+
+STATUS_OK, STATUS_INVALID_ARGUMENT, STATUS_CUDA, STATUS_STATE, STATUS_ALLOCATION, STATUS_MODEL = (
+    0, -1, -2, -3, -4, -5)
+
+
+class SamplingConfigC(C.Structure):   # qwen3_tts_native.h Qwen3TtsSamplingConfig (20 bytes)
+    _fields_ = [("do_sample", C.c_int32), ("top_k", C.c_int32), ("top_p", C.c_float),
+                ("temperature", C.c_float), ("repetition_penalty", C.c_float)]
+
+
+class PrefillResultC(C.Structure):    # 12 bytes
+    _fields_ = [("first_semantic_token", C.c_uint16), ("reserved", C.c_uint16),
+                ("prompt_tokens", C.c_uint32), ("talker_gpu_milliseconds", C.c_float)]
+
+
+class FrameInfoC(C.Structure):        # 16 bytes
+    _fields_ = [("talker_position", C.c_uint32), ("ended_by_eos", C.c_uint32),
+                ("predictor_gpu_milliseconds", C.c_float), ("talker_gpu_milliseconds", C.c_float)]
+
+
+class DeviceFrameViewV2C(C.Structure):   # 40 bytes, align 8
+    _fields_ = [("struct_size", C.c_uint32), ("code_count", C.c_uint32),
+                ("device_codes", C.c_void_p), ("ready_event", C.c_void_p),
+                ("lease_id", C.c_uint64), ("device_index", C.c_int32), ("reserved", C.c_uint32)]
+
+
+class StateInfoC(C.Structure):        # 40 bytes
+    _fields_ = [("abi_version", C.c_uint32), ("phase", C.c_uint32),
+                ("talker_position", C.c_uint32), ("semantic_history_count", C.c_uint32),
+                ("frames_generated", C.c_uint64), ("device_sample_count", C.c_uint64),
+                ("host_sync_count", C.c_uint64)]
+
+
+class ModelMemoryC(C.Structure):      # 16 bytes
+    _fields_ = [("shared_weight_bytes", C.c_uint64), ("tensor_count", C.c_uint32),
+                ("device_index", C.c_int32)]
+
+
+class SessionMemoryC(C.Structure):    # 32 bytes
+    _fields_ = [("talker_kv_bytes", C.c_uint64), ("predictor_kv_bytes", C.c_uint64),
+                ("workspace_bytes", C.c_uint64), ("max_sequence_length", C.c_uint32),
+                ("reserved", C.c_uint32)]
+
+
+class PrimitiveParityC(C.Structure):
+    _fields_ = [("rms_norm_max_absolute_error", C.c_float), ("rope_max_absolute_error", C.c_float),
+                ("attention_max_absolute_error", C.c_float), ("silu_gate_max_absolute_error", C.c_float)]
+
+
+class GemvBenchmarkC(C.Structure):
+    _fields_ = [("input_features", C.c_int32), ("output_features", C.c_int32),
+                ("iterations", C.c_int32), ("reserved", C.c_int32), ("weight_bytes", C.c_uint64),
+                ("cold_launch_microseconds", C.c_float), ("mean_launch_microseconds", C.c_float),
+                ("tera_operations_per_second", C.c_float)]
+
+
+class DeviceInfoC(C.Structure):
+    _fields_ = [("device_index", C.c_int32), ("compute_major", C.c_int32),
+                ("compute_minor", C.c_int32), ("total_global_memory_bytes", C.c_uint64),
+                ("runtime_free_memory_bytes", C.c_uint64), ("runtime_total_memory_bytes", C.c_uint64),
+                ("device_name", C.c_char * 256)]
+
+
+# every symbol the headers in include/ declare
+EXPORTED_SYMBOLS = (
+    "qwen3_tts_talker_abi_version", "qwen3_tts_probe_device",
+    "qwen3_tts_validate_transformer_primitives", "qwen3_tts_model_create",
+    "qwen3_tts_model_destroy", "qwen3_tts_model_upload_tensor", "qwen3_tts_model_finalize",
+    "qwen3_tts_session_create", "qwen3_tts_session_destroy", "qwen3_tts_session_reset",
+    "qwen3_tts_session_prefill", "qwen3_tts_session_next_frame",
+    "qwen3_tts_session_next_frame_begin_v2", "qwen3_tts_session_next_frame_finish_v2",
+    "qwen3_tts_model_batch_next_frame_begin_v2", "qwen3_tts_session_state_info",
+    "q3t_launch_int8_gemm_rows", "q3t_launch_int8_gemm_rows_add",
+    "q3t_launch_int8_gate_up_silu_rows", "q3t_launch_int8_gemm_ex",
+    "q3t_launch_quantize_weight_rows", "q3t_benchmark_int8_gemv", "q3t_launch_rms_norm_rows",
+    "q3t_launch_head_rms_norm_rows", "q3t_launch_rope_rows_at", "q3t_launch_kv_scatter_rows",
+    "q3t_launch_bias_activation_rows", "q3t_launch_add_in_place", "q3t_launch_silu_gate",
+    "q3t_launch_gather_embedding_rows", "q3t_launch_add_embedding_rows",
+    "q3t_attention_scratch_bytes", "q3t_launch_batch_causal_gqa_attention_fast",
+    "q3t_launch_decode_attention_ex", "q3t_launch_sample_logits", "q3t_launch_sample_logits_at",
+    "q3t_model_set_option", "q3t_model_run_frames", "q3t_session_read_state",
+)
+
+_lib: Optional[C.CDLL] = None
+
+
+def library() -> C.CDLL:
+    """dlopen the CUDA library; fails loudly when it has not been built."""
+    global _lib
+    if _lib is None:
+        path = os.environ.get("QWEN3_TTS_TALKER_LIBRARY", LIBRARY_PATH)
+        if not os.path.exists(path):
+            raise ImportError(
+                f"{path} is missing: build it with `python qwen3-tts-native_b200/build.py` "
+                "(there is no CPU fallback for the decode path)")
+        lib = C.CDLL(path)
+        lib.qwen3_tts_talker_abi_version.restype = C.c_uint32
+        lib.q3t_attention_scratch_bytes.restype = C.c_size_t
+        lib.qwen3_tts_model_destroy.restype = None
+        lib.qwen3_tts_session_destroy.restype = None
+        lib.qwen3_tts_model_destroy.argtypes = [C.c_void_p]
+        lib.qwen3_tts_session_destroy.argtypes = [C.c_void_p]
+        lib.qwen3_tts_session_next_frame.argtypes = [
+            C.c_void_p, C.c_uint16, C.c_int32, SamplingConfigC, SamplingConfigC,
+            C.POINTER(C.c_uint16), C.c_size_t, C.POINTER(C.c_uint16), C.POINTER(FrameInfoC),
+            C.c_char_p, C.c_size_t]
+        lib.qwen3_tts_session_next_frame_begin_v2.argtypes = [
+            C.c_void_p, C.c_int32, SamplingConfigC, SamplingConfigC, C.POINTER(DeviceFrameViewV2C),
+            C.c_char_p, C.c_size_t]
+        lib.qwen3_tts_session_next_frame_finish_v2.argtypes = [
+            C.c_void_p, C.c_uint64, C.c_void_p, C.POINTER(C.c_uint16), C.POINTER(FrameInfoC),
+            C.c_char_p, C.c_size_t]
+        lib.qwen3_tts_session_prefill.argtypes = [
+            C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32, SamplingConfigC,
+            C.POINTER(PrefillResultC), C.c_char_p, C.c_size_t]
+        lib.qwen3_tts_model_batch_next_frame_begin_v2.argtypes = [
+            C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.POINTER(C.c_int32),
+            C.POINTER(SamplingConfigC), C.POINTER(SamplingConfigC), C.POINTER(DeviceFrameViewV2C),
+            C.c_char_p, C.c_size_t]
+        lib.qwen3_tts_model_upload_tensor.argtypes = [
+            C.c_void_p, C.c_char_p, C.c_void_p, C.c_uint64, C.c_int32, C.POINTER(C.c_uint64),
+            C.c_char_p, C.c_size_t]
+        lib.qwen3_tts_session_create.argtypes = [
+            C.c_void_p, C.c_int32, C.c_uint64, C.POINTER(C.c_void_p), C.POINTER(SessionMemoryC),
+            C.c_char_p, C.c_size_t]
+        lib.qwen3_tts_session_reset.argtypes = [C.c_void_p, C.c_uint64, C.c_char_p, C.c_size_t]
+        lib.qwen3_tts_session_state_info.argtypes = [C.c_void_p, C.POINTER(StateInfoC), C.c_char_p,
+                                                     C.c_size_t]
+        lib.qwen3_tts_model_create.argtypes = [C.c_int32, C.POINTER(C.c_void_p), C.c_char_p, C.c_size_t]
+        lib.qwen3_tts_model_finalize.argtypes = [C.c_void_p, C.POINTER(ModelMemoryC), C.c_char_p,
+                                                 C.c_size_t]
+        lib.q3t_model_run_frames.argtypes = [
+            C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, SamplingConfigC,
+            SamplingConfigC, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_char_p, C.c_size_t]
+        lib.q3t_model_set_option.argtypes = [C.c_void_p, C.c_char_p, C.c_int32, C.c_char_p, C.c_size_t]
+        lib.q3t_session_read_state.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                               C.c_char_p, C.c_size_t]
+        _lib = lib
+    return _lib
+
+
+class NativeTalkerStatusError(RuntimeError):
+    """A call across the C ABI returned a negative status (native_talker.rs:32-57)."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"native talker status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+_ERR_CAP = 512
+
+
+def _check(status: int, err) -> None:
+    if status != STATUS_OK:
+        raise NativeTalkerStatusError(status, err.value.decode("utf-8", "replace"))
+
+
+@dataclass(frozen=True)
+class SamplingConfig:
+    """native_talker.rs:404-445"""
+    do_sample: bool = True
+    top_k: int = 50
+    top_p: float = 1.0
+    temperature: float = 0.9
+    repetition_penalty: float = 1.0
+
+    @staticmethod
+    def official_talker_defaults() -> "SamplingConfig":
+        return SamplingConfig(True, 50, 1.0, 0.9, 1.05)
+
+    @staticmethod
+    def official_predictor_defaults() -> "SamplingConfig":
+        return SamplingConfig(True, 50, 1.0, 0.9, 1.0)
+
+    @staticmethod
+    def greedy() -> "SamplingConfig":
+        return SamplingConfig(False, 0, 1.0, 1.0, 1.0)
+
+    def to_c(self) -> SamplingConfigC:
+        return SamplingConfigC(int(self.do_sample), int(self.top_k), float(self.top_p),
+                               float(self.temperature), float(self.repetition_penalty))
+
+
+@dataclass(frozen=True)
+class StreamingCodecFrame:
+    codes: Tuple[int, ...]
+    next_semantic_token: int
+    ended_by_eos: bool
+    talker_position: int
+    predictor_gpu_milliseconds: float
+    talker_gpu_milliseconds: float
+
+
+@dataclass(frozen=True)
+class SessionRuntimeState:
+    abi_version: int
+    phase: int
+    talker_position: int
+    semantic_history_count: int
+    frames_generated: int
+    device_sample_count: int
+    host_sync_count: int
+
+
+class PendingTalkerFrame:
+    """A begun frame whose codes live on the device until finish (native_talker.rs:548-626)."""
+
+    def __init__(self, session: "NativeTalkerSession", view: DeviceFrameViewV2C):
+        self._session = session
+        self.view = view
+
+    @property
+    def lease_id(self) -> int:
+        return int(self.view.lease_id)
+
+    @property
+    def device_codes(self) -> int:
+        return int(self.view.device_codes or 0)
+
+    @property
+    def ready_event(self) -> int:
+        return int(self.view.ready_event or 0)
+
+    def finish(self, consumer_done_event: int = 0) -> StreamingCodecFrame:
+        return self._session._finish(self.lease_id, consumer_done_event)
+
+    def finish_without_consumer(self) -> StreamingCodecFrame:
+        return self.finish(0)
+
+
+class NativeTalkerModel:
+    """Shared weights on one GPU (native_talker.rs:705-1215)."""
+
+    def __init__(self, handle: int, memory: ModelMemoryC, device_index: int):
+        self._handle = C.c_void_p(handle)
+        self.memory = memory
+        self.device_index = device_index
+
+    @staticmethod
+    def create(device_index: int = 0) -> "NativeTalkerModel":
+        lib = library()
+        err = C.create_string_buffer(_ERR_CAP)
+        handle = C.c_void_p()
+        _check(lib.qwen3_tts_model_create(device_index, C.byref(handle), err, _ERR_CAP), err)
+        return NativeTalkerModel(handle.value, ModelMemoryC(), device_index)
+
+    @staticmethod
+    def load(device_index: int, tensors: Iterable[Tuple[str, np.ndarray]]) -> "NativeTalkerModel":
+        """Uploads every (name, bf16 bit-pattern array) pair and finalizes."""
+        model = NativeTalkerModel.create(device_index)
+        try:
+            for name, array in tensors:
+                model.upload_tensor(name, array)
+            model.finalize()
+        except Exception:
+            model.close()
+            raise
+        return model
+
+    def upload_tensor(self, name: str, array: np.ndarray) -> None:
+        a = np.ascontiguousarray(array)
+        if a.dtype != np.uint16:
+            raise TypeError("tensors are passed as bf16 bit patterns (uint16)")
+        shape = (C.c_uint64 * a.ndim)(*a.shape)
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().qwen3_tts_model_upload_tensor(
+            self._handle, name.encode(), a.ctypes.data_as(C.c_void_p), a.nbytes, a.ndim, shape,
+            err, _ERR_CAP), err)
+
+    def finalize(self) -> ModelMemoryC:
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().qwen3_tts_model_finalize(self._handle, C.byref(self.memory), err, _ERR_CAP), err)
+        return self.memory
+
+    def set_option(self, key: str, value: int) -> None:
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().q3t_model_set_option(self._handle, key.encode(), int(value), err, _ERR_CAP), err)
+
+    def talker_abi_version(self) -> int:
+        return int(library().qwen3_tts_talker_abi_version())
+
+    def supports_device_frames(self) -> bool:
+        return True
+
+    def supports_batch_frames(self) -> bool:
+        return True
+
+    def create_session(self, max_sequence_length: int, seed: int) -> "NativeTalkerSession":
+        err = C.create_string_buffer(_ERR_CAP)
+        handle = C.c_void_p()
+        memory = SessionMemoryC()
+        _check(library().qwen3_tts_session_create(self._handle, max_sequence_length, seed,
+                                                  C.byref(handle), C.byref(memory), err, _ERR_CAP), err)
+        return NativeTalkerSession(self, handle.value, memory)
+
+    def start_prompt(self, text_ids: Sequence[int], codec_ids: Sequence[int],
+                     max_sequence_length: int, seed: int,
+                     talker_sampling: SamplingConfig = SamplingConfig.official_talker_defaults(),
+                     predictor_sampling: SamplingConfig = SamplingConfig.official_predictor_defaults(),
+                     ) -> "NativeTalkerSession":
+        """create + prefill (native_talker.rs:911-980)"""
+        session = self.create_session(max_sequence_length, seed)
+        try:
+            session.talker_sampling = talker_sampling
+            session.predictor_sampling = predictor_sampling
+            session.prefill(text_ids, codec_ids)
+        except Exception:
+            session.close()
+            raise
+        return session
+
+    def batch_begin_device_frames(self, sessions: Sequence["NativeTalkerSession"],
+                                  trailing_text_ids: Sequence[int]) -> list:
+        """One lockstep frame for all sessions (native_talker.rs:314-380)."""
+        n = len(sessions)
+        handles = (C.c_void_p * n)(*[s._handle for s in sessions])
+        trailing = (C.c_int32 * n)(*[int(t) for t in trailing_text_ids])
+        talker = (SamplingConfigC * n)(*[s.talker_sampling.to_c() for s in sessions])
+        predictor = (SamplingConfigC * n)(*[s.predictor_sampling.to_c() for s in sessions])
+        views = (DeviceFrameViewV2C * n)()
+        for v in views:
+            v.struct_size = C.sizeof(DeviceFrameViewV2C)
+            v.reserved = 0
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().qwen3_tts_model_batch_next_frame_begin_v2(
+            self._handle, handles, n, trailing, talker, predictor, views, err, _ERR_CAP), err)
+        out = []
+        for s, v in zip(sessions, views):
+            copy = DeviceFrameViewV2C.from_buffer_copy(v)
+            out.append(PendingTalkerFrame(s, copy))
+        return out
+
+    def run_frames(self, sessions: Sequence["NativeTalkerSession"], frames: int,
+                   trailing_text_id: int = 0, want_frame_ms: bool = False):
+        """Frame loop with no host round trip per frame; returns (total_ms, frame_ms|None)."""
+        n = len(sessions)
+        handles = (C.c_void_p * n)(*[s._handle for s in sessions])
+        per_frame = (C.c_float * frames)() if want_frame_ms else None
+        total = C.c_float(0.0)
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().q3t_model_run_frames(
+            self._handle, handles, n, frames, trailing_text_id,
+            sessions[0].talker_sampling.to_c(), sessions[0].predictor_sampling.to_c(),
+            per_frame, C.byref(total), err, _ERR_CAP), err)
+        return float(total.value), (np.array(per_frame[:], dtype=np.float32) if want_frame_ms else None)
+
+    def close(self) -> None:
+        if self._handle:
+            library().qwen3_tts_model_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class NativeTalkerSession:
+    """One utterance: KV cache, RNG, history (native_talker.rs:720-762, 1217-1648)."""
+
+    def __init__(self, model: NativeTalkerModel, handle: int, memory: SessionMemoryC):
+        self._model = model
+        self._handle = C.c_void_p(handle)
+        self.memory = memory
+        self.talker_sampling = SamplingConfig.official_talker_defaults()
+        self.predictor_sampling = SamplingConfig.official_predictor_defaults()
+        self.current_semantic_token = 0
+        self.frames_emitted = 0
+        self.ended = False
+
+    def memory_usage(self) -> SessionMemoryC:
+        return self.memory
+
+    def reset(self, seed: int) -> None:
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().qwen3_tts_session_reset(self._handle, seed, err, _ERR_CAP), err)
+        self.current_semantic_token = 0
+        self.frames_emitted = 0
+        self.ended = False
+
+    def prefill(self, text_ids: Sequence[int], codec_ids: Sequence[int]) -> PrefillResultC:
+        n = len(text_ids)
+        if len(codec_ids) != n:
+            raise ValueError("text and codec id arrays differ in length")
+        t = (C.c_int32 * max(n, 1))(*[int(x) for x in text_ids])
+        c = (C.c_int32 * max(n, 1))(*[int(x) for x in codec_ids])
+        out = PrefillResultC()
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().qwen3_tts_session_prefill(self._handle, t, c, n, self.talker_sampling.to_c(),
+                                                   C.byref(out), err, _ERR_CAP), err)
+        self.current_semantic_token = int(out.first_semantic_token)
+        self.ended = self.current_semantic_token == EOS
+        self.prefill_result = out
+        return out
+
+    def next_frame(self, trailing_text_id: int = 0) -> Optional[StreamingCodecFrame]:
+        """Host-visible frame (native_talker.rs:1279-1334)."""
+        if self.ended:
+            return None
+        codes = (C.c_uint16 * CODEBOOKS)()
+        nxt = C.c_uint16(0)
+        info = FrameInfoC()
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().qwen3_tts_session_next_frame(
+            self._handle, self.current_semantic_token, trailing_text_id, self.talker_sampling.to_c(),
+            self.predictor_sampling.to_c(), codes, CODEBOOKS, C.byref(nxt), C.byref(info), err,
+            _ERR_CAP), err)
+        return self._advance(tuple(int(c) for c in codes), nxt.value, info)
+
+    def begin_device_frame(self, trailing_text_id: int = 0) -> Optional[PendingTalkerFrame]:
+        """Device-resident frame (native_talker.rs:1340-1420)."""
+        if self.ended:
+            return None
+        view = DeviceFrameViewV2C()
+        view.struct_size = C.sizeof(DeviceFrameViewV2C)
+        view.reserved = 0
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().qwen3_tts_session_next_frame_begin_v2(
+            self._handle, trailing_text_id, self.talker_sampling.to_c(),
+            self.predictor_sampling.to_c(), C.byref(view), err, _ERR_CAP), err)
+        return PendingTalkerFrame(self, view)
+
+    def _finish(self, lease_id: int, consumer_done_event: int) -> StreamingCodecFrame:
+        nxt = C.c_uint16(0)
+        info = FrameInfoC()
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().qwen3_tts_session_next_frame_finish_v2(
+            self._handle, lease_id, C.c_void_p(consumer_done_event or None), C.byref(nxt),
+            C.byref(info), err, _ERR_CAP), err)
+        return self._advance((), nxt.value, info)
+
+    def _advance(self, codes, nxt: int, info: FrameInfoC) -> StreamingCodecFrame:
+        self.current_semantic_token = int(nxt)
+        self.frames_emitted += 1
+        self.ended = bool(info.ended_by_eos)
+        return StreamingCodecFrame(codes, int(nxt), bool(info.ended_by_eos), int(info.talker_position),
+                                   float(info.predictor_gpu_milliseconds),
+                                   float(info.talker_gpu_milliseconds))
+
+    def runtime_state(self) -> SessionRuntimeState:
+        out = StateInfoC()
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().qwen3_tts_session_state_info(self._handle, C.byref(out), err, _ERR_CAP), err)
+        return SessionRuntimeState(out.abi_version, out.phase, out.talker_position,
+                                   out.semantic_history_count, out.frames_generated,
+                                   out.device_sample_count, out.host_sync_count)
+
+    def read_state(self):
+        """(last_hidden bf16[2048], frame_tokens int32[16], rng_state) -- test hook."""
+        hidden = np.zeros(2048, dtype=np.uint16)
+        tokens = np.zeros(CODEBOOKS, dtype=np.int32)
+        rng = np.zeros(1, dtype=np.uint64)
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().q3t_session_read_state(self._handle, hidden.ctypes.data_as(C.c_void_p),
+                                                tokens.ctypes.data_as(C.c_void_p),
+                                                rng.ctypes.data_as(C.c_void_p), err, _ERR_CAP), err)
+        return hidden, tokens, int(rng[0])
+
+    def close(self) -> None:
+        if self._handle:
+            library().qwen3_tts_session_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def validate_transformer_primitives(device_index: int = 0) -> PrimitiveParityC:
+    out = PrimitiveParityC()
+    err = C.create_string_buffer(_ERR_CAP)
+    _check(library().qwen3_tts_validate_transformer_primitives(device_index, C.byref(out), err,
+                                                               _ERR_CAP), err)
+    return out
+
+
+def probe_device(device_index: int = 0) -> DeviceInfoC:
+    out = DeviceInfoC()
+    err = C.create_string_buffer(_ERR_CAP)
+    _check(library().qwen3_tts_probe_device(device_index, C.byref(out), err, _ERR_CAP), err)
+    return out
+
+
+def benchmark_int8_gemv(device_index: int, in_features: int, out_features: int, rows: int = 1,
+                        buffers: int = 16, iterations: int = 2000) -> GemvBenchmarkC:
+    out = GemvBenchmarkC()
+    err = C.create_string_buffer(_ERR_CAP)
+    _check(library().q3t_benchmark_int8_gemv(device_index, in_features, out_features, rows, buffers,
+                                             iterations, C.byref(out), err, _ERR_CAP), err)
+    return out
