@@ -1,0 +1,380 @@
+"""Benchmark of the Qwen3-TTS decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" is one codec frame (16 code-predictor positions + one talker decode step) for
+every session of the batch.  Workload: 64 concurrent sessions per GPU with ragged KV lengths
+uniform in [64, 2048] over a paged bf16 KV cache (BASELINE.json configs[3]/[4] shapes),
+synthetic int8 per-channel weights of the real architecture, sampling T=0.9 / top-k 50 /
+top-p 0.9.  Prints ONE JSON line:
+
+  value      codec frames/s over all GPUs, frames enqueued back to back with all state resident
+             in HBM (q3t_model_run_frames), timed with CUDA events, max over ranks
+  e2e        the same metric through the drop-in C ABI the reference's host calls
+             (qwen3_tts_model_batch_next_frame_begin_v2 + ..._finish_v2 per frame) with a host
+             round trip per frame: frame table up, next tokens and codes down
+  b1         the B=1 numbers (one session at KV length 512, BASELINE.json configs[1]/[2])
+  roofline   the batch-1 int8 GEMV (configs[0], 2048 -> 6144) against the measured HBM peak
+  cpu_baseline  the oracle's CPU restatement timed on this host's cores on a bounded sample
+
+--impl reference times that CPU restatement as its own arm (the reference has no CPU
+implementation of this path and its host is Rust, which this image cannot build).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SESSIONS = 64
+GEMV_BYTES = 6144 * 2048 + 6144 * 4 + 2048 * 2 + 6144 * 2          # W + scales + x + y
+TALKER_WEIGHT_BYTES = 1_423_966_208 + 2_322_432                      # int8 rows + fp32 scales
+PREDICTOR_FRAME_BYTES = 1_323_302_912
+KV_BYTES_PER_TOKEN = 28 * 2 * 1024 * 2                               # all layers, K and V
+
+
+def frame_bytes(lengths) -> int:
+    """Algorithmic HBM bytes of one lockstep frame: weights once, every session's KV once."""
+    return TALKER_WEIGHT_BYTES + PREDICTOR_FRAME_BYTES + KV_BYTES_PER_TOKEN * int(sum(lengths))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device = device
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ CPU restatement, timed
+
+def cpu_frame_seconds(repeats: int = 1):
+    """Times the oracle (oracle/q3t_oracle.c, OpenMP over output rows) on a bounded sample of one
+    B=1 frame -- one talker layer at KV length 513, one predictor layer, the heads and the
+    sampler, with the real shapes -- and scales it to a whole frame (28 talker layers, 16 x 5
+    predictor layers, 16 small projections and heads).  Returns (seconds per frame, threads,
+    description)."""
+    from oracle import oracle as o
+    o.build()
+    rng = np.random.default_rng(0)
+
+    def layer(hidden, inter, qw, kvw):
+        def q(n, k):
+            return (rng.integers(-127, 128, size=(n, k), dtype=np.int8),
+                    (rng.uniform(0.5, 1.5, size=n) / (73.6 * np.sqrt(k))).astype(np.float32))
+        ones = o.to_bf16(np.ones(hidden, dtype=np.float32))
+        hd = o.to_bf16(np.ones(128, dtype=np.float32))
+        return dict(input_norm=ones, qkv=q(qw + 2 * kvw, hidden), o=q(hidden, qw), q_norm=hd,
+                    k_norm=hd, post_norm=ones, gate_up=q(2 * inter, hidden), down=q(hidden, inter))
+
+    talker = layer(2048, 6144, 2048, 1024)
+    predictor = layer(1024, 3072, 2048, 1024)
+    kc = o.to_bf16(rng.standard_normal((513, 1024)).astype(np.float32))
+    vc = o.to_bf16(rng.standard_normal((513, 1024)).astype(np.float32))
+    pk = np.zeros((16, 1024), dtype=np.uint16)
+    pv = np.zeros((16, 1024), dtype=np.uint16)
+    h = o.to_bf16(rng.standard_normal(2048).astype(np.float32))
+    ph = o.to_bf16(rng.standard_normal(1024).astype(np.float32))
+    head_w = rng.integers(-127, 128, size=(3072, 2048), dtype=np.int8)
+    head_s = np.full(3072, 1.0 / 3000.0, dtype=np.float32)
+    phead_w = rng.integers(-127, 128, size=(2048, 1024), dtype=np.int8)
+    mtp_w = rng.integers(-127, 128, size=(1024, 2048), dtype=np.int8)
+    pdims = o.predictor_dims(128)
+
+    def timed(fn):
+        best = None
+        for _ in range(max(1, repeats)):
+            t0 = time.perf_counter()
+            fn()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        return best
+
+    t_talker = timed(lambda: o.decoder_layer(h, talker, o.TALKER_DIMS, kc, vc, 512))
+    t_pred = timed(lambda: o.decoder_layer(ph, predictor, pdims, pk, pv, 8))
+    t_head = timed(lambda: o.sample(o.int8_gemm_rows(head_w, head_s, h)[0], 1, suppress=True,
+                                    top_k=50, top_p=0.9))
+    t_phead = timed(lambda: o.sample(o.int8_gemm_rows(phead_w, head_s[:2048], ph)[0], 1, top_k=50))
+    t_mtp = timed(lambda: o.int8_gemm_rows(mtp_w, head_s[:1024], h))
+    t_text = 2 * timed(lambda: o.int8_gemm_rows(head_w[:2048], head_s[:2048], h))
+    frame = 28 * t_talker + 16 * 5 * t_pred + t_head + 15 * t_phead + 16 * t_mtp + t_text
+    sample = ("1 talker layer (L=513) + 1 predictor layer + heads + samplers of a B=1 frame, real "
+              "shapes, scaled x28 / x80 / x16 to one frame")
+    return frame, o.threads(), sample
+
+
+def run_reference_arm(args, rank: int) -> None:
+    """CPU arm: the restatement of the reference's kernels on this host's cores."""
+    if rank != 0:
+        return
+    for _ in range(max(0, min(args.warmup, 2))):
+        cpu_frame_seconds()
+    times = [cpu_frame_seconds()[0] for _ in range(max(1, min(args.steps, 5)))]
+    frame_s = float(np.mean(times))
+    _, threads, sample = cpu_frame_seconds()
+    value = 1.0 / frame_s
+    line = {
+        "impl": "reference", "metric": "codec frames/s", "value": value, "unit": "frames/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": frame_s * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 weights x bf16 activations, fp32 accumulate",
+        "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "frames/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference has no CPU implementation of this path and no Rust toolchain is "
+                "available; this is the C restatement of its kernels (oracle/), frames are "
+                "sequential on the CPU so the rate does not grow with the session count",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int):
+    return {"workload": "64 lockstep sessions/GPU, talker (28 layers, 2048 hidden) + code predictor "
+                        "(5 layers, 16 positions) per frame, ragged KV U[64,2048], 16-token paged "
+                        "bf16 KV, int8 per-channel weights, T=0.9 top-k 50 top-p 0.9",
+            "sessions_per_gpu": SESSIONS, "global_sessions": SESSIONS * n_gpus,
+            "kv_lengths": "randint(64, 2048, seed 3 + rank)", "parallelism": f"dp{n_gpus}",
+            "l2": "inputs larger than L2: 2.7 GB of weights and ~7.7 GB of KV per frame stream "
+                  "from HBM; the predictor's 112 MB weight set may stay L2-resident across its 16 "
+                  "positions, which is inherent to the workload"}
+
+
+def percentile(values, q):
+    return float(np.percentile(np.asarray(values, dtype=np.float64), q)) if len(values) else None
+
+
+def make_sessions(q3t, model, count, lengths, frames_needed, talker_cfg, predictor_cfg, seed0):
+    sessions = []
+    for i in range(count):
+        cap = min(8192, (int(lengths[i]) + frames_needed + 16 + 15) // 16 * 16)
+        s = model.create_session(cap, seed0 + i)
+        s.talker_sampling = talker_cfg
+        s.predictor_sampling = predictor_cfg
+        s.synthetic_prefill(int(lengths[i]), seed0 + i)
+        sessions.append(s)
+    return sessions
+
+
+def api_frames(model, sessions, frames, trailing=11):
+    """The call sequence of the reference's host: one lockstep begin, then every session's finish."""
+    for _ in range(frames):
+        if len(sessions) == 1:
+            sessions[0].next_frame(trailing)
+        else:
+            pending = model.batch_begin_device_frames(sessions, [trailing] * len(sessions))
+            for p in pending:
+                p.finish_without_consumer()
+
+
+def run_ours(args, rank: int, local_rank: int, world: int) -> None:
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); "
+                         "use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    q3t = importlib.import_module("qwen3-tts-native_b200")
+    synth = importlib.import_module("qwen3-tts-native_b200.synth")
+    native = q3t.native
+
+    model = q3t.NativeTalkerModel.load(local_rank, synth.checkpoint_cuda(local_rank, seed=0))
+    model.set_option("mask_eos", 1)
+    model.set_option("batch_host_codes", 1)
+    talker_cfg = q3t.SamplingConfig(True, 50, 0.9, 0.9, 1.0)
+    predictor_cfg = q3t.SamplingConfig(True, 50, 0.9, 0.9, 1.0)
+    K, W = args.steps, args.warmup
+    total_frames = 2 * (K + W) + 8
+
+    lengths = np.random.default_rng(3 + rank).integers(64, 2049, size=SESSIONS)
+    sessions = make_sessions(q3t, model, SESSIONS, lengths, total_frames, talker_cfg, predictor_cfg,
+                             1 + 1000 * rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident frame loop -----------------------------------------------------
+    model.run_frames(sessions, W, trailing_text_id=11)
+    launches_before = model.kernel_launches()
+    barrier()
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    total_ms, per_frame = model.run_frames(sessions, K, trailing_text_id=11, want_frame_ms=True)
+    barrier()
+    clock_report = clocks.stop()
+    launches = model.kernel_launches() - launches_before
+    elapsed = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    elapsed_s = float(elapsed.item()) * 1e-3
+    value = world * SESSIONS * K / elapsed_s
+
+    # ---- the same loop through the public C ABI, host round trip per frame ------------------
+    api_frames(model, sessions, W)
+    barrier()
+    t0 = time.perf_counter()
+    api_frames(model, sessions, K)
+    torch.cuda.synchronize()
+    api_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(api_s, op=dist.ReduceOp.MAX)
+    e2e_value = world * SESSIONS * K / float(api_s.item())
+    table_bytes = 64 * (3 * 4 + 8 * 8 + 2 * 20)      # sizeof(FrameTable)
+    e2e = {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": table_bytes,
+           "d2h_bytes_per_step": SESSIONS * (4 + 32),
+           "api": "qwen3_tts_model_batch_next_frame_begin_v2 + qwen3_tts_session_next_frame_finish_v2"}
+
+    lengths_now = [int(l) + W for l in lengths]
+    fbytes = frame_bytes(lengths_now)
+    hbm_peak, peak_kind = measured_peaks()
+    frame_s = elapsed_s / K
+    line = {
+        "metric": "codec frames/s", "value": value, "unit": "frames/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": frame_s * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 weights x bf16 activations, fp32 accumulate", "data": "synthetic",
+        "config": workload_config(world), "clocks": clock_report, "e2e": e2e,
+        "gpu_launches": int(launches),
+        "frame_latency_ms": {"p50": percentile(per_frame, 50), "p99": percentile(per_frame, 99)},
+        "frame_roofline": {"bound": "hbm", "achieved": fbytes / frame_s / 1e9, "peak": hbm_peak,
+                           "unit": "GB/s", "frac": fbytes / frame_s / 1e9 / hbm_peak,
+                           "algorithmic_bytes_per_frame": fbytes, "peak_kind": peak_kind,
+                           "frac_of_8TBs": fbytes / frame_s / 8.0e12},
+    }
+    for s in sessions:
+        s.close()
+
+    if rank == 0:
+        # ---- B=1: one session at KV length 512 (configs[1] + configs[2]) ------------------------
+        one = make_sessions(q3t, model, 1, [512], 2 * (K + W) + 80, talker_cfg, predictor_cfg, 77)
+        k1 = max(K, 50)
+        model.run_frames(one, W, trailing_text_id=11)
+        torch.cuda.synchronize()
+        ms1, per1 = model.run_frames(one, k1, trailing_text_id=11, want_frame_ms=True)
+        api_frames(model, one, W)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        api_frames(model, one, K)
+        torch.cuda.synchronize()
+        api1 = time.perf_counter() - t0
+        b1_bytes = frame_bytes([513 + W])
+        line["b1"] = {"value": k1 / (ms1 * 1e-3), "unit": "frames/s", "ms_per_frame": ms1 / k1,
+                      "e2e_value": K / api1, "p50_ms": percentile(per1, 50), "p99_ms": percentile(per1, 99),
+                      "roofline_frac": b1_bytes / (ms1 * 1e-3 / k1) / 1e9 / hbm_peak,
+                      "frac_of_8TBs": b1_bytes / (ms1 * 1e-3 / k1) / 8.0e12,
+                      "api": "qwen3_tts_session_next_frame"}
+        one[0].close()
+        # ---- batch-1 int8 GEMV, configs[0]: 16 weight images (201 MB > L2) round-robin --------------
+        g = native.benchmark_int8_gemv(local_rank, 2048, 6144, rows=1, buffers=16, iterations=4000)
+        gemv_s = g.mean_launch_microseconds * 1e-6
+        line["roofline"] = {"bound": "hbm", "kernel": "gemv_rows_kernel<1> 2048->6144 (configs[0])",
+                            "achieved": GEMV_BYTES / gemv_s / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                            "frac": GEMV_BYTES / gemv_s / 1e9 / hbm_peak, "peak_kind": peak_kind,
+                            "frac_of_8TBs": GEMV_BYTES / gemv_s / 8.0e12,
+                            "us_per_launch": g.mean_launch_microseconds, "traffic": None,
+                            "bytes_per_launch": GEMV_BYTES}
+        if world == 1 and not args.no_cpu_baseline:
+            frame_cpu, threads, sample = cpu_frame_seconds()
+            line["cpu_baseline"] = {"value": 1.0 / frame_cpu, "unit": "frames/s", "cores": threads,
+                                    "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    model.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -196,7 +196,8 @@ QWEN3_TTS_API int32_t q3t_launch_sample_logits_at(
 /* ---- engine extras --------------------------------------------------------------------- */
 
 /* Options: "mask_eos" (1: the talker sampler also masks EOS, for synthetic weights whose
- * logits would otherwise end a run at random), "use_graphs" (0: launch kernels one by one). */
+ * logits would otherwise end a run at random), "use_graphs" (0: launch kernels one by one),
+ * "batch_host_codes" (1: lockstep batches also mirror each frame's 16 codes to host memory). */
 QWEN3_TTS_API int32_t q3t_model_set_option(Qwen3TtsModelHandle model, const char* key,
                                            int32_t value, char* error, size_t error_capacity);
 
@@ -212,6 +213,18 @@ QWEN3_TTS_API int32_t q3t_model_run_frames(Qwen3TtsModelHandle model,
                                            Qwen3TtsSamplingConfig predictor_sampling,
                                            float* frame_milliseconds, float* total_milliseconds,
                                            char* error, size_t error_capacity);
+
+/* Benchmark harness: puts a READY session into the PREFILLED phase at `position` without a
+ * prompt.  KV rows [0, position) and the last hidden state get seeded pseudo-random N(0,1)
+ * values, the semantic history one token (the benchmark configurations ask for a KV cache
+ * "pre-filled with N(0,1) values"; values do not influence timing). */
+QWEN3_TTS_API int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle session, int32_t position,
+                                                    uint64_t seed, char* error,
+                                                    size_t error_capacity);
+
+/* Number of this library's kernels launched so far through frame graphs of the model. */
+QWEN3_TTS_API int32_t q3t_model_kernel_launches(Qwen3TtsModelHandle model, uint64_t* launches,
+                                                char* error, size_t error_capacity);
 
 /* Test hook: host copies of a session's device state (any pointer may be NULL):
  * last_hidden [2048] bf16, frame_tokens [16], random_state [1]. */

@@ -435,6 +435,10 @@ class OracleSession:
         w, s = self.m.q["talker.codec_head.weight"]
         logits = int8_gemm_rows(w, s, n)[0]
         self.trace["talker_logits"] = logits
+        if getattr(self, "mask_eos", False):
+            # harness option for random weights: EOS is masked like a reserved token
+            logits = logits.copy()
+            logits[EOS] = 0xFF80   # -inf
         tok, self.rng = sample(logits, self.rng, suppress=True, history=self.history, **cfg)
         self.history.append(tok)
         return tok

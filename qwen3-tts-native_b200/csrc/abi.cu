@@ -837,6 +837,8 @@ int32_t q3t_model_set_option(Qwen3TtsModelHandle model, const char* key, int32_t
             m->mask_eos = value != 0;
         } else if (std::strcmp(key, "use_graphs") == 0) {
             m->use_graphs = value != 0;
+        } else if (std::strcmp(key, "batch_host_codes") == 0) {
+            m->batch_host_codes = value != 0;
         } else {
             throw std::runtime_error(std::string("unknown model option: ") + key);
         }
@@ -866,6 +868,22 @@ int32_t q3t_model_run_frames(Qwen3TtsModelHandle model, Qwen3TtsSessionHandle* s
                             trailing_text_token_id, params_of(talker_sampling),
                             params_of(predictor_sampling), frame_milliseconds, total_milliseconds);
     }, QWEN3_TTS_TALKER_STATUS_STATE, error, error_capacity);
+}
+
+int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle session, int32_t position, uint64_t seed,
+                                      char* error, size_t error_capacity) {
+    return protect([&] { session_of(session)->synthetic_prefill(position, seed); },
+                   QWEN3_TTS_TALKER_STATUS_STATE, error, error_capacity);
+}
+
+int32_t q3t_model_kernel_launches(Qwen3TtsModelHandle model, uint64_t* launches, char* error,
+                                  size_t error_capacity) {
+    if (launches == nullptr) {
+        write_error(error, error_capacity, "launch counter output pointer is null");
+        return QWEN3_TTS_TALKER_STATUS_INVALID_ARGUMENT;
+    }
+    return protect([&] { *launches = model_of(model)->kernel_launches.load(); },
+                   QWEN3_TTS_TALKER_STATUS_STATE, error, error_capacity);
 }
 
 int32_t q3t_session_read_state(Qwen3TtsSessionHandle session, uint16_t* last_hidden,

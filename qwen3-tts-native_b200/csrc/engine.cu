@@ -539,8 +539,23 @@ void enqueue_prompt_step(Workspace& w, Model& m, const int* text_ids, const int*
     check_cuda(launch_advance_position(table, s), "advance position");
 }
 
+int count_kernel_nodes(cudaGraph_t graph) {
+    size_t total = 0;
+    if (cudaGraphGetNodes(graph, nullptr, &total) != cudaSuccess || total == 0) return 0;
+    std::vector<cudaGraphNode_t> nodes(total);
+    if (cudaGraphGetNodes(graph, nodes.data(), &total) != cudaSuccess) return 0;
+    int kernels = 0;
+    for (size_t i = 0; i < total; ++i) {
+        cudaGraphNodeType type;
+        if (cudaGraphNodeGetType(nodes[i], &type) == cudaSuccess && type == cudaGraphNodeTypeKernel) {
+            ++kernels;
+        }
+    }
+    return kernels;
+}
+
 template <class Enqueue>
-cudaGraphExec_t capture(cudaStream_t s, Enqueue&& enqueue) {
+cudaGraphExec_t capture(cudaStream_t s, Enqueue&& enqueue, int* kernel_nodes = nullptr) {
     check_cuda(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
     cudaGraph_t graph = nullptr;
     try {
@@ -551,6 +566,7 @@ cudaGraphExec_t capture(cudaStream_t s, Enqueue&& enqueue) {
         throw;
     }
     check_cuda(cudaStreamEndCapture(s, &graph), "cudaStreamEndCapture");
+    if (kernel_nodes != nullptr) *kernel_nodes = count_kernel_nodes(graph);
     cudaGraphExec_t exec = nullptr;
     const cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
     cudaGraphDestroy(graph);
@@ -745,9 +761,11 @@ Workspace::Graphs& Session::frame_graphs(Workspace& w, Model& m, int n, int spli
     auto found = w.graphs.find(key);
     if (found != w.graphs.end()) return found->second;
     Workspace::Graphs g;
-    g.predictor = capture(w.stream, [&] { enqueue_predictor(w, m, n, w.stream); });
+    g.predictor = capture(w.stream, [&] { enqueue_predictor(w, m, n, w.stream); },
+                          &g.predictor_kernels);
     try {
-        g.talker = capture(w.stream, [&] { enqueue_talker(w, m, n, splits, w.stream); });
+        g.talker = capture(w.stream, [&] { enqueue_talker(w, m, n, splits, w.stream); },
+                           &g.talker_kernels);
     } catch (...) {
         cudaGraphExecDestroy(g.predictor);
         throw;
@@ -786,6 +804,7 @@ void Session::launch_frame(Workspace& w, Model& m, Session** s, int n, bool uplo
         check_cuda(cudaEventRecord(w.talker_start, w.stream), "cudaEventRecord");
         check_cuda(cudaGraphLaunch(g.talker, w.stream), "cudaGraphLaunch(talker)");
         check_cuda(cudaEventRecord(w.talker_stop, w.stream), "cudaEventRecord");
+        m.kernel_launches += static_cast<uint64_t>(g.predictor_kernels + g.talker_kernels);
     } else {
         check_cuda(cudaEventRecord(w.predictor_start, w.stream), "cudaEventRecord");
         enqueue_predictor(w, m, n, w.stream);
@@ -869,11 +888,12 @@ void Session::batch_begin(Model* model, Session** s, int n, const int* trailing_
         s[i]->validate_begin(s[i]->current_token_, trailing_text[i], talker[i], predictor[i]);
     }
     Workspace& w = model->batch_workspace();
-    for (int i = 0; i < n; ++i) s[i]->take_lease(&w, false);
+    const bool host_codes = model->batch_host_codes != 0;
+    for (int i = 0; i < n; ++i) s[i]->take_lease(&w, host_codes);
     try {
         check_cuda(cudaEventSynchronize(w.table_uploaded), "cudaEventSynchronize(table)");
         for (int i = 0; i < n; ++i) {
-            s[i]->fill_row(*w.host_table, i, trailing_text[i], talker[i], predictor[i], false);
+            s[i]->fill_row(*w.host_table, i, trailing_text[i], talker[i], predictor[i], host_codes);
         }
         // order the batch stream after each session's earlier work
         for (int i = 0; i < n; ++i) {
@@ -1088,6 +1108,36 @@ void Session::run_frames(Model* model, Session** s, int n, int frames, int trail
         throw;
     }
     for (cudaEvent_t ev : marks) cudaEventDestroy(ev);
+}
+
+void Session::synthetic_prefill(int position, uint64_t seed) {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(synthetic prefill)");
+    if (poisoned_) throw std::runtime_error("talker session is poisoned and must be destroyed");
+    if (frame_in_flight_) throw std::runtime_error("a device frame lease is in flight");
+    if (position < 1 || position >= max_seq_) {
+        throw std::runtime_error("synthetic prefill position must be in [1, max_sequence_length)");
+    }
+    Workspace& w = *solo_;
+    Model& m = *model_;
+    Session* self = this;
+    bind_rows(w, &self, 1);
+    const int pages = (position + kPageTokens - 1) / kPageTokens;
+    const KvPool& pool = *m.talker_pool;
+    check_cuda(launch_fill_kv_pages(pool.slab_table(), pool.slab_shift(), pool.page_elems(),
+                                    pool.plane_elems(), w.talker_pages.as<int>(), pages,
+                                    pool.layers() * 2, seed * 2 + 1, w.stream), "fill KV pages");
+    check_cuda(launch_fill_normal(d_last_hidden_, 2048, seed * 2 + 2, w.stream), "fill last hidden");
+    const int token = static_cast<int>(seed % 2048);
+    check_cuda(cudaMemcpyAsync(d_sampled_, &token, sizeof(int), cudaMemcpyHostToDevice, w.stream),
+               "store semantic token");
+    check_cuda(cudaMemcpyAsync(d_history_, &token, sizeof(int), cudaMemcpyHostToDevice, w.stream),
+               "store semantic history");
+    check_cuda(cudaStreamSynchronize(w.stream), "cudaStreamSynchronize(synthetic prefill)");
+    position_ = position;
+    generated_ = 1;
+    current_token_ = static_cast<uint16_t>(token);
+    *h_token_ = token;
+    phase_ = kPhasePrefilled;
 }
 
 void Session::read_state(uint16_t* last_hidden, int* frame_tokens, unsigned long long* rng) const {

@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 
 #include <array>
+#include <atomic>
 #include <cstdint>
 #include <map>
 #include <memory>
@@ -78,6 +79,11 @@ public:
     void release(int page);
     KvLayout layout(int layer, const int* page_table, int table_stride) const;
     uint64_t page_bytes() const;    // K+V bytes of one page over all layers
+    bf16* const* slab_table() const { return slab_table_.as<bf16*>(); }
+    int slab_shift() const { return slab_shift_; }
+    int layers() const { return layers_; }
+    long long page_elems() const { return page_elems_; }
+    long long plane_elems() const { return plane_elems_; }
     static constexpr int kMaxSlabs = 512;
 private:
     void add_slab();
@@ -120,6 +126,8 @@ struct Workspace {
     struct Graphs {
         cudaGraphExec_t predictor = nullptr;
         cudaGraphExec_t talker = nullptr;
+        int predictor_kernels = 0;   // kernel nodes in each graph
+        int talker_kernels = 0;
     };
     std::map<std::pair<int, int>, Graphs> graphs;   // (rows, talker splits) -> graphs
     cudaEvent_t predictor_start = nullptr, predictor_stop = nullptr;
@@ -161,6 +169,8 @@ public:
     int mask_eos = 0;
     int use_graphs = 1;
     int option_epoch = 0;           // bumped when an option that captured graphs bake in changes
+    int batch_host_codes = 0;       // lockstep batches also mirror the 16 codes to pinned host memory
+    std::atomic<uint64_t> kernel_launches{0};   // kernels of this library launched through frame graphs
 
 private:
     struct Spec {
@@ -239,6 +249,10 @@ public:
 
     // parity-test hook: copies of the device-side state (any pointer may be null)
     void read_state(uint16_t* last_hidden, int* frame_tokens, unsigned long long* rng) const;
+    // Benchmark harness: puts the session in the PREFILLED phase at `position` without running a
+    // prompt: KV rows [0, position) and last_hidden are filled with seeded pseudo-random
+    // N(0,1) values, the semantic history gets one token.
+    void synthetic_prefill(int position, uint64_t seed);
 
 private:
     friend struct Workspace;

@@ -131,6 +131,42 @@ prompt_combine_kernel(const FrameTable* t, const int* __restrict__ text_ids,
     }
 }
 
+// ---- benchmark harness: seeded pseudo-random N(0,1) fills ------------------------------------
+
+__device__ __forceinline__ float hashed_normal(unsigned long long index, unsigned long long seed) {
+    unsigned long long z = index * 0x9e3779b97f4a7c15ULL + seed;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL;
+    z ^= z >> 31;
+    const float u1 = (static_cast<float>(z >> 40) + 1.0f) * (1.0f / 16777217.0f);
+    const float u2 = static_cast<float>((z >> 16) & 0xffffffull) * (1.0f / 16777216.0f);
+    return sqrtf(-2.0f * logf(u1)) * cosf(6.2831853f * u2);
+}
+
+__global__ void __launch_bounds__(kThreads)
+fill_normal_kernel(bf16* __restrict__ dst, size_t count, unsigned long long seed) {
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < count;
+         i += (size_t)gridDim.x * kThreads) {
+        dst[i] = f2bf(hashed_normal(i, seed));
+    }
+}
+
+// grid (pages, layers*2): block (p, plane) fills the 16 x kv_width page `page_ids[p]` of that
+// K or V plane
+__global__ void __launch_bounds__(kThreads)
+fill_kv_pages_kernel(bf16* const* slabs, int slab_shift, long long page_elems,
+                     long long plane_elems, const int* __restrict__ page_ids,
+                     unsigned long long seed) {
+    const int pid = page_ids[blockIdx.x];
+    bf16* dst = slabs[pid >> slab_shift] + (long long)blockIdx.y * plane_elems
+        + (long long)(pid & ((1 << slab_shift) - 1)) * page_elems;
+    const unsigned long long base =
+        ((unsigned long long)blockIdx.y * gridDim.x + blockIdx.x) * (unsigned long long)page_elems;
+    for (long long i = threadIdx.x; i < page_elems; i += kThreads) {
+        dst[i] = f2bf(hashed_normal(base + i, seed));
+    }
+}
+
 __global__ void advance_position_kernel(FrameTable* t) {
     if (threadIdx.x == 0 && blockIdx.x == 0) t->position[0] += 1;
 }
@@ -184,6 +220,23 @@ cudaError_t launch_prompt_combine(const FrameTable* table, const int* text_ids, 
                                   int width, cudaStream_t stream) {
     prompt_combine_kernel<<<4, kThreads, 0, stream>>>(table, text_ids, codec_ids, codec_embedding,
                                                       codec_vocabulary, hidden, width);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_fill_normal(bf16* dst, size_t count, unsigned long long seed, cudaStream_t stream) {
+    if (dst == nullptr || count == 0) return cudaErrorInvalidValue;
+    size_t blocks = (count + kThreads - 1) / kThreads;
+    if (blocks > 2048) blocks = 2048;
+    fill_normal_kernel<<<static_cast<unsigned int>(blocks), kThreads, 0, stream>>>(dst, count, seed);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_fill_kv_pages(bf16* const* slabs, int slab_shift, long long page_elems,
+                                 long long plane_elems, const int* page_ids, int pages, int planes,
+                                 unsigned long long seed, cudaStream_t stream) {
+    if (pages < 1 || planes < 1) return cudaErrorInvalidValue;
+    fill_kv_pages_kernel<<<dim3(pages, planes), kThreads, 0, stream>>>(slabs, slab_shift, page_elems,
+                                                                      plane_elems, page_ids, seed);
     return cudaGetLastError();
 }
 

@@ -199,6 +199,12 @@ cudaError_t launch_prompt_gather(const FrameTable* table, const int* text_ids,
 cudaError_t launch_prompt_combine(const FrameTable* table, const int* text_ids, const int* codec_ids,
                                   const bf16* codec_embedding, int codec_vocabulary, bf16* hidden,
                                   int width, cudaStream_t stream);
+// benchmark harness: seeded pseudo-random N(0,1) fills of a flat buffer / of whole KV pages
+// (grid over `pages` page ids and `planes` = layers*2 K/V planes of every slab)
+cudaError_t launch_fill_normal(bf16* dst, size_t count, unsigned long long seed, cudaStream_t stream);
+cudaError_t launch_fill_kv_pages(bf16* const* slabs, int slab_shift, long long page_elems,
+                                 long long plane_elems, const int* page_ids, int pages, int planes,
+                                 unsigned long long seed, cudaStream_t stream);
 // position[0] += 1 (prompt rows advance one KV slot per step)
 cudaError_t launch_advance_position(FrameTable* table, cudaStream_t stream);
 

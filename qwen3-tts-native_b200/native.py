@@ -108,6 +108,7 @@ EXPORTED_SYMBOLS = (
     "q3t_attention_scratch_bytes", "q3t_launch_batch_causal_gqa_attention_fast",
     "q3t_launch_decode_attention_ex", "q3t_launch_sample_logits", "q3t_launch_sample_logits_at",
     "q3t_model_set_option", "q3t_model_run_frames", "q3t_session_read_state",
+    "q3t_session_synthetic_prefill", "q3t_model_kernel_launches",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -164,6 +165,10 @@ def library() -> C.CDLL:
         lib.q3t_model_set_option.argtypes = [C.c_void_p, C.c_char_p, C.c_int32, C.c_char_p, C.c_size_t]
         lib.q3t_session_read_state.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                C.c_char_p, C.c_size_t]
+        lib.q3t_session_synthetic_prefill.argtypes = [C.c_void_p, C.c_int32, C.c_uint64, C.c_char_p,
+                                                      C.c_size_t]
+        lib.q3t_model_kernel_launches.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.c_char_p,
+                                                  C.c_size_t]
         _lib = lib
     return _lib
 
@@ -306,6 +311,12 @@ class NativeTalkerModel:
         err = C.create_string_buffer(_ERR_CAP)
         _check(library().q3t_model_set_option(self._handle, key.encode(), int(value), err, _ERR_CAP), err)
 
+    def kernel_launches(self) -> int:
+        out = C.c_uint64(0)
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().q3t_model_kernel_launches(self._handle, C.byref(out), err, _ERR_CAP), err)
+        return int(out.value)
+
     def talker_abi_version(self) -> int:
         return int(library().qwen3_tts_talker_abi_version())
 
@@ -423,6 +434,13 @@ class NativeTalkerSession:
         self.ended = self.current_semantic_token == EOS
         self.prefill_result = out
         return out
+
+    def synthetic_prefill(self, position: int, seed: int) -> None:
+        """Benchmark harness: PREFILLED at `position` with seeded random KV (no prompt run)."""
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().q3t_session_synthetic_prefill(self._handle, position, seed, err, _ERR_CAP), err)
+        self.current_semantic_token = seed % 2048
+        self.ended = False
 
     def next_frame(self, trailing_text_id: int = 0) -> Optional[StreamingCodecFrame]:
         """Host-visible frame (native_talker.rs:1279-1334)."""

@@ -239,11 +239,17 @@ def attention_ex(q, positions, q_heads, kv_heads, head_dim, *, k=None, v=None, p
     dq = _dev(np.asarray(q, dtype=np.uint16)); keep.append(dq)
     d.query = dq.data_ptr()
     if fused:
-        dkn, dvn = _dev(np.asarray(k_new, dtype=np.uint16)), _dev(np.asarray(v_new, dtype=np.uint16))
         dqn, dkw = _dev(np.asarray(q_norm_w, dtype=np.uint16)), _dev(np.asarray(k_norm_w, dtype=np.uint16))
-        keep += [dkn, dvn, dqn, dkw]
-        d.key_new, d.value_new = dkn.data_ptr(), dvn.data_ptr()
+        keep += [dqn, dkw]
         d.query_norm_weight, d.key_norm_weight = dqn.data_ptr(), dkw.data_ptr()
+        if k_new is None:
+            # q is the packed [rows][q | k | v] projection output; k and v start inside it
+            d.key_new = dq.data_ptr() + 2 * q_heads * head_dim
+            d.value_new = dq.data_ptr() + 2 * (q_heads * head_dim + kvw)
+        else:
+            dkn, dvn = _dev(np.asarray(k_new, dtype=np.uint16)), _dev(np.asarray(v_new, dtype=np.uint16))
+            keep += [dkn, dvn]
+            d.key_new, d.value_new = dkn.data_ptr(), dvn.data_ptr()
     dp = _dev(np.asarray(positions, dtype=np.int32)); keep.append(dp)
     d.positions = dp.data_ptr()
     do = torch.zeros((rows, q_heads * head_dim), dtype=torch.int16, device="cuda")

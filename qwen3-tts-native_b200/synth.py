@@ -92,6 +92,28 @@ def make_tensor(name: str, shape: Tuple[int, ...], seed: int = 0) -> np.ndarray:
     return t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
 
 
+def checkpoint_cuda(device: int, seed: int = 0,
+                    predictor_head_dim: int = 128) -> Iterator[Tuple[str, np.ndarray]]:
+    """Same distributions as checkpoint(), drawn with the GPU's generator (seconds instead of
+    a minute on a busy host; values differ from checkpoint()'s).  For benchmarks only: tests
+    that compare against the oracle use checkpoint(), whose values do not depend on the GPU."""
+    dev = torch.device("cuda", device)
+    g = torch.Generator(device=dev)
+    for name, shape in tensor_shapes(predictor_head_dim).items():
+        g.manual_seed((zlib.crc32(name.encode()) ^ (seed * 0x9E3779B1)) & 0x7FFFFFFF)
+        kind = _kind(name)
+        if kind == "norm":
+            t = 1.0 + 0.02 * torch.randn(shape, generator=g, device=dev)
+        elif kind == "small":
+            t = 0.02 * torch.randn(shape, generator=g, device=dev)
+        else:
+            rows, cols = shape
+            q = torch.randint(-127, 128, shape, generator=g, device=dev, dtype=torch.int8)
+            scale = (0.5 + torch.rand((rows, 1), generator=g, device=dev)) / (73.6 * float(cols) ** 0.5)
+            t = q.to(torch.float32) * scale
+        yield name, t.to(torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+
+
 def checkpoint(seed: int = 0, predictor_head_dim: int = 128) -> Iterator[Tuple[str, np.ndarray]]:
     """Yields (name, bf16 bits) for all 404 tensors, one at a time (about 3.8 GB in total)."""
     for name, shape in tensor_shapes(predictor_head_dim).items():

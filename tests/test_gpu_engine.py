@@ -1,0 +1,288 @@
+"""GPU tests of the drop-in boundary itself: the native talker ABI v3 driven the way the
+reference's host crate drives it (prefill, next_frame, begin/finish leases, lockstep batch),
+checked against the CPU oracle's restatement of the frame algorithm and against the
+self-consistency protocol of the reference's session benchmark (same seed => same codes
+whatever the batching; different seeds differ; a dropped session does not disturb siblings;
+lease misuse is a STATE error that leaves the GPU alone)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+PROMPT_TEXT = [1501, 77, 151935, -1, 9000, 42, 31337, 8]
+PROMPT_CODEC = [-1, 2148, 3, 2049, -1, 100, 7, 2000]
+
+
+def cfgs(q3t, sampled=True):
+    if sampled:
+        return (q3t.SamplingConfig(True, 50, 0.9, 0.9, 1.05), q3t.SamplingConfig(True, 50, 1.0, 0.9, 1.0))
+    return q3t.SamplingConfig.greedy(), q3t.SamplingConfig.greedy()
+
+
+def start(q3t, model, seed, sampled=True, max_seq=64, prompt=(PROMPT_TEXT, PROMPT_CODEC)):
+    t, p = cfgs(q3t, sampled)
+    return model.start_prompt(prompt[0], prompt[1], max_seq, seed, t, p)
+
+
+def as_kwargs(c):
+    return dict(do_sample=int(c.do_sample), top_k=c.top_k, top_p=c.top_p, temperature=c.temperature,
+                penalty=c.repetition_penalty)
+
+
+@pytest.fixture(scope="module")
+def model(gpu_model):
+    gpu_model.set_option("mask_eos", 1)      # random logits would end sessions at random
+    return gpu_model
+
+
+def test_model_memory_and_state(q3t, model):
+    assert model.memory.tensor_count == 404
+    assert model.memory.shared_weight_bytes == 3_833_352_704     # the reference's README figure
+    s = model.create_session(64, 1)
+    st = s.runtime_state()
+    assert (st.abi_version, st.phase, st.talker_position) == (3, 1, 0)     # READY
+    assert s.memory.max_sequence_length == 64
+    assert s.memory.talker_kv_bytes == 4 * 28 * 2 * 16 * 1024 * 2          # 4 pages
+    assert s.memory.predictor_kv_bytes == 5 * 2 * 16 * 1024 * 2
+    s.close()
+
+
+@pytest.mark.parametrize("sampled", [False, True])
+def test_frames_match_the_oracle(q3t, orc, model, checkpoint, sampled):
+    """Prefill + two frames: first semantic token, all 16 codes of each frame and the next
+    semantic tokens equal the CPU restatement; the final-normed hidden state agrees."""
+    om = test_frames_match_the_oracle.__dict__.setdefault("om", None)
+    if om is None:
+        om = orc.OracleModel(checkpoint)
+        test_frames_match_the_oracle.om = om
+    tcfg, pcfg = cfgs(q3t, sampled)
+    seed = 4242
+    s = start(q3t, model, seed, sampled)
+    o = orc.OracleSession(om, 64, seed)
+    o.mask_eos = True
+    first = o.prefill(PROMPT_TEXT, PROMPT_CODEC, as_kwargs(tcfg))
+    hidden, _, rng = s.read_state()
+    d = orc.bf16_ulp_distance(hidden, o.last_hidden)
+    assert (d <= 1).mean() > 0.9, float((d <= 1).mean())
+    cos = np.dot(orc.from_bf16(hidden), orc.from_bf16(o.last_hidden)) / (
+        np.linalg.norm(orc.from_bf16(hidden)) * np.linalg.norm(orc.from_bf16(o.last_hidden)))
+    assert cos > 0.9995, cos
+    assert s.current_semantic_token == first
+    assert rng == o.rng
+    for frame in range(2):
+        want_codes, want_next = o.frame(555 + frame, as_kwargs(tcfg), as_kwargs(pcfg))
+        got = s.next_frame(555 + frame)
+        assert list(got.codes) == want_codes, (frame, got.codes, want_codes)
+        assert got.next_semantic_token == want_next
+        assert got.talker_position == len(PROMPT_TEXT) + frame
+    assert s.read_state()[2] == o.rng
+    st = s.runtime_state()
+    assert (st.frames_generated, st.device_sample_count, st.host_sync_count) == (2, 1 + 2 * 16, 1 + 2)
+    assert st.semantic_history_count == 3 and st.talker_position == len(PROMPT_TEXT) + 2
+    s.close()
+
+
+def run_solo(q3t, model, seed, frames, sampled=True):
+    s = start(q3t, model, seed, sampled)
+    out = []
+    for f in range(frames):
+        fr = s.next_frame(100 + f)
+        out.append((fr.codes, fr.next_semantic_token))
+    s.close()
+    return out
+
+
+@pytest.mark.parametrize("n", [2, 3, 8, 9, 20])
+def test_lockstep_batch_equals_solo(q3t, model, n):
+    """session_bench.rs protocol: identical code sequences with and without batching."""
+    frames = 3
+    seeds = [1000 + i for i in range(n)]
+    solo = {seed: run_solo(q3t, model, seed, frames) for seed in seeds[:3]}
+    sessions = [start(q3t, model, seed) for seed in seeds]
+    got = {seed: [] for seed in seeds}
+    for f in range(frames):
+        pending = model.batch_begin_device_frames(sessions, [100 + f] * n)
+        assert len({p.lease_id for p in pending}) <= n
+        for s, p in zip(sessions, pending):
+            assert p.device_codes and p.ready_event and p.view.code_count == 16
+            fr = p.finish_without_consumer()
+            _, tokens, _ = s.read_state()
+            got[seeds[sessions.index(s)]].append((tuple(int(t) for t in tokens), fr.next_semantic_token))
+    for seed in seeds[:3]:
+        assert got[seed] == solo[seed], seed
+    # duplicate seed => identical, different seeds => different (session_bench.rs:228-232)
+    assert got[seeds[0]] != got[seeds[1]]
+    for s in sessions:
+        s.close()
+
+
+def test_duplicate_seed_and_dropped_sibling(q3t, model):
+    a, b, c = start(q3t, model, 7), start(q3t, model, 7), start(q3t, model, 8)
+    seq = {0: [], 1: []}
+    for f in range(2):
+        pend = model.batch_begin_device_frames([a, b, c], [5, 5, 5])
+        for i, p in enumerate(pend):
+            fr = p.finish_without_consumer()
+            if i < 2:
+                seq[i].append(fr.next_semantic_token)
+    assert seq[0] == seq[1]
+    c.close()                                   # drop one participant mid-stream
+    want = run_solo(q3t, model, 7, 4)
+    for f in range(2, 4):
+        pend = model.batch_begin_device_frames([a, b], [100 + f, 100 + f])
+        for p in pend:
+            p.finish_without_consumer()
+    # a and b continued with trailing ids 5,5 then 102,103; re-run solo with the same ids
+    s = start(q3t, model, 7)
+    nxt = [s.next_frame(5).next_semantic_token, s.next_frame(5).next_semantic_token,
+           s.next_frame(102).next_semantic_token, s.next_frame(103).next_semantic_token]
+    assert a.current_semantic_token == b.current_semantic_token == nxt[-1]
+    assert want  # solo run with other trailing ids simply has to complete
+    for x in (a, b, s):
+        x.close()
+
+
+def test_run_frames_equals_stepping(q3t, model):
+    a, b = start(q3t, model, 31), start(q3t, model, 31)
+    for f in range(3):
+        a.next_frame(9)
+    total_ms, per_frame = model.run_frames([b], 3, trailing_text_id=9, want_frame_ms=True)
+    assert total_ms > 0 and per_frame.shape == (3,) and (per_frame > 0).all()
+    ha, ta, ra = a.read_state()
+    hb, tb, rb = b.read_state()
+    assert np.array_equal(ta, tb) and ra == rb and np.array_equal(ha, hb)
+    assert a.runtime_state().talker_position == b.runtime_state().talker_position
+    # and both continue identically through the normal API
+    assert a.next_frame(1).codes == b.next_frame(1).codes
+    a.close()
+    b.close()
+
+
+def test_device_frame_lease_protocol(q3t, model):
+    s = start(q3t, model, 55)
+    err = C.create_string_buffer(256)
+    lib = q3t.library()
+    p = s.begin_device_frame(3)
+    assert p.lease_id >= 1 and p.view.device_index == 0
+    # a second begin, a prefill or a reset while the lease is out: STATE, nothing enqueued
+    with pytest.raises(q3t.NativeTalkerStatusError) as e:
+        s.begin_device_frame(3)
+    assert e.value.status == q3t.native.STATUS_STATE
+    with pytest.raises(q3t.NativeTalkerStatusError):
+        s.reset(1)
+    # stale lease id
+    nxt = C.c_uint16()
+    info = q3t.native.FrameInfoC()
+    rc = lib.qwen3_tts_session_next_frame_finish_v2(s._handle, p.lease_id + 17, None, C.byref(nxt),
+                                                   C.byref(info), err, 256)
+    assert rc == q3t.native.STATUS_STATE and b"lease" in err.value
+    fr = p.finish_without_consumer()
+    assert fr.predictor_gpu_milliseconds > 0 and fr.talker_gpu_milliseconds > 0
+    # finish without begin
+    rc = lib.qwen3_tts_session_next_frame_finish_v2(s._handle, p.lease_id, None, C.byref(nxt),
+                                                   C.byref(info), err, 256)
+    assert rc == q3t.native.STATUS_STATE
+    # view with a wrong struct_size / reserved field: INVALID_ARGUMENT
+    view = q3t.native.DeviceFrameViewV2C()
+    view.struct_size = 8
+    rc = lib.qwen3_tts_session_next_frame_begin_v2(s._handle, 0, s.talker_sampling.to_c(),
+                                                  s.predictor_sampling.to_c(), C.byref(view), err, 256)
+    assert rc == q3t.native.STATUS_INVALID_ARGUMENT
+    s.close()
+
+
+def test_argument_and_state_errors(q3t, model):
+    lib = q3t.library()
+    err = C.create_string_buffer(256)
+    s = model.create_session(16, 3)
+    # frame before prefill
+    with pytest.raises(q3t.NativeTalkerStatusError) as e:
+        s.next_frame(0)
+    assert e.value.status == q3t.native.STATUS_STATE and "prefill" in e.value.message
+    # prompt longer than the KV capacity, empty prompt, position without input
+    for text, codec in (([1] * 17, [1] * 17), ([], []), ([-1], [-1])):
+        with pytest.raises(q3t.NativeTalkerStatusError):
+            s.prefill(text, codec)
+    s.prefill([5, 6], [-1, 7])
+    # invalid sampling configurations (talker.cu:3588-3591)
+    for bad in (q3t.SamplingConfig(True, -1, 1.0, 1.0, 1.0), q3t.SamplingConfig(True, 5, 0.0, 1.0, 1.0),
+                q3t.SamplingConfig(True, 5, 1.5, 1.0, 1.0), q3t.SamplingConfig(True, 5, 1.0, 0.0, 1.0),
+                q3t.SamplingConfig(True, 5, 1.0, 1.0, 0.0)):
+        s.talker_sampling = bad
+        with pytest.raises(q3t.NativeTalkerStatusError):
+            s.next_frame(0)
+    s.talker_sampling = q3t.SamplingConfig.official_talker_defaults()
+    # wrong semantic token, text id out of range, undersized code buffer
+    codes = (C.c_uint16 * 16)()
+    nxt = C.c_uint16()
+    info = q3t.native.FrameInfoC()
+    wrong = (s.current_semantic_token + 1) % 2048
+    rc = lib.qwen3_tts_session_next_frame(s._handle, wrong, 0, s.talker_sampling.to_c(),
+                                          s.predictor_sampling.to_c(), codes, 16, C.byref(nxt),
+                                          C.byref(info), err, 256)
+    assert rc == q3t.native.STATUS_STATE and b"does not match" in err.value
+    with pytest.raises(q3t.NativeTalkerStatusError):
+        s.next_frame(151936)
+    rc = lib.qwen3_tts_session_next_frame(s._handle, s.current_semantic_token, 0,
+                                          s.talker_sampling.to_c(), s.predictor_sampling.to_c(), codes,
+                                          15, C.byref(nxt), C.byref(info), err, 256)
+    assert rc == q3t.native.STATUS_INVALID_ARGUMENT
+    # the session is still usable and fills its KV capacity exactly
+    frames = 0
+    while True:
+        try:
+            s.next_frame(1)
+            frames += 1
+        except q3t.NativeTalkerStatusError as full:
+            assert "full" in full.message
+            break
+    assert frames == 16 - 2
+    # out-of-range session capacity, batch of zero and of 65
+    with pytest.raises(q3t.NativeTalkerStatusError):
+        model.create_session(15, 0)
+    with pytest.raises(q3t.NativeTalkerStatusError):
+        model.create_session(8193, 0)
+    views = (q3t.native.DeviceFrameViewV2C * 1)()
+    rc = lib.qwen3_tts_model_batch_next_frame_begin_v2(model._handle, None, 0, None, None, None, views,
+                                                      err, 256)
+    assert rc == q3t.native.STATUS_INVALID_ARGUMENT
+    s.close()
+
+
+def test_upload_validation(q3t, synth):
+    m = q3t.NativeTalkerModel.create(0)
+    good = synth.make_tensor("talker.model.norm.weight", (2048,), 0)
+    with pytest.raises(q3t.NativeTalkerStatusError) as e:
+        m.upload_tensor("talker.model.norm.weight", good[:100].copy())
+    assert e.value.status == q3t.native.STATUS_MODEL and "shape" in e.value.message
+    with pytest.raises(q3t.NativeTalkerStatusError):
+        m.upload_tensor("not.a.tensor", good)
+    m.upload_tensor("talker.model.norm.weight", good)
+    with pytest.raises(q3t.NativeTalkerStatusError) as e:
+        m.upload_tensor("talker.model.norm.weight", good)
+    assert "duplicate" in e.value.message
+    with pytest.raises(q3t.NativeTalkerStatusError) as e:
+        m.finalize()
+    assert "missing" in e.value.message or "404" in e.value.message
+    with pytest.raises(q3t.NativeTalkerStatusError):
+        m.create_session(64, 0)                 # not finalized
+    m.close()
+
+
+def test_seed_zero_and_reset(q3t, model):
+    a = start(q3t, model, 0)
+    b = start(q3t, model, 0x9E3779B97F4A7C15)   # what seed 0 is replaced by (talker.cu:1022)
+    assert a.next_frame(2).codes == b.next_frame(2).codes
+    first = a.current_semantic_token
+    a.reset(0)
+    assert a.runtime_state().phase == 1 and a.runtime_state().talker_position == 0
+    a.prefill(PROMPT_TEXT, PROMPT_CODEC)
+    b.reset(0)
+    b.prefill(PROMPT_TEXT, PROMPT_CODEC)
+    assert a.current_semantic_token == b.current_semantic_token
+    assert a.next_frame(2).codes == b.next_frame(2).codes
+    assert first >= 0
+    a.close()
+    b.close()
