@@ -222,6 +222,11 @@ QWEN3_TTS_API int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle sessio
                                                     uint64_t seed, char* error,
                                                     size_t error_capacity);
 
+/* The semantic token the next frame of the session will expand (what the reference's host
+ * tracks from the prefill result and each finished frame; needed after q3t_model_run_frames). */
+QWEN3_TTS_API int32_t q3t_session_current_token(Qwen3TtsSessionHandle session, uint16_t* token,
+                                                char* error, size_t error_capacity);
+
 /* Number of this library's kernels launched so far through frame graphs of the model. */
 QWEN3_TTS_API int32_t q3t_model_kernel_launches(Qwen3TtsModelHandle model, uint64_t* launches,
                                                 char* error, size_t error_capacity);

@@ -375,23 +375,31 @@ class OracleModel:
         self.pred_emb = [t[f"talker.code_predictor.model.codec_embedding.{g}.weight"] for g in range(15)]
 
 
-def decoder_layer(h, lw, dims, kcache, vcache, pos):
+import sys as _sys
+
+_THIS = _sys.modules[__name__]
+
+
+def decoder_layer(h, lw, dims, kcache, vcache, pos, b=None):
     """One layer of the fused int8 batch path (talker.cu:2054-2333) for a single row.
-    kcache/vcache: [capacity][kv_width] and are appended in place."""
+    kcache/vcache: [capacity][kv_width] and are appended in place.  `b` is the module or object
+    that supplies the primitives (this module by default; the GPU tests pass an adapter over
+    the operator-level C ABI to run the same composition on the kernels under test)."""
+    b = b or _THIS
     qh, kvh, hd = dims["q_heads"], dims["kv_heads"], dims["head_dim"]
     qw, kvw = qh * hd, kvh * hd
-    n = rms_norm_rows(h[None, :], lw["input_norm"])
-    qkv = int8_gemm_rows(lw["qkv"][0], lw["qkv"][1], n)[0]
+    n = b.rms_norm_rows(h[None, :], lw["input_norm"])
+    qkv = b.int8_gemm_rows(lw["qkv"][0], lw["qkv"][1], n)[0]
     q, k, v = qkv[:qw], qkv[qw:qw + kvw], qkv[qw + kvw:]
-    q = rope_rows_at(head_rms_norm(q, lw["q_norm"], hd), 1, qh, hd, [pos])
-    k = rope_rows_at(head_rms_norm(k, lw["k_norm"], hd), 1, kvh, hd, [pos])
-    kcache[pos] = k
+    q = b.rope_rows_at(b.head_rms_norm(q, lw["q_norm"], hd), 1, qh, hd, [pos])
+    k = b.rope_rows_at(b.head_rms_norm(k, lw["k_norm"], hd), 1, kvh, hd, [pos])
+    kcache[pos] = k.reshape(-1)
     vcache[pos] = v
-    a = attention(q, kcache[None], vcache[None], [pos], qh, kvh, hd, fast=True)
-    h = int8_gemm_rows(lw["o"][0], lw["o"][1], a, y_in=h[None, :], mode=1)
-    n = rms_norm_rows(h, lw["post_norm"])
-    g = int8_gate_up_silu_rows(lw["gate_up"][0], lw["gate_up"][1], n)
-    h = int8_gemm_rows(lw["down"][0], lw["down"][1], g, y_in=h, mode=1)
+    a = b.attention(q, kcache[None, :pos + 1], vcache[None, :pos + 1], [pos], qh, kvh, hd, fast=True)
+    h = b.int8_gemm_rows(lw["o"][0], lw["o"][1], a, y_in=h[None, :], mode=1)
+    n = b.rms_norm_rows(h, lw["post_norm"])
+    g = b.int8_gate_up_silu_rows(lw["gate_up"][0], lw["gate_up"][1], n)
+    h = b.int8_gemm_rows(lw["down"][0], lw["down"][1], g, y_in=h, mode=1)
     return h[0]
 
 
@@ -399,8 +407,9 @@ class OracleSession:
     """Single-session restatement of prefill + frame generation with the fused int8 semantics
     (frame algorithm: talker.cu:1495-1881; prompt embedding: talker.cu:2676-2748)."""
 
-    def __init__(self, model: OracleModel, max_seq: int, seed: int):
+    def __init__(self, model: OracleModel, max_seq: int, seed: int, backend=None):
         self.m = model
+        self.b = backend or _THIS   # supplier of the primitives (see decoder_layer)
         self.max_seq = max_seq
         kvw = 1024
         self.k = np.zeros((28, max_seq, kvw), dtype=np.uint16)
@@ -420,26 +429,26 @@ class OracleSession:
         x = t["talker.model.text_embedding.weight"][token]
         w1, s1 = self.m.q["talker.text_projection.linear_fc1.weight"]
         w2, s2 = self.m.q["talker.text_projection.linear_fc2.weight"]
-        p = bias_activation_rows(int8_gemm_rows(w1, s1, x), t["talker.text_projection.linear_fc1.bias"], True)
-        return bias_activation_rows(int8_gemm_rows(w2, s2, p), t["talker.text_projection.linear_fc2.bias"], False)[0]
+        p = self.b.bias_activation_rows(self.b.int8_gemm_rows(w1, s1, x), t["talker.text_projection.linear_fc1.bias"], True)
+        return self.b.bias_activation_rows(self.b.int8_gemm_rows(w2, s2, p), t["talker.text_projection.linear_fc2.bias"], False)[0]
 
     def _talker_layers(self, h, pos):
         for l, lw in enumerate(self.m.talker_layers):
-            h = decoder_layer(h, lw, TALKER_DIMS, self.k[l], self.v[l], pos)
+            h = decoder_layer(h, lw, TALKER_DIMS, self.k[l], self.v[l], pos, self.b)
         return h
 
     def _talker_head(self, h, cfg):
         t = self.m.t
-        n = rms_norm_rows(h[None, :], t["talker.model.norm.weight"])[0]
+        n = self.b.rms_norm_rows(h[None, :], t["talker.model.norm.weight"])[0]
         self.last_hidden = n.copy()
         w, s = self.m.q["talker.codec_head.weight"]
-        logits = int8_gemm_rows(w, s, n)[0]
+        logits = self.b.int8_gemm_rows(w, s, n)[0]
         self.trace["talker_logits"] = logits
         if getattr(self, "mask_eos", False):
             # harness option for random weights: EOS is masked like a reserved token
             logits = logits.copy()
             logits[EOS] = 0xFF80   # -inf
-        tok, self.rng = sample(logits, self.rng, suppress=True, history=self.history, **cfg)
+        tok, self.rng = self.b.sample(logits, self.rng, suppress=True, history=self.history, **cfg)
         self.history.append(tok)
         return tok
 
@@ -451,7 +460,7 @@ class OracleSession:
         for i, (ti, ci) in enumerate(zip(text_ids, codec_ids)):
             h = self._project_text(ti) if ti >= 0 else np.zeros(2048, dtype=np.uint16)
             if ci >= 0:
-                h = add(h, t["talker.model.codec_embedding.weight"][ci])
+                h = self.b.add(h, t["talker.model.codec_embedding.weight"][ci])
             h = self._talker_layers(h, i)
         self.position = len(text_ids)
         self.current = self._talker_head(h, cfg)
@@ -460,13 +469,13 @@ class OracleSession:
     def _predictor_position(self, x, pos, head):
         t = self.m.t
         w, s = self.m.q["talker.code_predictor.small_to_mtp_projection.weight"]
-        h = bias_activation_rows(int8_gemm_rows(w, s, x), t["talker.code_predictor.small_to_mtp_projection.bias"], False)[0]
+        h = self.b.bias_activation_rows(self.b.int8_gemm_rows(w, s, x), t["talker.code_predictor.small_to_mtp_projection.bias"], False)[0]
         for l, lw in enumerate(self.m.predictor_layers):
-            h = decoder_layer(h, lw, self.m.pd, self.pk[l], self.pv[l], pos)
+            h = decoder_layer(h, lw, self.m.pd, self.pk[l], self.pv[l], pos, self.b)
         if head < 0:
             return None
-        n = rms_norm_rows(h[None, :], t["talker.code_predictor.model.norm.weight"])
-        return int8_gemm_rows(self.m.heads[head][0], self.m.heads[head][1], n)[0]
+        n = self.b.rms_norm_rows(h[None, :], t["talker.code_predictor.model.norm.weight"])
+        return self.b.int8_gemm_rows(self.m.heads[head][0], self.m.heads[head][1], n)[0]
 
     def frame(self, trailing_text, talker_cfg, predictor_cfg):
         """Returns (codes[16], next_semantic_token)."""
@@ -478,14 +487,14 @@ class OracleSession:
         for p in range(1, 16):
             logits = self._predictor_position(x, p, p - 1)
             self.trace["predictor_logits"].append(logits)
-            nt, self.rng = sample(logits, self.rng, suppress=False, **predictor_cfg)
+            nt, self.rng = self.b.sample(logits, self.rng, suppress=False, **predictor_cfg)
             tok.append(nt)
             if p < 15:
                 x = self.m.pred_emb[p - 1][nt]
         h = t["talker.model.codec_embedding.weight"][tok[0]].copy()
         for r in range(15):
-            h = add(h, self.m.pred_emb[r][tok[r + 1]])
-        h = add(h, self._project_text(trailing_text))
+            h = self.b.add(h, self.m.pred_emb[r][tok[r + 1]])
+        h = self.b.add(h, self._project_text(trailing_text))
         self.trace["talker_input"] = h
         h = self._talker_layers(h, self.position)
         self.trace["talker_hidden"] = h

@@ -876,6 +876,16 @@ int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle session, int32_t pos
                    QWEN3_TTS_TALKER_STATUS_STATE, error, error_capacity);
 }
 
+int32_t q3t_session_current_token(Qwen3TtsSessionHandle session, uint16_t* token, char* error,
+                                  size_t error_capacity) {
+    if (token == nullptr) {
+        write_error(error, error_capacity, "token output pointer is null");
+        return QWEN3_TTS_TALKER_STATUS_INVALID_ARGUMENT;
+    }
+    return protect([&] { *token = session_of(session)->current_token(); },
+                   QWEN3_TTS_TALKER_STATUS_STATE, error, error_capacity);
+}
+
 int32_t q3t_model_kernel_launches(Qwen3TtsModelHandle model, uint64_t* launches, char* error,
                                   size_t error_capacity) {
     if (launches == nullptr) {

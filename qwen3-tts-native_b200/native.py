@@ -108,7 +108,7 @@ EXPORTED_SYMBOLS = (
     "q3t_attention_scratch_bytes", "q3t_launch_batch_causal_gqa_attention_fast",
     "q3t_launch_decode_attention_ex", "q3t_launch_sample_logits", "q3t_launch_sample_logits_at",
     "q3t_model_set_option", "q3t_model_run_frames", "q3t_session_read_state",
-    "q3t_session_synthetic_prefill", "q3t_model_kernel_launches",
+    "q3t_session_synthetic_prefill", "q3t_model_kernel_launches", "q3t_session_current_token",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -383,6 +383,12 @@ class NativeTalkerModel:
             self._handle, handles, n, frames, trailing_text_id,
             sessions[0].talker_sampling.to_c(), sessions[0].predictor_sampling.to_c(),
             per_frame, C.byref(total), err, _ERR_CAP), err)
+        for s in sessions:
+            tok = C.c_uint16(0)
+            _check(library().q3t_session_current_token(s._handle, C.byref(tok), err, _ERR_CAP), err)
+            s.current_semantic_token = int(tok.value)
+            s.frames_emitted += frames
+            s.ended = s.current_semantic_token == EOS
         return float(total.value), (np.array(per_frame[:], dtype=np.float32) if want_frame_ms else None)
 
     def close(self) -> None:
