@@ -258,6 +258,27 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     K, W = args.steps, args.warmup
     total_frames = 2 * (K + W) + 8
 
+    if args.leg != "all":
+        # single legs, for profiling runs (ncu wants few launches and a small footprint)
+        out = {"leg": args.leg}
+        if args.leg == "gemv":
+            g = native.benchmark_int8_gemv(local_rank, args.gemv_in, args.gemv_out, rows=args.rows,
+                                           buffers=16, iterations=max(K, 1))
+            out.update(us_per_launch=g.mean_launch_microseconds, cold_us=g.cold_launch_microseconds)
+        else:
+            count = 1 if args.leg == "b1" else SESSIONS
+            lens = [512] if args.leg == "b1" else list(
+                np.random.default_rng(3).integers(64, 2049, size=SESSIONS))
+            ss = make_sessions(q3t, model, count, lens, K + W + 8, talker_cfg, predictor_cfg, 77)
+            model.run_frames(ss, W, trailing_text_id=11)
+            ms, _ = model.run_frames(ss, K, trailing_text_id=11)
+            out.update(ms_per_frame=ms / K, frames_per_s=count * K / (ms * 1e-3))
+            for s in ss:
+                s.close()
+        print(json.dumps(out), flush=True)
+        model.close()
+        return
+
     lengths = np.random.default_rng(3 + rank).integers(64, 2049, size=SESSIONS)
     sessions = make_sessions(q3t, model, SESSIONS, lengths, total_frames, talker_cfg, predictor_cfg,
                              1 + 1000 * rank)
@@ -365,6 +386,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--leg", choices=["all", "b64", "b1", "gemv"], default="all",
+                    help="profiling aid: run one leg only and print a short JSON line")
+    ap.add_argument("--gemv-in", type=int, default=2048)
+    ap.add_argument("--gemv-out", type=int, default=6144)
+    ap.add_argument("--rows", type=int, default=1)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
