@@ -140,6 +140,24 @@ QWEN3_TTS_API int32_t q3t_launch_batch_causal_gqa_attention_fast(
     int32_t key_value_heads, int32_t head_dimension, int32_t max_sequence_length, void* scratch,
     size_t scratch_bytes, void* stream);
 
+/* No counterpart in the reference.  The same operator for hosts that may not allocate device
+ * memory where they run it (a real-time audio thread, a process with a fixed, policed memory
+ * budget, a plugin that is lent streams and buffers only): the scratch lives in a 4 MiB array
+ * built into the library's device image, so the caller passes inputs and outputs and nothing
+ * else, and the call itself allocates nothing.  Shapes that need more scratch than the array holds
+ * (see q3t_attention_scratch_bytes) are rejected with STATUS_INVALID_ARGUMENT and a message.
+ * The first call on a device resolves the array's device address; make it before any stream
+ * capture.  All calls on a device share the array: calls that overlap on the GPU race.
+ * Returns a QWEN3_TTS_TALKER_STATUS_* code; `error` follows the convention of qwen3_tts_native.h. */
+QWEN3_TTS_API int32_t q3t_launch_batch_causal_gqa_attention_fast_noalloc(
+    const uint16_t* query, uint16_t* const* key_bases, uint16_t* const* value_bases,
+    const int32_t* positions, uint16_t* output, int32_t rows, int32_t query_heads,
+    int32_t key_value_heads, int32_t head_dimension, int32_t max_sequence_length, void* stream,
+    char* error, size_t error_capacity);
+
+/* Bytes of the built-in scratch array used by the _noalloc entry point. */
+QWEN3_TTS_API size_t q3t_attention_static_scratch_capacity(void);
+
 /* Full form: paged KV and/or the fused per-head RMSNorm + RoPE + KV append, which the reference
  * issues as launch_head_rms_norm_rows x2, launch_rope_rows_at x2, launch_kv_scatter_rows x2
  * (talker.cu:2101-2175) before the attention launch. */

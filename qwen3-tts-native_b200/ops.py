@@ -240,6 +240,29 @@ def attention_contiguous(q, k, v, positions, q_heads, kv_heads, head_dim):
     return _u16(do)
 
 
+def attention_contiguous_noalloc(q, k, v, positions, q_heads, kv_heads, head_dim):
+    """The entry point for hosts that may not allocate: same arguments as
+    attention_contiguous minus the scratch buffer, which the library keeps in a built-in array.
+    Returns (status, message, output)."""
+    lib = native.library()
+    k = np.ascontiguousarray(k, dtype=np.uint16)
+    v = np.ascontiguousarray(v, dtype=np.uint16)
+    rows, capacity = k.shape[0], k.shape[1]
+    dq, dk, dv = _dev(np.asarray(q, dtype=np.uint16)), _dev(k), _dev(v)
+    stride = dk[0].numel() * 2
+    kb = torch.tensor([dk.data_ptr() + r * stride for r in range(rows)], dtype=torch.int64, device="cuda")
+    vb = torch.tensor([dv.data_ptr() + r * stride for r in range(rows)], dtype=torch.int64, device="cuda")
+    dp = _dev(np.asarray(positions, dtype=np.int32))
+    do = torch.zeros((rows, q_heads * head_dim), dtype=torch.int16, device="cuda")
+    err = C.create_string_buffer(256)
+    torch.cuda.synchronize()
+    status = lib.q3t_launch_batch_causal_gqa_attention_fast_noalloc(
+        _ptr(dq), _ptr(kb), _ptr(vb), _ptr(dp), _ptr(do), rows, q_heads, kv_heads, head_dim, capacity,
+        None, err, C.c_size_t(256))
+    torch.cuda.synchronize()
+    return int(status), err.value.decode(), _u16(do)
+
+
 def attention_ex(q, positions, q_heads, kv_heads, head_dim, *, k=None, v=None, pages=None,
                  page_table=None, slab_shift=0, k_new=None, v_new=None, q_norm_w=None,
                  k_norm_w=None, fused=False, q_stride=0, new_stride=0, max_seq=None,
