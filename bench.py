@@ -250,6 +250,16 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     synth = importlib.import_module("qwen3-tts-native_b200.synth")
     native = q3t.native
 
+    if args.leg == "gemv":
+        # operator microbenchmark: no model needed (keeps ncu captures small)
+        g = native.benchmark_int8_gemv(local_rank, args.gemv_in, args.gemv_out, rows=args.rows,
+                                       buffers=16, iterations=max(args.steps, 1))
+        print(json.dumps({"leg": "gemv", "in": args.gemv_in, "out": args.gemv_out, "rows": args.rows,
+                          "us_per_launch": g.mean_launch_microseconds,
+                          "cold_us": g.cold_launch_microseconds,
+                          "GBps": (args.gemv_in * args.gemv_out) / g.mean_launch_microseconds / 1e3}),
+              flush=True)
+        return
     model = q3t.NativeTalkerModel.load(local_rank, synth.checkpoint_cuda(local_rank, seed=0))
     model.set_option("mask_eos", 1)
     model.set_option("batch_host_codes", 1)
@@ -261,11 +271,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     if args.leg != "all":
         # single legs, for profiling runs (ncu wants few launches and a small footprint)
         out = {"leg": args.leg}
-        if args.leg == "gemv":
-            g = native.benchmark_int8_gemv(local_rank, args.gemv_in, args.gemv_out, rows=args.rows,
-                                           buffers=16, iterations=max(K, 1))
-            out.update(us_per_launch=g.mean_launch_microseconds, cold_us=g.cold_launch_microseconds)
-        else:
+        if True:
             count = 1 if args.leg == "b1" else SESSIONS
             lens = [512] if args.leg == "b1" else list(
                 np.random.default_rng(3).integers(64, 2049, size=SESSIONS))

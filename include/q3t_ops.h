@@ -215,7 +215,10 @@ QWEN3_TTS_API int32_t q3t_launch_sample_logits_at(
 
 /* Options: "mask_eos" (1: the talker sampler also masks EOS, for synthetic weights whose
  * logits would otherwise end a run at random), "use_graphs" (0: launch kernels one by one),
- * "batch_host_codes" (1: lockstep batches also mirror each frame's 16 codes to host memory). */
+ * "batch_host_codes" (1: lockstep batches also mirror each frame's 16 codes to host memory),
+ * "tc_min_rows" (process-wide: projections with at least this many rows run on the tensor
+ * cores, default 9; 65 keeps every row count on the SIMT kernels, whose results do not depend on
+ * the batch size). */
 QWEN3_TTS_API int32_t q3t_model_set_option(Qwen3TtsModelHandle model, const char* key,
                                            int32_t value, char* error, size_t error_capacity);
 
@@ -244,6 +247,11 @@ QWEN3_TTS_API int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle sessio
  * tracks from the prefill result and each finished frame; needed after q3t_model_run_frames). */
 QWEN3_TTS_API int32_t q3t_session_current_token(Qwen3TtsSessionHandle session, uint16_t* token,
                                                 char* error, size_t error_capacity);
+
+/* Health counter: how many bounded device-side waits (mbarrier waits of the bulk-copy GEMV and
+ * of the tensor-core GEMM)
+ * have run out since the library was loaded.  0 on a healthy run; kernels never spin forever. */
+QWEN3_TTS_API uint32_t q3t_kernel_error_count(void);
 
 /* Number of this library's kernels launched so far through frame graphs of the model. */
 QWEN3_TTS_API int32_t q3t_model_kernel_launches(Qwen3TtsModelHandle model, uint64_t* launches,

@@ -35,6 +35,8 @@ cudaError_t configure_device() {
     std::lock_guard<std::mutex> lock(guard);
     if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
     e = configure_gemv_kernels();
+    if (e == cudaSuccess) e = configure_gemv_b1_kernels();
+    if (e == cudaSuccess) e = configure_tc_kernels();
     if (e == cudaSuccess) e = configure_sampler_kernels();
     if (e == cudaSuccess && device >= 0 && device < 64) done[device] = true;
     return e;
@@ -861,6 +863,8 @@ int32_t q3t_model_set_option(Qwen3TtsModelHandle model, const char* key, int32_t
             m->use_graphs = value != 0;
         } else if (std::strcmp(key, "batch_host_codes") == 0) {
             m->batch_host_codes = value != 0;
+        } else if (std::strcmp(key, "tc_min_rows") == 0) {
+            set_tc_min_rows(value);     // process-wide: rows at or above this use the tensor cores
         } else {
             throw std::runtime_error(std::string("unknown model option: ") + key);
         }
@@ -897,6 +901,8 @@ int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle session, int32_t pos
     return protect([&] { session_of(session)->synthetic_prefill(position, seed); },
                    QWEN3_TTS_TALKER_STATUS_STATE, error, error_capacity);
 }
+
+uint32_t q3t_kernel_error_count(void) { return gemv_b1_error_count() + gemm_tc_error_count(); }
 
 int32_t q3t_session_current_token(Qwen3TtsSessionHandle session, uint16_t* token, char* error,
                                   size_t error_capacity) {

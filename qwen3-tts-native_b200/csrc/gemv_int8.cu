@@ -19,6 +19,9 @@
 
 #include "q3t_kernels.cuh"
 
+#include <cstdlib>
+#include <cstring>
+
 namespace q3t {
 namespace {
 
@@ -272,6 +275,14 @@ cudaError_t configure_gemv_kernels() {
 }
 
 cudaError_t launch_int8_gemm(const GemvArgs& a, cudaStream_t stream) {
+    // The bulk-copy batch-1 kernel is opt-in (QWEN3_TTS_B1_GEMV=bulk): alone it matches the SIMT
+    // kernel, inside a captured frame it measured slower, so the SIMT kernel stays the default.
+    static const bool b1_enabled = [] {
+        const char* v = std::getenv("QWEN3_TTS_B1_GEMV");
+        return v != nullptr && std::strcmp(v, "bulk") == 0;
+    }();
+    if (gemm_tc_supports(a)) return launch_int8_gemm_tc(a, stream);
+    if (b1_enabled && gemv_b1_supports(a)) return launch_int8_gemv_b1(a, stream);
     return launch_int8_gemm_simt(a, stream);
 }
 

@@ -43,6 +43,19 @@ struct GemvArgs {
 // Dispatcher: 1..8 rows run the SIMT kernel; more rows run it in passes of 8 rows.
 cudaError_t launch_int8_gemm(const GemvArgs& args, cudaStream_t stream);
 cudaError_t launch_int8_gemm_simt(const GemvArgs& args, cudaStream_t stream);
+// batch-1 kernel (bulk-copy rings, packed fp32x2 math): rows == 1 and K in {1024,2048,3072,6144}
+bool gemv_b1_supports(const GemvArgs& args);
+cudaError_t launch_int8_gemv_b1(const GemvArgs& args, cudaStream_t stream);
+cudaError_t configure_gemv_b1_kernels();
+// tensor-core path (tcgen05, TMEM accumulators): rows >= tc_min_rows() and K % 64 == 0
+bool gemm_tc_supports(const GemvArgs& args);
+cudaError_t launch_int8_gemm_tc(const GemvArgs& args, cudaStream_t stream);
+cudaError_t configure_tc_kernels();      // also allocates the per-device scratch of that path
+void set_tc_min_rows(int rows);          // 65 or more: never use the tensor-core path
+int tc_min_rows();
+unsigned int gemm_tc_error_count();
+// number of bounded waits that ran out in gemv_b1 kernels since the library was loaded (0 = healthy)
+unsigned int gemv_b1_error_count();
 
 cudaError_t launch_quantize_weight_rows(const bf16* weight, int8_t* quantized, float* scales,
                                         int in_features, int out_features, cudaStream_t stream);

@@ -110,6 +110,7 @@ EXPORTED_SYMBOLS = (
     "q3t_model_set_option", "q3t_model_run_frames", "q3t_session_read_state",
     "q3t_session_synthetic_prefill", "q3t_model_kernel_launches", "q3t_session_current_token",
     "q3t_launch_batch_causal_gqa_attention_fast_noalloc", "q3t_attention_static_scratch_capacity",
+    "q3t_kernel_error_count",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -128,6 +129,7 @@ def library() -> C.CDLL:
         lib.qwen3_tts_talker_abi_version.restype = C.c_uint32
         lib.q3t_attention_scratch_bytes.restype = C.c_size_t
         lib.q3t_attention_static_scratch_capacity.restype = C.c_size_t
+        lib.q3t_kernel_error_count.restype = C.c_uint32
         lib.qwen3_tts_model_destroy.restype = None
         lib.qwen3_tts_session_destroy.restype = None
         lib.qwen3_tts_model_destroy.argtypes = [C.c_void_p]

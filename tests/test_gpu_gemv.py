@@ -19,6 +19,8 @@ SHAPES = [  # (out_features, in_features)
     (1024, 2048),   # k, v, small_to_mtp
     (3072, 2048),   # codec head
     (2048, 1024),   # predictor lm_head / q
+    (1024, 3072),   # predictor down
+    (131, 1024), (77, 3072), (5, 6144),   # odd channel counts on the batch-1 kernel
 ]
 
 
@@ -63,7 +65,7 @@ def test_residual_epilogue_bit_exact(orc, ops, n, k, rows):
     assert np.array_equal(got, want), ulp_report(orc, got, want)
 
 
-@pytest.mark.parametrize("n,k,rows", [(24, 96, 2), (6144, 2048, 1), (3072, 1024, 8), (40, 64, 11)])
+@pytest.mark.parametrize("n,k,rows", [(24, 96, 2), (6144, 2048, 1), (3072, 1024, 8), (40, 80, 11)])
 def test_gate_up_silu(orc, ops, n, k, rows):
     rng = np.random.default_rng(4)
     w = rng.integers(-127, 128, size=(2 * n, k), dtype=np.int8)
@@ -102,7 +104,7 @@ def test_norm_prologue(orc, ops, k, n, rows):
     assert worst <= 2 and frac < 0.05, (worst, frac)
 
 
-@pytest.mark.parametrize("rows", [1, 4, 12])
+@pytest.mark.parametrize("rows", [1, 4, 8])
 def test_bias_epilogues(orc, ops, rows):
     k, n = 2048, 1024
     rng = np.random.default_rng(7)
@@ -159,3 +161,8 @@ def test_quantizer_vs_reference_kernel(orc, ops, ref):
     q, s = ops.quantize_rows(wt)
     rq, rs = ref.ref_quantize_rows(wt)
     assert np.array_equal(q, rq) and np.array_equal(s, rs)
+
+
+def test_no_device_wait_ran_out(q3t, ops):
+    """The bulk-copy GEMV bounds every mbarrier wait; a healthy run never exhausts one."""
+    assert q3t.library().q3t_kernel_error_count() == 0
