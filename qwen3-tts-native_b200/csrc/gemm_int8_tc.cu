@@ -5,16 +5,19 @@
 // the sessions are the UMMA "N" dimension (16, 32 or 64 columns of fp32 accumulators in TMEM).
 //
 //   TMA (cp.async.bulk.tensor.2d)   int8 W tile 128 x 64  -> shared ring (8 stages)
-//   TMA, 128-byte swizzle           bf16 x tile  MT x 64  -> shared, already in UMMA K-major layout
-//   4 warps                         int8 -> bf16 in registers (exact; XOR + PRMT into the mantissa
+//   TMA, 128-byte swizzle           bf16 x tile  MT x 64  -> shared ring (6 stages), UMMA K-major layout
+//   2 x 4 warps, chunks in turn     int8 -> bf16 in registers (exact: XOR, PRMT into the mantissa
 //                                   of 2^23, packed subtract, PRMT of the high halves) -> shared,
 //                                   128-byte-swizzled K-major A tile
-//   1 thread                        tcgen05.mma.cta_group::1.kind::f16, 128 x MT x 16 per
-//                                   instruction, accumulators in TMEM; tcgen05.commit frees stages
+//   1 thread                        tcgen05.mma.cta_group::1.kind::f16 (bf16 x bf16 -> fp32),
+//                                   128 x MT x 16 per instruction, accumulators in TMEM;
+//                                   tcgen05.commit frees stages
 //   4 warps                         tcgen05.ld the accumulators, per-channel scale and the same
 //                                   epilogues as the SIMT path
-// K is split across CTAs so that every SM streams weights; the K-slices of a channel tile are
-// summed in slice order by the CTA that takes the tile's last ticket (deterministic).
+// K is split across the CTAs of a thread-block cluster (up to 8) so that every SM streams
+// weights; each CTA pushes the rows of its slice into the shared memory of the CTA that owns
+// them (distributed shared memory) and, after one cluster barrier, sums the rows it owns over
+// all slices in slice order (deterministic).
 //
 // The reference has no counterpart: its int8 path stops at 8 rows of SIMT FMAs
 // (int8_gemv.cu:329) and its larger row counts go through cuBLAS bf16 GEMMs.
@@ -31,16 +34,42 @@
 namespace q3t {
 namespace {
 
-constexpr int kTcThreads = 256;
+// Warp roles.  A warp's scheduler is warp % 4.  The three single-thread roles (weight copies, MMA
+// issue, activation copies) sit on scheduler 0, which runs no dequantiser: a scheduler keeps
+// issuing from a warp that is ready, and the dequantisers' long runs of independent math would
+// otherwise delay every instruction of a role that shares their scheduler.
+constexpr int kGroups = 2;             // dequantiser groups of 4 warps, taking chunks in turn
+constexpr int kTcWarps = 12;
+constexpr int kTcThreads = kTcWarps * 32;
+constexpr int kWarpW = 0, kWarpMma = 4, kWarpX = 8, kWarpTmem = 11;
+// dequantisers: warps 1,2,3,5 (group 0) and 6,7,9,10 (group 1)
+__device__ __forceinline__ int dequant_index(int warp) {
+    return (warp % 4 == 0 || warp == kWarpTmem) ? -1 : (warp / 4) * 3 + (warp % 4) - 1;
+}
 constexpr int kTileN = 128;            // output channels per CTA = TMEM lanes
 constexpr int kBK = 64;                // K elements per pipeline chunk
 constexpr int kWStages = 8;            // int8 ring
-constexpr int kAStages = 3;            // bf16 A / x ring
+constexpr int kAStages = 4;            // dequantised A ring
+constexpr int kXStages = 6;            // activation ring (its loads come from L2 and are latency-bound)
+constexpr int kRedBytes = 36 * 1024;   // K-slice exchange: up to 8 slices x ceil(64 / slices) rows x 128 fp32
 constexpr int kWStageBytes = kTileN * kBK;          // 8 KB
 constexpr int kAStageBytes = kTileN * kBK * 2;      // 16 KB
 constexpr unsigned long long kBudgetNs = 2000000000ull;   // 2 s for the whole kernel
 
 __device__ unsigned int g_tc_errors = 0;
+
+// Optional phase timestamps of CTA 0 (SM clock), compiled in only for pipeline studies.
+#ifdef Q3T_TC_TRACE
+__device__ long long g_tc_trace[160];
+__device__ unsigned long long g_tc_span[2 + 2 * 160];   // min start, max end, per-CTA start/end (global timer)
+#define TC_TRACE(slot) do { if (blockIdx.x == 0 && (slot) < 160) g_tc_trace[(slot)] = clock64(); } while (0)
+#define TC_SPAN(which) do { unsigned long long now_ = 0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now_)); \
+        if (blockIdx.x < 160) g_tc_span[2 + 2 * blockIdx.x + (which)] = now_; \
+        if (which) atomicMax(&g_tc_span[1], now_); else atomicMin(&g_tc_span[0], now_); } while (0)
+#else
+#define TC_TRACE(slot) do { } while (0)
+#define TC_SPAN(which) do { } while (0)
+#endif
 
 struct TcParams {
     const float* scales;
@@ -48,13 +77,11 @@ struct TcParams {
     float* y32;
     const bf16* bias;
     bf16* resid;
-    float* partials;          // [tile][split][MT][128] fp32, only when splits > 1
-    unsigned int* tickets;    // [tiles]
     int out_features;         // N (GATEUP: channels, the matrix has 2N rows)
     int rows;                 // valid sessions
     int epilogue;
-    int splits;
-    int chunks_per_split;     // K chunks of 64 per split
+    int splits;               // K-slices per channel tile = CTAs per cluster
+    int chunks;               // K chunks of 64 in the whole contraction
     int tiles;
 };
 
@@ -88,14 +115,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// One lane of a converged warp.  Unlike a test of the lane index, this tells the compiler that
+// the code below runs in exactly one thread, which the instructions that take their operands
+// from uniform registers (TMA copies, MMA issue) need in order to be emitted without a loop
+// over the active lanes.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t chosen;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(chosen));
+    return chosen != 0;
+}
+
 // Shared by all roles of a CTA: deadline and an abort flag that turns every later wait into a no-op.
 struct Guard {
     unsigned long long deadline;
     volatile int* abort_flag;
     __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity) const {
+        // the clock is read once per 1024 polls: a read of the global timer costs about as much
+        // as a whole pipeline stage
+        uint32_t polls = 0;
         while (!mbar_try_wait(bar, parity)) {
+            if ((++polls & 63u) != 0) continue;
             if (*abort_flag) return false;
-            if (now_ns() > deadline) {
+            if ((polls & 1023u) == 0 && now_ns() > deadline) {
                 *abort_flag = 1;
                 return false;
             }
@@ -109,6 +154,25 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
+}
+
+// Hardware barrier over every thread of the cluster (one CTA per K-slice of a channel tile).
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// address of the same shared-memory location in the CTA of another rank of the cluster
+__device__ __forceinline__ uint32_t peer_smem(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 // K-major, 128-byte-swizzled operand tile: rows at a 128-byte pitch, 8-row groups 1024 bytes apart
@@ -155,8 +219,7 @@ __device__ __forceinline__ void dequant4(uint32_t word, uint32_t& lo, uint32_t& 
     hi = __byte_perm(static_cast<uint32_t>(b), static_cast<uint32_t>(b >> 32), 0x7632);
 }
 
-__device__ __forceinline__ float finish(const TcParams& p, float acc, int channel, size_t o) {
-    const float scale = p.scales[channel];
+__device__ __forceinline__ float finish(const TcParams& p, float acc, float scale, int channel, size_t o) {
     switch (p.epilogue) {
         case EPI_ADD: return fmaf(acc, scale, bf2f(p.y[o]));
         case EPI_BIAS: return rbf(acc * scale) + bf2f(p.bias[channel]);
@@ -170,24 +233,22 @@ __device__ __forceinline__ float finish(const TcParams& p, float acc, int channe
     }
 }
 
-template <int MT>
-__device__ __forceinline__ void tmem_load_row(uint32_t taddr, float (&v)[MT]) {
+// NCOL consecutive fp32 accumulator columns of this thread's TMEM lane
+template <int NCOL>
+__device__ __forceinline__ void tmem_load_row(uint32_t taddr, float (&v)[NCOL]) {
 #pragma unroll
-    for (int c = 0; c < MT; c += 16) {
-        uint32_t r[16];
+    for (int c = 0; c < NCOL; c += 8) {
+        uint32_t r[8];
         asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
             : "r"(taddr + c));
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[c + i] = __uint_as_float(r[i]);
+        for (int i = 0; i < 8; ++i) v[c + i] = __uint_as_float(r[i]);
     }
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int MT, bool GATEUP>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -195,6 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                const TcParams p) {
     constexpr int kXStageBytes = MT * 128;
     constexpr uint32_t kTmemCols = MT < 32 ? 32 : MT;
+    // fp32 accumulate, A and B bf16 (format 1), both K-major
     constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17)
                                 | ((uint32_t)(kTileN >> 4) << 24);
     extern __shared__ unsigned char smem_raw[];
@@ -202,29 +264,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* a16 = smem;
     unsigned char* xs = a16 + kAStages * kAStageBytes;
-    unsigned char* w8 = xs + kAStages * kXStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(w8 + kWStages * kWStageBytes);
+    unsigned char* w8 = xs + kXStages * kXStageBytes;
+    float* red = reinterpret_cast<float*>(w8 + kWStages * kWStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(red) + kRedBytes);
     uint64_t* full_w = bars;
     uint64_t* empty_w = full_w + kWStages;
     uint64_t* full_a = empty_w + kWStages;
-    uint64_t* full_x = full_a + kAStages;
-    uint64_t* empty_ax = full_x + kAStages;
-    uint64_t* acc_done = empty_ax + kAStages;
+    uint64_t* empty_a = full_a + kAStages;
+    uint64_t* full_x = empty_a + kAStages;
+    uint64_t* empty_x = full_x + kXStages;
+    uint64_t* acc_done = empty_x + kXStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* last_flag = const_cast<int*>(abort_flag) + 1;
 
     const int tid = threadIdx.x;
-    const int warp = tid / kWarp;
+    const int warp = __shfl_sync(0xffffffffu, tid / kWarp, 0);      // warp-uniform by construction
     const int lane = tid % kWarp;
-    const int tile = blockIdx.x % p.tiles;
-    const int split = blockIdx.x / p.tiles;
-    const int nk = p.chunks_per_split;
-    const int k_first = split * nk * kBK;
+    const int split = (int)cluster_rank();           // cluster = the K-slices of one channel tile
+    const int tile = blockIdx.x / p.splits;
+    const int chunk_first = p.chunks * split / p.splits;            // slices may differ by one chunk
+    const int nk = p.chunks * (split + 1) / p.splits - chunk_first;
+    const int k_first = chunk_first * kBK;
     const int N = p.out_features;
+    const int rows_share = (MT + p.splits - 1) / p.splits;      // rows a CTA owns in the K-slice sum
     const int row_a = GATEUP ? tile * 64 : tile * kTileN;          // first W row of box 0
     const int row_b = GATEUP ? N + tile * 64 : tile * kTileN + 64;  // first W row of box 1
 
+    if (tid == 0) TC_TRACE(0);
+    if (tid == 0) TC_SPAN(0);
     Guard guard;
     guard.deadline = now_ns() + kBudgetNs;
     guard.abort_flag = abort_flag;
@@ -236,16 +303,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
         }
         for (int s = 0; s < kAStages; ++s) {
             mbar_init(&full_a[s], 4);
+            mbar_init(&empty_a[s], 1);
+        }
+        for (int s = 0; s < kXStages; ++s) {
             mbar_init(&full_x[s], 1);
-            mbar_init(&empty_ax[s], 1);
+            mbar_init(&empty_x[s], 1);
         }
         mbar_init(acc_done, 1);
         *abort_flag = 0;
-        *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 3) {
+    if (warp == kWarpTmem) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -254,8 +323,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    if (tid == 0) TC_TRACE(1);
 
-    if (warp == 0 && lane == 0) {
+    const int dq = dequant_index(warp);
+    if (warp == kWarpW) {
+        if (elect_one()) {
         // ---- weight producer --------------------------------------------------------------
         for (int i = 0; i < nk; ++i) {
             const int s = i % kWStages;
@@ -265,43 +337,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             tma_load_2d(dst, &w_map, k_first + i * kBK, row_a, &full_w[s]);
             tma_load_2d(dst + kWStageBytes / 2, &w_map, k_first + i * kBK, row_b, &full_w[s]);
         }
-    } else if (warp == 2 && lane == 0) {
+        }
+    } else if (warp == kWarpX) {
+        if (elect_one()) {
         // ---- activation producer ----------------------------------------------------------
         for (int i = 0; i < nk; ++i) {
-            const int sa = i % kAStages;
-            if (i >= kAStages && !guard.wait(&empty_ax[sa], ((i / kAStages) - 1) & 1)) break;
-            mbar_expect_tx(&full_x[sa], kXStageBytes);
-            tma_load_2d(xs + sa * kXStageBytes, &x_map, k_first + i * kBK, 0, &full_x[sa]);
+            const int sx = i % kXStages;
+            if (i >= kXStages && !guard.wait(&empty_x[sx], ((i / kXStages) - 1) & 1)) break;
+            mbar_expect_tx(&full_x[sx], kXStageBytes);
+            tma_load_2d(xs + sx * kXStageBytes, &x_map, k_first + i * kBK, 0, &full_x[sx]);
         }
-    } else if (warp == 1 && lane == 0) {
+        }
+    } else if (warp == kWarpMma) {
+        if (elect_one()) {
         // ---- MMA issuer -------------------------------------------------------------------
         bool ok = true;
         for (int i = 0; i < nk && ok; ++i) {
             const int sa = i % kAStages;
-            const uint32_t parity = (i / kAStages) & 1;
-            ok = guard.wait(&full_a[sa], parity) && guard.wait(&full_x[sa], parity);
+            const int sx = i % kXStages;
+            ok = guard.wait(&full_x[sx], (i / kXStages) & 1);
+            if (i < 16) TC_TRACE(64 + i);
+            ok = ok && guard.wait(&full_a[sa], (i / kAStages) & 1);
+            if (i < 16) TC_TRACE(80 + i);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_addr = smem_u32(a16 + sa * kAStageBytes);
-            const uint32_t b_addr = smem_u32(xs + sa * kXStageBytes);
+            const uint32_t b_addr = smem_u32(xs + sx * kXStageBytes);
 #pragma unroll
             for (int j = 0; j < kBK / 16; ++j) {
                 umma_f16(tmem_base, umma_desc(a_addr + 32 * j), umma_desc(b_addr + 32 * j), kIdesc,
                          (i | j) != 0 ? 1u : 0u);
             }
-            umma_commit(&empty_ax[sa]);
+            umma_commit(&empty_a[sa]);
+            umma_commit(&empty_x[sx]);
+            if (i < 16) TC_TRACE(8 + i);
         }
         umma_commit(acc_done);   // fires when every MMA issued above has completed
-    } else if (warp >= 4) {
-        // ---- dequantisers, then epilogue ----------------------------------------------------
-        const int t = tid - 128;          // 0..127 = tile row = TMEM lane
+        }
+    } else if (dq >= 0) {
+        // ---- dequantisers -------------------------------------------------------------------
+        const int group = dq / 4;                    // chunks group, group + kGroups, ...
+        const int t = (dq % 4) * 32 + lane;          // 0..127 within the group
         bool ok = true;
-        for (int i = 0; i < nk && ok; ++i) {
+        for (int i = group; i < nk && ok; i += kGroups) {
             const int s = i % kWStages;
             const int sa = i % kAStages;
             // a wait that gives up does so for the whole warp: the warp-level sync below must be
             // reached by all 32 lanes or by none
             if (!__all_sync(0xffffffffu, guard.wait(&full_w[s], (i / kWStages) & 1))) { ok = false; break; }
+            if (t == 0 && i < 16) TC_TRACE(24 + i);
             const unsigned char* src = w8 + s * kWStageBytes;
             uint32_t out[4][8];
 #pragma unroll
@@ -315,7 +399,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 dequant4(static_cast<uint32_t>(raw.w), out[q][6], out[q][7]);
             }
             if (i >= kAStages
-                && !__all_sync(0xffffffffu, guard.wait(&empty_ax[sa], ((i / kAStages) - 1) & 1))) {
+                && !__all_sync(0xffffffffu, guard.wait(&empty_a[sa], ((i / kAStages) - 1) & 1))) {
                 ok = false;
                 break;
             }
@@ -337,97 +421,96 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 mbar_arrive(&full_a[sa]);
                 mbar_arrive(&empty_w[s]);
             }
+            if (t == 0 && i < 16) TC_TRACE(40 + i);
         }
-        if (ok) ok = guard.wait(acc_done, 0);
         if (!ok) *abort_flag = 1;
-        // all 128 epilogue threads meet here, so that they agree on whether the tile is complete
-        // (the named barriers below must be reached by all of them or by none)
-        epilogue_barrier();
-        if (*abort_flag == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float v[MT];
-            tmem_load_row<MT>(tmem_base + ((uint32_t)((warp - 4) * 32) << 16), v);
-            const int channel = GATEUP ? tile * 64 + (t & 63) : tile * kTileN + t;
-            if (p.splits == 1) {
-                if (GATEUP) {
-                    float* stage = reinterpret_cast<float*>(w8);   // the weight ring is drained
-                    if (t >= 64) {
+    }
+
+    // ---- accumulators -> owners of the rows: warps 0..7, once their own role has finished; warp w
+    // reads TMEM lanes 32 * (w % 4) and the column half w / 4 ----------------------------------
+    __syncwarp();
+    if (warp < 8) {
+        if (!__all_sync(0xffffffffu, guard.wait(acc_done, 0))) *abort_flag = 1;
+    }
+    if (tid == 0) TC_TRACE(56);
+    __syncthreads();      // everyone agrees on whether the tile is complete
+    if (warp < 8 && *abort_flag == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        constexpr int kCols = MT / 2;
+        const int half = warp / 4;
+        const int t = (warp % 4) * 32 + lane;        // TMEM lane = channel within the tile
+        float v[kCols];
+        tmem_load_row<kCols>(tmem_base + ((uint32_t)((warp % 4) * 32) << 16) + half * kCols, v);
+        if (tid == 0) TC_TRACE(61);
+        // every row of this K-slice goes to the shared memory of the CTA that owns the row
+        const uint32_t slot0 = smem_u32(red) + (uint32_t)(split * rows_share * kTileN + t) * 4u;
+        int owner = (half * kCols) / rows_share;            // one division, then counted up
+        int within = half * kCols - owner * rows_share;
 #pragma unroll
-                        for (int s = 0; s < MT; ++s) stage[s * 64 + (t - 64)] = v[s];
-                    }
-                    epilogue_barrier();
-                    if (t < 64 && channel < N) {
-                        const float sg = p.scales[channel];
-                        const float su = p.scales[N + channel];
-#pragma unroll
-                        for (int s = 0; s < MT; ++s) {
-                            if (s < p.rows) {
-                                const float gate = v[s] * sg;
-                                const float up = stage[s * 64 + t] * su;
-                                const float val = gate / (1.0f + expf(-gate)) * up;
-                                const size_t o = (size_t)s * N + channel;
-                                if (p.y32 != nullptr) p.y32[o] = val;
-                                p.y[o] = f2bf(val);
-                            }
-                        }
-                    }
-                } else if (channel < N) {
-#pragma unroll
-                    for (int s = 0; s < MT; ++s) {
-                        if (s < p.rows) {
-                            const size_t o = (size_t)s * N + channel;
-                            const float val = finish(p, v[s], channel, o);
-                            if (p.y32 != nullptr) p.y32[o] = val;
-                            if (p.epilogue == EPI_BIAS_ADD) p.resid[o] = f2bf(val);
-                            else p.y[o] = f2bf(val);
-                        }
-                    }
-                }
-            } else {
-                // ---- K was split: park the slice, the last CTA of the tile sums in slice order ----
-                float* mine = p.partials + ((size_t)(tile * p.splits + split) * MT) * kTileN;
-#pragma unroll
-                for (int s = 0; s < MT; ++s) mine[s * kTileN + t] = v[s];
-                __threadfence();
-                epilogue_barrier();
-                if (t == 0) {
-                    const unsigned int ticket = atomicAdd(&p.tickets[tile], 1u);
-                    *last_flag = ticket == static_cast<unsigned int>(p.splits - 1);
-                }
-                epilogue_barrier();
-                if (*last_flag) {
-                    __threadfence();
-                    const float* base = p.partials + ((size_t)tile * p.splits * MT) * kTileN;
-                    const bool active = GATEUP ? (t < 64 && channel < N) : channel < N;
-                    if (active) {
-                        for (int s = 0; s < p.rows; ++s) {
-                            float acc = 0.0f, acc_up = 0.0f;
-                            for (int sp = 0; sp < p.splits; ++sp) {
-                                const float* slice = base + ((size_t)sp * MT + s) * kTileN;
-                                acc += __ldcg(slice + t);
-                                if (GATEUP) acc_up += __ldcg(slice + t + 64);
-                            }
-                            const size_t o = (size_t)s * N + channel;
-                            float val;
-                            if (GATEUP) {
-                                const float gate = acc * p.scales[channel];
-                                const float up = acc_up * p.scales[N + channel];
-                                val = gate / (1.0f + expf(-gate)) * up;
-                            } else {
-                                val = finish(p, acc, channel, o);
-                            }
-                            if (p.y32 != nullptr) p.y32[o] = val;
-                            if (!GATEUP && p.epilogue == EPI_BIAS_ADD) p.resid[o] = f2bf(val);
-                            else p.y[o] = f2bf(val);
-                        }
-                    }
-                    if (t == 0) p.tickets[tile] = 0u;
-                }
+        for (int j = 0; j < kCols; ++j) {
+            if (half * kCols + j < p.rows) {
+                st_cluster(peer_smem(slot0 + (uint32_t)(within * kTileN) * 4u, (uint32_t)owner), v[j]);
+            }
+            if (++within == rows_share) {
+                within = 0;
+                ++owner;
             }
         }
     }
 
+    // ---- the K-slices of a channel tile live in the CTAs of one cluster; CTA s owns rows
+    // [s * rows_share, (s + 1) * rows_share) and sums them over all slices in slice order ----------
+    constexpr int kPerRow = GATEUP ? 64 : kTileN;
+    const int c = tid % kPerRow;                       // kTcThreads is a multiple of kPerRow
+    const int channel = tile * kPerRow + c;
+    float scale = 0.0f, scale_up = 0.0f;
+    if (channel < N) {
+        scale = p.scales[channel];
+        if (GATEUP) scale_up = p.scales[N + channel];
+    }
+    __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (tid == 0) TC_TRACE(57);
+    cluster_sync();       // the only cluster barrier: nothing remote is touched after it
+    if (tid == 0) TC_TRACE(58);
+    if (*abort_flag == 0 && channel < N) {
+        const int row0 = split * rows_share;
+        const int my_rows = min(rows_share, p.rows - row0);
+#pragma unroll 2
+        for (int j = tid / kPerRow; j < my_rows; j += kTcThreads / kPerRow) {
+            float part[8], part_up[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                part[sp] = 0.0f;
+                part_up[sp] = 0.0f;
+                if (sp < p.splits) {
+                    const float* at = red + (sp * rows_share + j) * kTileN + c;
+                    part[sp] = at[0];
+                    if (GATEUP) part_up[sp] = at[64];
+                }
+            }
+            float acc = part[0], acc_up = part_up[0];
+#pragma unroll
+            for (int sp = 1; sp < 8; ++sp) {
+                acc += part[sp];
+                acc_up += part_up[sp];
+            }
+            const size_t out = (size_t)(row0 + j) * N + channel;
+            float val;
+            if (GATEUP) {
+                const float gate = acc * scale;
+                const float up = acc_up * scale_up;
+                val = gate / (1.0f + expf(-gate)) * up;
+            } else {
+                val = finish(p, acc, scale, channel, out);
+            }
+            if (p.y32 != nullptr) p.y32[out] = val;
+            if (!GATEUP && p.epilogue == EPI_BIAS_ADD) p.resid[out] = f2bf(val);
+            else p.y[out] = f2bf(val);
+            if (tid == 0 && j < 24 * (kTcThreads / kPerRow)) TC_TRACE(100 + j / (kTcThreads / kPerRow));
+        }
+    }
+    if (tid == 0) TC_TRACE(59);
     __syncthreads();
     if (*abort_flag) {
         // give copies that are still in flight time to land before the CTA's memory is released
@@ -436,7 +519,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
         while (now_ns() < until) __nanosleep(1000);
         __syncthreads();
     }
-    if (warp == 3) {
+    if (tid == 0) TC_SPAN(1);
+    if (warp == kWarpTmem) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
                      : "memory");
     }
@@ -474,18 +558,16 @@ bool make_map(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint
               swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Per-device scratch of the tensor-core path: K-slice partials, tile tickets and a buffer for
-// normalised activations.  Allocated once per device by configure_tc_kernels(); launches on one
-// device that use it must be ordered (the engine issues them on one stream).
+// Per-device scratch of the tensor-core path: a buffer for normalised activations.  Allocated
+// once per device by configure_tc_kernels(); launches on one device that use it must be ordered
+// (the engine issues them on one stream).
 struct TcScratch {
-    float* partials = nullptr;
-    unsigned int* tickets = nullptr;
     bf16* normalized = nullptr;
     int sms = 148;
+    // clusters of 1..8 CTAs that the device can hold at once, per kernel variant [MT index][GATEUP]
+    int resident_clusters[3][2][9] = {};
     bool ready = false;
 };
-constexpr size_t kPartialFloats = (size_t)512 * 64 * kTileN;     // up to 512 (tile, slice) pairs
-constexpr int kTicketCount = 4096;
 constexpr size_t kNormalizedElems = (size_t)kMaxRows * 8192;
 TcScratch g_scratch[64];
 std::mutex g_scratch_guard;
@@ -498,21 +580,49 @@ TcScratch* scratch_for_current_device() {
 
 template <int MT, bool GATEUP>
 size_t tc_smem_bytes() {
-    return 1024 + (size_t)kAStages * kAStageBytes + (size_t)kAStages * MT * 128
-        + (size_t)kWStages * kWStageBytes + 26 * sizeof(uint64_t) + 64;
+    return 1024 + (size_t)kAStages * kAStageBytes + (size_t)kXStages * MT * 128
+        + (size_t)kWStages * kWStageBytes + kRedBytes
+        + (2 * kWStages + 2 * kAStages + 2 * kXStages + 1) * sizeof(uint64_t) + 64;
 }
 
 template <int MT, bool GATEUP>
-cudaError_t configure_one() {
-    return cudaFuncSetAttribute(gemm_tc_kernel<MT, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                static_cast<int>(tc_smem_bytes<MT, GATEUP>()));
+cudaError_t configure_one(int (&resident)[9]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MT, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(tc_smem_bytes<MT, GATEUP>()));
+    for (int size = 1; size <= 8 && e == cudaSuccess; ++size) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(size * 64), 1, 1);
+        cfg.blockDim = dim3(kTcThreads, 1, 1);
+        cfg.dynamicSmemBytes = tc_smem_bytes<MT, GATEUP>();
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)size;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<MT, GATEUP>, &cfg);
+        resident[size] = clusters;
+    }
+    return e;
 }
 
 template <int MT, bool GATEUP>
 cudaError_t launch_mt(const CUtensorMap& wm, const CUtensorMap& xm, const TcParams& p, cudaStream_t stream) {
-    gemm_tc_kernel<MT, GATEUP>
-        <<<p.tiles * p.splits, kTcThreads, tc_smem_bytes<MT, GATEUP>(), stream>>>(wm, xm, p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.tiles * p.splits), 1, 1);
+    cfg.blockDim = dim3(kTcThreads, 1, 1);
+    cfg.dynamicSmemBytes = tc_smem_bytes<MT, GATEUP>();
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)p.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, GATEUP>, wm, xm, p);
 }
 
 int g_tc_min_rows = 9;
@@ -523,24 +633,21 @@ void set_tc_min_rows(int rows) { g_tc_min_rows = rows < 2 ? 2 : rows; }
 int tc_min_rows() { return g_tc_min_rows; }
 
 cudaError_t configure_tc_kernels() {
-    cudaError_t e = configure_one<16, false>();
-    if (e == cudaSuccess) e = configure_one<16, true>();
-    if (e == cudaSuccess) e = configure_one<32, false>();
-    if (e == cudaSuccess) e = configure_one<32, true>();
-    if (e == cudaSuccess) e = configure_one<64, false>();
-    if (e == cudaSuccess) e = configure_one<64, true>();
-    if (e != cudaSuccess) return e;
     int device = 0;
-    e = cudaGetDevice(&device);
+    cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return e;
     if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> lock(g_scratch_guard);
     TcScratch& s = g_scratch[device];
     if (s.ready) return cudaSuccess;
-    e = cudaMalloc(&s.partials, kPartialFloats * sizeof(float));
-    if (e == cudaSuccess) e = cudaMalloc(&s.tickets, kTicketCount * sizeof(unsigned int));
-    if (e == cudaSuccess) e = cudaMemset(s.tickets, 0, kTicketCount * sizeof(unsigned int));
-    if (e == cudaSuccess) e = cudaMalloc(&s.normalized, kNormalizedElems * sizeof(bf16));
+    e = configure_one<16, false>(s.resident_clusters[0][0]);
+    if (e == cudaSuccess) e = configure_one<16, true>(s.resident_clusters[0][1]);
+    if (e == cudaSuccess) e = configure_one<32, false>(s.resident_clusters[1][0]);
+    if (e == cudaSuccess) e = configure_one<32, true>(s.resident_clusters[1][1]);
+    if (e == cudaSuccess) e = configure_one<64, false>(s.resident_clusters[2][0]);
+    if (e == cudaSuccess) e = configure_one<64, true>(s.resident_clusters[2][1]);
+    if (e != cudaSuccess) return e;
+    e = cudaMalloc(&s.normalized, kNormalizedElems * sizeof(bf16));
     if (e != cudaSuccess) return e;
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && sms > 0) s.sms = sms;
@@ -581,17 +688,18 @@ cudaError_t launch_int8_gemm_tc(const GemvArgs& a, cudaStream_t stream) {
     const int mt = a.rows <= 16 ? 16 : (a.rows <= 32 ? 32 : 64);
     TcParams p;
     p.scales = a.scales; p.y = a.y; p.y32 = a.y32; p.bias = a.bias; p.resid = a.resid;
-    p.partials = scratch->partials; p.tickets = scratch->tickets;
     p.out_features = N; p.rows = a.rows; p.epilogue = a.epilogue;
     p.tiles = gateup ? (N + 63) / 64 : (N + kTileN - 1) / kTileN;
     const int nk = K / kBK;
+    // K-slices per tile = cluster size: as many as still let every cluster be resident at once (a
+    // second wave would double the time); slices and row shares may be ragged
+    const int (&resident)[9] = scratch->resident_clusters[mt == 16 ? 0 : (mt == 32 ? 1 : 2)][gateup ? 1 : 0];
     int splits = 1;
-    for (int s = 1; s <= nk; ++s) {
-        if (nk % s == 0 && (long long)p.tiles * s <= scratch->sms) splits = s;
+    for (int s = 2; s <= 8 && s <= nk; ++s) {
+        if (p.tiles <= resident[s]) splits = s;
     }
-    if ((size_t)p.tiles * splits * mt * kTileN > kPartialFloats || p.tiles > kTicketCount) splits = 1;
     p.splits = splits;
-    p.chunks_per_split = nk / splits;
+    p.chunks = nk;
 
     alignas(64) CUtensorMap wm, xm;
     const uint64_t w_rows = gateup ? 2ull * N : (uint64_t)N;
