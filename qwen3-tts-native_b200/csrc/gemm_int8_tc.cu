@@ -4,16 +4,18 @@
 // are the UMMA "A" operand: a CTA owns 128 output channels (one TMEM lane each) and a slice of K,
 // the sessions are the UMMA "N" dimension (16, 32 or 64 columns of fp32 accumulators in TMEM).
 //
-//   TMA (cp.async.bulk.tensor.2d)   int8 W tile 128 x 64  -> shared ring (8 stages)
-//   TMA, 128-byte swizzle           bf16 x tile  MT x 64  -> shared ring (6 stages), UMMA K-major layout
-//   2 x 4 warps, chunks in turn     int8 -> bf16 in registers (exact: XOR, PRMT into the mantissa
-//                                   of 2^23, packed subtract, PRMT of the high halves) -> shared,
-//                                   128-byte-swizzled K-major A tile
-//   1 thread                        tcgen05.mma.cta_group::1.kind::f16 (bf16 x bf16 -> fp32),
-//                                   128 x MT x 16 per instruction, accumulators in TMEM;
-//                                   tcgen05.commit frees stages
-//   4 warps                         tcgen05.ld the accumulators, per-channel scale and the same
-//                                   epilogues as the SIMT path
+//   TMA, 128-byte swizzle           int8 W tile 128 x 128 -> shared ring (6 stages of 16 KB)
+//   TMA, 128-byte swizzle           bf16 x tile MT x 128  -> shared ring (4 stages), UMMA K-major
+//   2 x 4 warps, steps in turn      a thread owns a channel: 128 int8 of its row -> bf16 in
+//                                   registers (exact: XOR, PRMT into the mantissa of 2^23, packed
+//                                   subtract, PRMT of the high halves) -> tcgen05.st into the TMEM
+//                                   columns of an A stage.  The dequantised weights never touch
+//                                   shared memory, whose bandwidth bounds this kernel.
+//   1 thread                        tcgen05.mma.cta_group::1.kind::f16 with A from TMEM and B
+//                                   (activations) from shared memory, 128 x MT x 16 per
+//                                   instruction; tcgen05.commit frees the stages
+//   the same 8 warps                tcgen05.ld the accumulators, then the K-slice exchange below
+//                                   and the same epilogues as the SIMT path
 // K is split across the CTAs of a thread-block cluster (up to 8) so that every SM streams
 // weights; each CTA pushes the rows of its slice into the shared memory of the CTA that owns
 // them (distributed shared memory) and, after one cluster barrier, sums the rows it owns over
@@ -34,26 +36,21 @@
 namespace q3t {
 namespace {
 
-// Warp roles.  A warp's scheduler is warp % 4.  The three single-thread roles (weight copies, MMA
-// issue, activation copies) sit on scheduler 0, which runs no dequantiser: a scheduler keeps
-// issuing from a warp that is ready, and the dequantisers' long runs of independent math would
-// otherwise delay every instruction of a role that shares their scheduler.
-constexpr int kGroups = 2;             // dequantiser groups of 4 warps, taking chunks in turn
-constexpr int kTcWarps = 12;
-constexpr int kTcThreads = kTcWarps * 32;
-constexpr int kWarpW = 0, kWarpMma = 4, kWarpX = 8, kWarpTmem = 11;
-// dequantisers: warps 1,2,3,5 (group 0) and 6,7,9,10 (group 1)
-__device__ __forceinline__ int dequant_index(int warp) {
-    return (warp % 4 == 0 || warp == kWarpTmem) ? -1 : (warp / 4) * 3 + (warp % 4) - 1;
-}
+// Warp roles: 0 weight copies, 1 MMA issue, 2 activation copies, 3 TMEM allocation (one elected
+// thread each); 4..7 and 8..11 are the two dequantiser groups.  Warp w may touch TMEM lanes
+// 32 * (w % 4) .. + 31 only, so a dequantiser owns the channel (w % 4) * 32 + lane.
+constexpr int kGroups = 2;
+constexpr int kTcThreads = 128 + 128 * kGroups;
 constexpr int kTileN = 128;            // output channels per CTA = TMEM lanes
-constexpr int kBK = 64;                // K elements per pipeline chunk
-constexpr int kWStages = 8;            // int8 ring
-constexpr int kAStages = 4;            // dequantised A ring
-constexpr int kXStages = 6;            // activation ring (its loads come from L2 and are latency-bound)
+constexpr int kBK = 128;               // K elements per pipeline step
+constexpr int kWStages = 6;            // int8 ring in shared memory
+constexpr int kXStages = 4;            // activation ring in shared memory
+constexpr int kAStages = 4;            // dequantised A stages in TMEM
+constexpr int kWStageBytes = kTileN * kBK;          // 16 KB
+constexpr int kAStageCols = kBK / 2;   // 64 TMEM columns: two bf16 per 32-bit column
+constexpr int kAccCols = 64;           // accumulators sit in columns [0, 64), A stages follow
+constexpr uint32_t kTmemCols = 512;    // 64 + 4 * 64 rounded up to a power of two
 constexpr int kRedBytes = 36 * 1024;   // K-slice exchange: up to 8 slices x ceil(64 / slices) rows x 128 fp32
-constexpr int kWStageBytes = kTileN * kBK;          // 8 KB
-constexpr int kAStageBytes = kTileN * kBK * 2;      // 16 KB
 constexpr unsigned long long kBudgetNs = 2000000000ull;   // 2 s for the whole kernel
 
 __device__ unsigned int g_tc_errors = 0;
@@ -180,13 +177,28 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
+// A (128 x 16 bf16) from TMEM columns, B from shared memory
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+// 32 consecutive columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr),
+          "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
 
@@ -225,8 +237,7 @@ __device__ __forceinline__ float finish(const TcParams& p, float acc, float scal
         case EPI_BIAS: return rbf(acc * scale) + bf2f(p.bias[channel]);
         case EPI_BIAS_SILU: {
             float v = rbf(acc * scale) + bf2f(p.bias[channel]);
-            v *= 1.0f / (1.0f + expf(-v));
-            return v;
+            return __fdividef(v, 1.0f + __expf(-v));
         }
         case EPI_BIAS_ADD: return bf2f(p.resid[o]) + rbf(rbf(acc * scale) + bf2f(p.bias[channel]));
         default: return acc * scale;
@@ -250,30 +261,33 @@ __device__ __forceinline__ void tmem_load_row(uint32_t taddr, float (&v)[NCOL]) 
 }
 
 
+__device__ __forceinline__ void dequant_barrier() {
+    asm volatile("bar.sync 1, %0;" ::"n"(128 * kGroups) : "memory");
+}
+
 template <int MT, bool GATEUP>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                const TcParams p) {
-    constexpr int kXStageBytes = MT * 128;
-    constexpr uint32_t kTmemCols = MT < 32 ? 32 : MT;
+    constexpr int kXAtomBytes = MT * 128;          // MT rows x 64 bf16, one 128-byte-swizzled atom
+    constexpr int kXStageBytes = 2 * kXAtomBytes;  // 128 K elements per step
     // fp32 accumulate, A and B bf16 (format 1), both K-major
     constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17)
                                 | ((uint32_t)(kTileN >> 4) << 24);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    unsigned char* a16 = smem;
-    unsigned char* xs = a16 + kAStages * kAStageBytes;
-    unsigned char* w8 = xs + kXStages * kXStageBytes;
-    float* red = reinterpret_cast<float*>(w8 + kWStages * kWStageBytes);
+    unsigned char* w8 = smem;
+    unsigned char* xs = w8 + kWStages * kWStageBytes;
+    float* red = reinterpret_cast<float*>(xs + kXStages * kXStageBytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(red) + kRedBytes);
     uint64_t* full_w = bars;
     uint64_t* empty_w = full_w + kWStages;
-    uint64_t* full_a = empty_w + kWStages;
-    uint64_t* empty_a = full_a + kAStages;
-    uint64_t* full_x = empty_a + kAStages;
+    uint64_t* full_x = empty_w + kWStages;
     uint64_t* empty_x = full_x + kXStages;
-    uint64_t* acc_done = empty_x + kXStages;
+    uint64_t* full_a = empty_x + kXStages;
+    uint64_t* empty_a = full_a + kAStages;
+    uint64_t* acc_done = empty_a + kAStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -282,13 +296,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     const int lane = tid % kWarp;
     const int split = (int)cluster_rank();           // cluster = the K-slices of one channel tile
     const int tile = blockIdx.x / p.splits;
-    const int chunk_first = p.chunks * split / p.splits;            // slices may differ by one chunk
-    const int nk = p.chunks * (split + 1) / p.splits - chunk_first;
-    const int k_first = chunk_first * kBK;
+    const int step_first = p.chunks * split / p.splits;             // slices may differ by one step
+    const int nk = p.chunks * (split + 1) / p.splits - step_first;
+    const int k_first = step_first * kBK;
     const int N = p.out_features;
     const int rows_share = (MT + p.splits - 1) / p.splits;      // rows a CTA owns in the K-slice sum
-    const int row_a = GATEUP ? tile * 64 : tile * kTileN;          // first W row of box 0
-    const int row_b = GATEUP ? N + tile * 64 : tile * kTileN + 64;  // first W row of box 1
+    const int row_a = GATEUP ? tile * 64 : tile * kTileN;          // first W row of the tile
+    const int row_b = N + tile * 64;                               // GATEUP: first row of the "up" half
 
     if (tid == 0) TC_TRACE(0);
     if (tid == 0) TC_SPAN(0);
@@ -301,20 +315,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             mbar_init(&full_w[s], 1);
             mbar_init(&empty_w[s], 4);
         }
-        for (int s = 0; s < kAStages; ++s) {
-            mbar_init(&full_a[s], 4);
-            mbar_init(&empty_a[s], 1);
-        }
         for (int s = 0; s < kXStages; ++s) {
             mbar_init(&full_x[s], 1);
             mbar_init(&empty_x[s], 1);
+        }
+        for (int s = 0; s < kAStages; ++s) {
+            mbar_init(&full_a[s], 4);
+            mbar_init(&empty_a[s], 1);
         }
         mbar_init(acc_done, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == kWarpTmem) {
+    if (warp == 3) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -325,97 +339,102 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     if (tid == 0) TC_TRACE(1);
 
-    const int dq = dequant_index(warp);
-    if (warp == kWarpW) {
+    if (warp == 0) {
         if (elect_one()) {
-        // ---- weight producer --------------------------------------------------------------
-        for (int i = 0; i < nk; ++i) {
-            const int s = i % kWStages;
-            if (i >= kWStages && !guard.wait(&empty_w[s], ((i / kWStages) - 1) & 1)) break;
-            mbar_expect_tx(&full_w[s], kWStageBytes);
-            unsigned char* dst = w8 + s * kWStageBytes;
-            tma_load_2d(dst, &w_map, k_first + i * kBK, row_a, &full_w[s]);
-            tma_load_2d(dst + kWStageBytes / 2, &w_map, k_first + i * kBK, row_b, &full_w[s]);
-        }
-        }
-    } else if (warp == kWarpX) {
-        if (elect_one()) {
-        // ---- activation producer ----------------------------------------------------------
-        for (int i = 0; i < nk; ++i) {
-            const int sx = i % kXStages;
-            if (i >= kXStages && !guard.wait(&empty_x[sx], ((i / kXStages) - 1) & 1)) break;
-            mbar_expect_tx(&full_x[sx], kXStageBytes);
-            tma_load_2d(xs + sx * kXStageBytes, &x_map, k_first + i * kBK, 0, &full_x[sx]);
-        }
-        }
-    } else if (warp == kWarpMma) {
-        if (elect_one()) {
-        // ---- MMA issuer -------------------------------------------------------------------
-        bool ok = true;
-        for (int i = 0; i < nk && ok; ++i) {
-            const int sa = i % kAStages;
-            const int sx = i % kXStages;
-            ok = guard.wait(&full_x[sx], (i / kXStages) & 1);
-            if (i < 16) TC_TRACE(64 + i);
-            ok = ok && guard.wait(&full_a[sa], (i / kAStages) & 1);
-            if (i < 16) TC_TRACE(80 + i);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_addr = smem_u32(a16 + sa * kAStageBytes);
-            const uint32_t b_addr = smem_u32(xs + sx * kXStageBytes);
-#pragma unroll
-            for (int j = 0; j < kBK / 16; ++j) {
-                umma_f16(tmem_base, umma_desc(a_addr + 32 * j), umma_desc(b_addr + 32 * j), kIdesc,
-                         (i | j) != 0 ? 1u : 0u);
+            // ---- weight producer ----------------------------------------------------------
+            for (int i = 0; i < nk; ++i) {
+                const int s = i % kWStages;
+                if (i >= kWStages && !guard.wait(&empty_w[s], ((i / kWStages) - 1) & 1)) break;
+                mbar_expect_tx(&full_w[s], kWStageBytes);
+                unsigned char* dst = w8 + s * kWStageBytes;
+                if (GATEUP) {
+                    tma_load_2d(dst, &w_map, k_first + i * kBK, row_a, &full_w[s]);
+                    tma_load_2d(dst + kWStageBytes / 2, &w_map, k_first + i * kBK, row_b, &full_w[s]);
+                } else {
+                    tma_load_2d(dst, &w_map, k_first + i * kBK, row_a, &full_w[s]);
+                }
             }
-            umma_commit(&empty_a[sa]);
-            umma_commit(&empty_x[sx]);
-            if (i < 16) TC_TRACE(8 + i);
         }
-        umma_commit(acc_done);   // fires when every MMA issued above has completed
+    } else if (warp == 2) {
+        if (elect_one()) {
+            // ---- activation producer ------------------------------------------------------
+            for (int i = 0; i < nk; ++i) {
+                const int sx = i % kXStages;
+                if (i >= kXStages && !guard.wait(&empty_x[sx], ((i / kXStages) - 1) & 1)) break;
+                mbar_expect_tx(&full_x[sx], kXStageBytes);
+                unsigned char* dst = xs + sx * kXStageBytes;
+                tma_load_2d(dst, &x_map, k_first + i * kBK, 0, &full_x[sx]);
+                tma_load_2d(dst + kXAtomBytes, &x_map, k_first + i * kBK + 64, 0, &full_x[sx]);
+            }
         }
-    } else if (dq >= 0) {
-        // ---- dequantisers -------------------------------------------------------------------
-        const int group = dq / 4;                    // chunks group, group + kGroups, ...
-        const int t = (dq % 4) * 32 + lane;          // 0..127 within the group
+    } else if (warp == 1) {
+        if (elect_one()) {
+            // ---- MMA issuer ---------------------------------------------------------------
+            for (int i = 0; i < nk; ++i) {
+                const int sa = i % kAStages;
+                const int sx = i % kXStages;
+                bool ok = guard.wait(&full_x[sx], (i / kXStages) & 1);
+                if (i < 16) TC_TRACE(64 + i);
+                ok = ok && guard.wait(&full_a[sa], (i / kAStages) & 1);
+                if (i < 16) TC_TRACE(80 + i);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_col = tmem_base + kAccCols + sa * kAStageCols;
+                const uint32_t b_addr = smem_u32(xs + sx * kXStageBytes);
+#pragma unroll
+                for (int j = 0; j < kBK / 16; ++j) {
+                    // 16 K elements = 8 TMEM columns of A, 32 bytes within a row of the B atom
+                    umma_f16_ts(tmem_base, a_col + 8 * j,
+                                umma_desc(b_addr + (j / 4) * kXAtomBytes + 32 * (j % 4)), kIdesc,
+                                (i | j) != 0 ? 1u : 0u);
+                }
+                umma_commit(&empty_a[sa]);
+                umma_commit(&empty_x[sx]);
+                if (i < 16) TC_TRACE(8 + i);
+            }
+            umma_commit(acc_done);   // fires when every MMA issued above has completed
+        }
+    } else if (warp >= 4) {
+        // ---- dequantisers, then accumulator readers -----------------------------------------
+        const int group = (warp - 4) / 4;            // steps group, group + kGroups, ...
+        const int t = (warp % 4) * 32 + lane;        // channel within the tile = TMEM lane
+        const uint32_t lane_base = tmem_base + ((uint32_t)((warp % 4) * 32) << 16);
         bool ok = true;
         for (int i = group; i < nk && ok; i += kGroups) {
             const int s = i % kWStages;
             const int sa = i % kAStages;
-            // a wait that gives up does so for the whole warp: the warp-level sync below must be
+            // a wait that gives up does so for the whole warp: the warp-level syncs below must be
             // reached by all 32 lanes or by none
             if (!__all_sync(0xffffffffu, guard.wait(&full_w[s], (i / kWStages) & 1))) { ok = false; break; }
             if (t == 0 && i < 16) TC_TRACE(24 + i);
-            const unsigned char* src = w8 + s * kWStageBytes;
-            uint32_t out[4][8];
+            // this thread's row: 128 bytes, whose 16-byte pieces sit at piece ^ (row & 7)
+            const unsigned char* rowp = w8 + s * kWStageBytes + t * 128;
+            int4 raw[8];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                // 32 consecutive 16-byte chunks per warp: conflict-free reads
-                const int chunk = q * 128 + t;
-                const int4 raw = *reinterpret_cast<const int4*>(src + (size_t)chunk * 16);
-                dequant4(static_cast<uint32_t>(raw.x), out[q][0], out[q][1]);
-                dequant4(static_cast<uint32_t>(raw.y), out[q][2], out[q][3]);
-                dequant4(static_cast<uint32_t>(raw.z), out[q][4], out[q][5]);
-                dequant4(static_cast<uint32_t>(raw.w), out[q][6], out[q][7]);
+            for (int c = 0; c < 8; ++c) {
+                raw[c] = *reinterpret_cast<const int4*>(rowp + ((c ^ (t & 7)) << 4));
             }
             if (i >= kAStages
                 && !__all_sync(0xffffffffu, guard.wait(&empty_a[sa], ((i / kAStages) - 1) & 1))) {
                 ok = false;
                 break;
             }
-            unsigned char* dst = a16 + sa * kAStageBytes;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int chunk = q * 128 + t;
-                const int row = chunk >> 2;
-                const int c = chunk & 3;       // 16 int8 = bf16 chunks 2c and 2c+1 of the row
-                unsigned char* rowp = dst + row * 128;
-                *reinterpret_cast<int4*>(rowp + (((2 * c) ^ (row & 7)) << 4)) =
-                    make_int4(out[q][0], out[q][1], out[q][2], out[q][3]);
-                *reinterpret_cast<int4*>(rowp + (((2 * c + 1) ^ (row & 7)) << 4)) =
-                    make_int4(out[q][4], out[q][5], out[q][6], out[q][7]);
+            for (int h = 0; h < 2; ++h) {
+                uint32_t out[32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int4 v = raw[4 * h + c];
+                    dequant4(static_cast<uint32_t>(v.x), out[8 * c + 0], out[8 * c + 1]);
+                    dequant4(static_cast<uint32_t>(v.y), out[8 * c + 2], out[8 * c + 3]);
+                    dequant4(static_cast<uint32_t>(v.z), out[8 * c + 4], out[8 * c + 5]);
+                    dequant4(static_cast<uint32_t>(v.w), out[8 * c + 6], out[8 * c + 7]);
+                }
+                tmem_store_32(lane_base + kAccCols + sa * kAStageCols + 32 * h, out);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(&full_a[sa]);
@@ -423,37 +442,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             }
             if (t == 0 && i < 16) TC_TRACE(40 + i);
         }
+        if (ok) ok = guard.wait(acc_done, 0);
+        if (t == 0 && group == 0) TC_TRACE(56);
         if (!ok) *abort_flag = 1;
-    }
-
-    // ---- accumulators -> owners of the rows: warps 0..7, once their own role has finished; warp w
-    // reads TMEM lanes 32 * (w % 4) and the column half w / 4 ----------------------------------
-    __syncwarp();
-    if (warp < 8) {
-        if (!__all_sync(0xffffffffu, guard.wait(acc_done, 0))) *abort_flag = 1;
-    }
-    if (tid == 0) TC_TRACE(56);
-    __syncthreads();      // everyone agrees on whether the tile is complete
-    if (warp < 8 && *abort_flag == 0) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        constexpr int kCols = MT / 2;
-        const int half = warp / 4;
-        const int t = (warp % 4) * 32 + lane;        // TMEM lane = channel within the tile
-        float v[kCols];
-        tmem_load_row<kCols>(tmem_base + ((uint32_t)((warp % 4) * 32) << 16) + half * kCols, v);
-        if (tid == 0) TC_TRACE(61);
-        // every row of this K-slice goes to the shared memory of the CTA that owns the row
-        const uint32_t slot0 = smem_u32(red) + (uint32_t)(split * rows_share * kTileN + t) * 4u;
-        int owner = (half * kCols) / rows_share;            // one division, then counted up
-        int within = half * kCols - owner * rows_share;
+        // all accumulator readers meet here, so that they agree on whether the tile is complete
+        dequant_barrier();
+        if (*abort_flag == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // each group takes half of the accumulator columns (= activation rows); every row of
+            // this K-slice goes to the shared memory of the CTA that owns the row
+            constexpr int kCols = MT / kGroups;
+            float v[kCols];
+            tmem_load_row<kCols>(lane_base + group * kCols, v);
+            if (t == 0 && group == 0) TC_TRACE(61);
+            if (p.splits == 1) {
+                // nothing to exchange: park the rows in this CTA's own shared memory
 #pragma unroll
-        for (int j = 0; j < kCols; ++j) {
-            if (half * kCols + j < p.rows) {
-                st_cluster(peer_smem(slot0 + (uint32_t)(within * kTileN) * 4u, (uint32_t)owner), v[j]);
-            }
-            if (++within == rows_share) {
-                within = 0;
-                ++owner;
+                for (int j = 0; j < kCols; ++j) red[(group * kCols + j) * kTileN + t] = v[j];
+            } else {
+                const uint32_t slot0 = smem_u32(red) + (uint32_t)(split * rows_share * kTileN + t) * 4u;
+                int owner = (group * kCols) / rows_share;            // one division, then counted up
+                int within = group * kCols - owner * rows_share;
+#pragma unroll
+                for (int j = 0; j < kCols; ++j) {
+                    if (group * kCols + j < p.rows) {
+                        st_cluster(peer_smem(slot0 + (uint32_t)(within * kTileN) * 4u, (uint32_t)owner), v[j]);
+                    }
+                    if (++within == rows_share) {
+                        within = 0;
+                        ++owner;
+                    }
+                }
             }
         }
     }
@@ -478,36 +497,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
         const int my_rows = min(rows_share, p.rows - row0);
 #pragma unroll 2
         for (int j = tid / kPerRow; j < my_rows; j += kTcThreads / kPerRow) {
-            float part[8], part_up[8];
+            const float* at = red + j * kTileN + c;
+            float acc = at[0], acc_up = GATEUP ? at[64] : 0.0f;
+            if (p.splits > 1) {
+                float part[8], part_up[8];
 #pragma unroll
-            for (int sp = 0; sp < 8; ++sp) {
-                part[sp] = 0.0f;
-                part_up[sp] = 0.0f;
-                if (sp < p.splits) {
-                    const float* at = red + (sp * rows_share + j) * kTileN + c;
-                    part[sp] = at[0];
-                    if (GATEUP) part_up[sp] = at[64];
+                for (int sp = 1; sp < 8; ++sp) {
+                    part[sp] = 0.0f;
+                    part_up[sp] = 0.0f;
+                    if (sp < p.splits) {
+                        part[sp] = at[sp * rows_share * kTileN];
+                        if (GATEUP) part_up[sp] = at[sp * rows_share * kTileN + 64];
+                    }
                 }
-            }
-            float acc = part[0], acc_up = part_up[0];
 #pragma unroll
-            for (int sp = 1; sp < 8; ++sp) {
-                acc += part[sp];
-                acc_up += part_up[sp];
+                for (int sp = 1; sp < 8; ++sp) {
+                    acc += part[sp];
+                    acc_up += part_up[sp];
+                }
             }
             const size_t out = (size_t)(row0 + j) * N + channel;
             float val;
             if (GATEUP) {
                 const float gate = acc * scale;
                 const float up = acc_up * scale_up;
-                val = gate / (1.0f + expf(-gate)) * up;
+                // hardware exp2/reciprocal (good to about 2^-21); this path is compared at bf16 tolerance
+                val = __fdividef(gate, 1.0f + __expf(-gate)) * up;
             } else {
                 val = finish(p, acc, scale, channel, out);
             }
             if (p.y32 != nullptr) p.y32[out] = val;
             if (!GATEUP && p.epilogue == EPI_BIAS_ADD) p.resid[out] = f2bf(val);
             else p.y[out] = f2bf(val);
-            if (tid == 0 && j < 24 * (kTcThreads / kPerRow)) TC_TRACE(100 + j / (kTcThreads / kPerRow));
         }
     }
     if (tid == 0) TC_TRACE(59);
@@ -520,7 +541,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
         __syncthreads();
     }
     if (tid == 0) TC_SPAN(1);
-    if (warp == kWarpTmem) {
+    if (warp == 3) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
                      : "memory");
     }
@@ -580,8 +601,7 @@ TcScratch* scratch_for_current_device() {
 
 template <int MT, bool GATEUP>
 size_t tc_smem_bytes() {
-    return 1024 + (size_t)kAStages * kAStageBytes + (size_t)kXStages * MT * 128
-        + (size_t)kWStages * kWStageBytes + kRedBytes
+    return 1024 + (size_t)kWStages * kWStageBytes + (size_t)kXStages * MT * 256 + kRedBytes
         + (2 * kWStages + 2 * kAStages + 2 * kXStages + 1) * sizeof(uint64_t) + 64;
 }
 
@@ -703,8 +723,9 @@ cudaError_t launch_int8_gemm_tc(const GemvArgs& a, cudaStream_t stream) {
 
     alignas(64) CUtensorMap wm, xm;
     const uint64_t w_rows = gateup ? 2ull * N : (uint64_t)N;
-    if (!make_map(&wm, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.w, K, w_rows, K, kBK, 64, CU_TENSOR_MAP_SWIZZLE_NONE)
-        || !make_map(&xm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, K, a.rows, (uint64_t)K * 2, kBK, mt,
+    if (!make_map(&wm, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.w, K, w_rows, K, kBK, gateup ? 64 : kTileN,
+                  CU_TENSOR_MAP_SWIZZLE_128B)
+        || !make_map(&xm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, K, a.rows, (uint64_t)K * 2, 64, mt,
                      CU_TENSOR_MAP_SWIZZLE_128B)) {
         return cudaErrorInvalidValue;
     }
