@@ -248,6 +248,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     q3t = importlib.import_module("qwen3-tts-native_b200")
     synth = importlib.import_module("qwen3-tts-native_b200.synth")
+    dp = importlib.import_module("qwen3-tts-native_b200.dp")
     native = q3t.native
 
     if args.leg == "gemv":
@@ -285,9 +286,9 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         model.close()
         return
 
-    lengths = np.random.default_rng(3 + rank).integers(64, 2049, size=SESSIONS)
+    lengths = dp.shard_kv_lengths(rank, SESSIONS)
     sessions = make_sessions(q3t, model, SESSIONS, lengths, total_frames, talker_cfg, predictor_cfg,
-                             1 + 1000 * rank)
+                             dp.shard_session_seeds(rank, SESSIONS)[0])
 
     def barrier():
         if world > 1:
@@ -304,11 +305,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     barrier()
     clock_report = clocks.stop()
     launches = model.kernel_launches() - launches_before
-    elapsed = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-    elapsed_s = float(elapsed.item()) * 1e-3
-    value = world * SESSIONS * K / elapsed_s
+    value, elapsed_s, _ = dp.whole_job_throughput(total_ms * 1e-3, SESSIONS * K, world, device="cuda")
 
     # ---- the same loop through the public C ABI, host round trip per frame ------------------
     api_frames(model, sessions, W)
@@ -316,10 +313,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     t0 = time.perf_counter()
     api_frames(model, sessions, K)
     torch.cuda.synchronize()
-    api_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(api_s, op=dist.ReduceOp.MAX)
-    e2e_value = world * SESSIONS * K / float(api_s.item())
+    e2e_value, _, _ = dp.whole_job_throughput(time.perf_counter() - t0, SESSIONS * K, world, device="cuda")
     table_bytes = 64 * (3 * 4 + 8 * 8 + 2 * 20)      # sizeof(FrameTable)
     e2e = {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": table_bytes,
            "d2h_bytes_per_step": SESSIONS * (4 + 32),

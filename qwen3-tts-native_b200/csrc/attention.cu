@@ -32,13 +32,17 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     constexpr int TPI = kWarp / LPT;       // tokens per warp iteration
     constexpr int ITERS = kWarpTokens / TPI;
 
-    const int split = blockIdx.x;
     const int kvh = blockIdx.y;
     const int row = blockIdx.z;
     const int pos = a.positions[row];
     const int len = pos + 1;
     const int nsplits = (len + kAttnChunk - 1) / kAttnChunk;
-    if (split >= nsplits) return;
+    // A CTA walks `units` consecutive 64-token splits.  Each split still produces its own
+    // (max, sum, weighted V) partial, so the result does not depend on how many a CTA takes.
+    const int units = a.units_per_cta > 0 ? a.units_per_cta : 1;
+    const int split_first = blockIdx.x * units;
+    if (split_first >= nsplits) return;
+    const int split_end = min(nsplits, split_first + units);
 
     __shared__ float qs[G][HD];
     __shared__ float wm[kAttnWarps][G];
@@ -74,7 +78,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
             // warps 0..G-1: query heads; warp G%4: the new key (last split only)
             for (int job = warp; job <= G; job += kAttnWarps) {
                 const bool is_key = job == G;
-                if (is_key && split != nsplits - 1) continue;
+                if (is_key && split_end != nsplits) continue;
                 const bf16* src = is_key ? a.k_new + (size_t)row * kn_stride + (size_t)kvh * HD
                                          : a.q + (size_t)row * q_stride + (size_t)(kvh * G + job) * HD;
                 const bf16* nw = is_key ? a.k_norm_w : a.q_norm_w;
@@ -131,12 +135,20 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     }
     __syncthreads();   // qs ready; this CTA's K/V append is visible to its own loads
 
-    // ---- this warp's 16 tokens --------------------------------------------------------
-    const int c1 = min(len, (split + 1) * kAttnChunk);
-    const int w0 = split * kAttnChunk + warp * kWarpTokens;
     const int sub = lane / LPT;
     const int j8 = (lane % LPT) * 8;
     const float scale = rsqrtf(static_cast<float>(HD));
+    const size_t part_stride = HD + 2;
+    float qreg[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qreg[g][e] = qs[g][j8 + e];
+
+    for (int split = split_first; split < split_end; ++split) {
+    // ---- this warp's 16 tokens --------------------------------------------------------
+    const int c1 = min(len, (split + 1) * kAttnChunk);
+    const int w0 = split * kAttnChunk + warp * kWarpTokens;
 
     float m_w[G], l_w[G], acc[G][8];
 #pragma unroll
@@ -150,17 +162,18 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     if (w0 < c1) {
         const bf16* kpage = kv_row(w0, false);   // the 16 tokens of a warp share one page
         const bf16* vpage = kv_row(w0, true);
-        int4 raw[ITERS];
+        // keys and values of the page are requested together: one memory latency per page
+        int4 raw[ITERS], rawv[ITERS];
 #pragma unroll
         for (int it = 0; it < ITERS; ++it) {
             const int t = it * TPI + sub;
             if (w0 + t < c1) raw[it] = *reinterpret_cast<const int4*>(kpage + (size_t)t * kvw + j8);
         }
-        float qreg[G][8];
 #pragma unroll
-        for (int g = 0; g < G; ++g)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) qreg[g][e] = qs[g][j8 + e];
+        for (int it = 0; it < ITERS; ++it) {
+            const int t = it * TPI + sub;
+            if (w0 + t < c1) rawv[it] = *reinterpret_cast<const int4*>(vpage + (size_t)t * kvw + j8);
+        }
 
         float s[G][ITERS];
 #pragma unroll
@@ -193,14 +206,9 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
         // values
 #pragma unroll
         for (int it = 0; it < ITERS; ++it) {
-            const int t = it * TPI + sub;
-            if (w0 + t < c1) raw[it] = *reinterpret_cast<const int4*>(vpage + (size_t)t * kvw + j8);
-        }
-#pragma unroll
-        for (int it = 0; it < ITERS; ++it) {
             const bool valid = w0 + it * TPI + sub < c1;
-            const uint32_t vw[4] = {(uint32_t)raw[it].x, (uint32_t)raw[it].y,
-                                    (uint32_t)raw[it].z, (uint32_t)raw[it].w};
+            const uint32_t vw[4] = {(uint32_t)rawv[it].x, (uint32_t)rawv[it].y,
+                                    (uint32_t)rawv[it].z, (uint32_t)rawv[it].w};
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 const float p = valid ? expf(s[g][it] - m_w[g]) : 0.0f;
@@ -241,7 +249,6 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     __syncthreads();
 
     // ---- merge the four warps ------------------------------------------------------------
-    const size_t part_stride = HD + 2;
     for (int i = tid; i < G * HD; i += kAttnThreads) {
         const int g = i / HD;
         const int d = i % HD;
@@ -273,6 +280,8 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
             part[2 + d] = A;
         }
     }
+    __syncthreads();   // the warp partials are reused by the next split
+    }   // splits of this CTA
     if (nsplits == 1) return;
 
     // ---- last CTA of this (row, kv head) merges the splits in order -------------------------
@@ -280,7 +289,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     __syncthreads();
     if (tid == 0) {
         const unsigned int ticket = atomicAdd(&a.counters[row * a.kv_heads + kvh], 1u);
-        is_last = ticket == static_cast<unsigned int>(nsplits - 1);
+        is_last = ticket == static_cast<unsigned int>((nsplits + units - 1) / units - 1);
     }
     __syncthreads();
     if (!is_last) return;
@@ -308,7 +317,8 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
 
 template <int HD, int G>
 cudaError_t launch_hd_g(const AttentionArgs& a, cudaStream_t stream) {
-    const dim3 grid(a.max_splits, a.kv_heads, a.rows);
+    const int units = a.units_per_cta > 0 ? a.units_per_cta : 1;
+    const dim3 grid((a.max_splits + units - 1) / units, a.kv_heads, a.rows);
     if (a.kv.page_table != nullptr) {
         decode_attention_kernel<HD, G, true><<<grid, kAttnThreads, 0, stream>>>(a);
     } else {
@@ -349,10 +359,17 @@ cudaError_t launch_decode_attention(const AttentionArgs& a, cudaStream_t stream)
                     || a.k_norm_w == nullptr || a.head_dim < 64)) {
         return cudaErrorInvalidValue;
     }
-    switch (a.head_dim) {
-        case 32: return launch_hd<32>(a, stream);
-        case 64: return launch_hd<64>(a, stream);
-        case 128: return launch_hd<128>(a, stream);
+    AttentionArgs b = a;
+    if (b.units_per_cta <= 0) {
+        // many small CTAs pay the query prologue and the launch machinery once per 64 tokens:
+        // with thousands of them, let each walk a few splits
+        const long long ctas = (long long)a.rows * a.kv_heads * a.max_splits;
+        b.units_per_cta = ctas >= 8192 ? 4 : (ctas >= 2048 ? 2 : 1);
+    }
+    switch (b.head_dim) {
+        case 32: return launch_hd<32>(b, stream);
+        case 64: return launch_hd<64>(b, stream);
+        case 128: return launch_hd<128>(b, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -115,6 +115,7 @@ struct AttentionArgs {
     int head_dim = 0;                   // 64 or 128 (32 allowed when not fused)
     int max_splits = 0;                 // grid.x; >= ceil(max length / kAttnChunk)
     int fused = 0;                      // 1: head-norm + RoPE on q/k_new, append k/v at position
+    int units_per_cta = 0;              // splits one CTA walks (0: chosen from the grid size); no effect on results
     float eps = kRmsEps;
     float theta = kRopeTheta;
 };
