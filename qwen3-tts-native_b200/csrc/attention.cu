@@ -18,6 +18,8 @@
 
 #include "q3t_kernels.cuh"
 
+#include <cstdlib>
+
 namespace q3t {
 namespace {
 
@@ -25,6 +27,25 @@ constexpr int kAttnThreads = 128;
 constexpr int kAttnWarps = kAttnThreads / kWarp;
 constexpr int kWarpTokens = kAttnChunk / kAttnWarps;   // 16 = one page
 static_assert(kWarpTokens == kPageTokens, "a warp must cover exactly one KV page");
+
+// D += A (16 x 16, bf16, row-major) * B (16 x 8, bf16, column-major), fp32 accumulate.  Lane l
+// holds, with g = l / 4 and t = l % 4:  a0 = A[g][2t, 2t+1], a1 = A[g+8][2t, 2t+1],
+// a2 = A[g][2t+8, 2t+9], a3 = A[g+8][2t+8, 2t+9];  b0 = B[2t, 2t+1][g], b1 = B[2t+8, 2t+9][g];
+// d0, d1 = D[g][2t, 2t+1], d2, d3 = D[g+8][2t, 2t+1].
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// (lo, hi) -> bf16x2 with lo in the low half
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
 
 template <int HD, int G, bool PAGED>
 __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const AttentionArgs a) {
@@ -145,10 +166,153 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
 #pragma unroll
         for (int e = 0; e < 8; ++e) qreg[g][e] = qs[g][j8 + e];
 
+    // head_dim 128 runs on the tensor cores (mma.sync, 16 x 8 x 16): the G query heads are rows
+    // 0..G-1 of the 16-row A operand, the other rows are zero.  A contraction may visit its
+    // index in any order as long as both operands agree, so a lane loads 16 contiguous bytes of
+    // K (8 dims of one token) and feeds them to two MMAs as they come; qa[] holds the query in
+    // the matching order: MMA (jj, m) of lane (gid, tig) covers dims 32 jj + 8 tig + 4 m + 0..3.
+    const int gid = lane >> 2;
+    const int tig = lane & 3;
+    uint32_t qa[4][2][2];
+    if constexpr (HD == 128) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const int d = 32 * jj + 8 * tig + 4 * m;
+                const bool real = gid < G;          // q is already bf16-valued: the pack is exact
+                qa[jj][m][0] = real ? pack_bf16x2(qs[gid % G][d], qs[gid % G][d + 1]) : 0u;
+                qa[jj][m][1] = real ? pack_bf16x2(qs[gid % G][d + 2], qs[gid % G][d + 3]) : 0u;
+            }
+    }
+
     for (int split = split_first; split < split_end; ++split) {
     // ---- this warp's 16 tokens --------------------------------------------------------
     const int c1 = min(len, (split + 1) * kAttnChunk);
     const int w0 = split * kAttnChunk + warp * kWarpTokens;
+
+    if constexpr (HD == 128) {
+        float mx = -INFINITY, lsum = 0.0f;
+        float o[2][8][4];
+#pragma unroll
+        for (int jb = 0; jb < 2; ++jb)
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[jb][x][e] = 0.0f;
+        if (w0 < c1) {
+            const bf16* kpage = kv_row(w0, false);   // the 16 tokens of a warp share one page
+            const bf16* vpage = kv_row(w0, true);
+            const int4 zero4 = make_int4(0, 0, 0, 0);
+            // K: token 8 nt + gid, dims 32 jj + 8 tig .. + 7
+            int4 kr[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const int t = 8 * nt + gid;
+                const bool valid = w0 + t < c1;
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    kr[nt][jj] = valid ? *reinterpret_cast<const int4*>(kpage + (size_t)t * kvw + 32 * jj + 8 * tig)
+                                       : zero4;
+                }
+            }
+            // V: tokens 8 h + 2 tig + p, dims 64 jb + 8 gid .. + 7.  Tokens past the end read as
+            // zero: their probability is zero, but 0 * (stale bits that decode as NaN) is not.
+            int4 vr[2][2][2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int pp = 0; pp < 2; ++pp) {
+                    const int t = 8 * h + 2 * tig + pp;
+                    const bool valid = w0 + t < c1;
+#pragma unroll
+                    for (int jb = 0; jb < 2; ++jb) {
+                        vr[h][pp][jb] = valid ? *reinterpret_cast<const int4*>(vpage + (size_t)t * kvw + 64 * jb + 8 * gid)
+                                              : zero4;
+                    }
+                }
+            // scores: s[nt][0..1] = head gid, tokens 8 nt + 2 tig + {0, 1}
+            float sc[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[nt][e] = 0.0f;
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    mma_bf16_16816(sc[nt], qa[jj][0][0], 0u, qa[jj][0][1], 0u,
+                                   (uint32_t)kr[nt][jj].x, (uint32_t)kr[nt][jj].y);
+                    mma_bf16_16816(sc[nt], qa[jj][1][0], 0u, qa[jj][1][1], 0u,
+                                   (uint32_t)kr[nt][jj].z, (uint32_t)kr[nt][jj].w);
+                }
+            }
+            float pr[2][2];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const bool valid = w0 + 8 * nt + 2 * tig + e < c1;
+                    pr[nt][e] = valid ? sc[nt][e] * scale : -INFINITY;
+                    mx = fmaxf(mx, pr[nt][e]);
+                }
+            // the four lanes of a group hold the 16 tokens of one head
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    pr[nt][e] = pr[nt][e] == -INFINITY ? 0.0f : expf(pr[nt][e] - mx);
+                    lsum += pr[nt][e];
+                }
+            lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+            lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+            // probabilities as the A operand of P V: the score fragment already has that layout.
+            // bf16 holds 8 bits of a probability; hi + lo keeps 16, so the product stays within
+            // 2^-16 of the fp32 one.
+            uint32_t ph[2], pl[2];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                ph[nt] = pack_bf16x2(pr[nt][0], pr[nt][1]);
+                const float r0 = pr[nt][0] - __uint_as_float(ph[nt] << 16);
+                const float r1 = pr[nt][1] - __uint_as_float(ph[nt] & 0xffff0000u);
+                pl[nt] = pack_bf16x2(r0, r1);
+            }
+            // output tile (jb, x): column n of the MMA is dim 64 jb + 8 n + x, so that a lane can
+            // build its B fragment (two tokens, one dim) from the 16 bytes it loaded per token
+#pragma unroll
+            for (int jb = 0; jb < 2; ++jb) {
+                const uint32_t t00[4] = {(uint32_t)vr[0][0][jb].x, (uint32_t)vr[0][0][jb].y,
+                                         (uint32_t)vr[0][0][jb].z, (uint32_t)vr[0][0][jb].w};
+                const uint32_t t01[4] = {(uint32_t)vr[0][1][jb].x, (uint32_t)vr[0][1][jb].y,
+                                         (uint32_t)vr[0][1][jb].z, (uint32_t)vr[0][1][jb].w};
+                const uint32_t t10[4] = {(uint32_t)vr[1][0][jb].x, (uint32_t)vr[1][0][jb].y,
+                                         (uint32_t)vr[1][0][jb].z, (uint32_t)vr[1][0][jb].w};
+                const uint32_t t11[4] = {(uint32_t)vr[1][1][jb].x, (uint32_t)vr[1][1][jb].y,
+                                         (uint32_t)vr[1][1][jb].z, (uint32_t)vr[1][1][jb].w};
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    const uint32_t sel = (x & 1) ? 0x7632u : 0x5410u;
+                    const uint32_t b0 = __byte_perm(t00[x >> 1], t01[x >> 1], sel);
+                    const uint32_t b1 = __byte_perm(t10[x >> 1], t11[x >> 1], sel);
+                    mma_bf16_16816(o[jb][x], ph[0], 0u, ph[1], 0u, b0, b1);
+                    mma_bf16_16816(o[jb][x], pl[0], 0u, pl[1], 0u, b0, b1);
+                }
+            }
+        }
+        if (gid < G) {
+            if (tig == 0) {
+                wm[warp][gid] = mx;
+                wl[warp][gid] = lsum;
+            }
+#pragma unroll
+            for (int jb = 0; jb < 2; ++jb)
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    wacc[warp][gid][64 * jb + 16 * tig + x] = o[jb][x][0];
+                    wacc[warp][gid][64 * jb + 16 * tig + 8 + x] = o[jb][x][1];
+                }
+        }
+    } else {
 
     float m_w[G], l_w[G], acc[G][8];
 #pragma unroll
@@ -246,6 +410,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
 #pragma unroll
             for (int e = 0; e < 8; ++e) wacc[warp][g][j8 + e] = acc[g][e];
     }
+    }   // head_dim other than 128
     __syncthreads();
 
     // ---- merge the four warps ------------------------------------------------------------
@@ -364,7 +529,11 @@ cudaError_t launch_decode_attention(const AttentionArgs& a, cudaStream_t stream)
         // many small CTAs pay the query prologue and the launch machinery once per 64 tokens:
         // with thousands of them, let each walk a few splits
         const long long ctas = (long long)a.rows * a.kv_heads * a.max_splits;
-        b.units_per_cta = ctas >= 8192 ? 4 : (ctas >= 2048 ? 2 : 1);
+        static const int forced = [] {
+            const char* v = std::getenv("QWEN3_TTS_ATTN_UNITS");
+            return v != nullptr ? std::atoi(v) : 0;
+        }();
+        b.units_per_cta = forced > 0 ? forced : (ctas >= 8192 ? 4 : (ctas >= 2048 ? 2 : 1));
     }
     switch (b.head_dim) {
         case 32: return launch_hd<32>(b, stream);
