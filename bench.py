@@ -253,9 +253,14 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
     if args.leg == "gemv":
         # operator microbenchmark: no model needed (keeps ncu captures small)
-        g = native.benchmark_int8_gemv(local_rank, args.gemv_in, args.gemv_out, rows=args.rows,
-                                       buffers=16, iterations=max(args.steps, 1))
+        if args.chain > 1:
+            g = native.benchmark_int8_gemv_chain(local_rank, args.gemv_in, args.gemv_out, chain=args.chain,
+                                                 buffers=16, iterations=max(args.steps, 1))
+        else:
+            g = native.benchmark_int8_gemv(local_rank, args.gemv_in, args.gemv_out, rows=args.rows,
+                                           buffers=16, iterations=max(args.steps, 1))
         print(json.dumps({"leg": "gemv", "in": args.gemv_in, "out": args.gemv_out, "rows": args.rows,
+                          "chain": args.chain,
                           "us_per_launch": g.mean_launch_microseconds,
                           "cold_us": g.cold_launch_microseconds,
                           "GBps": (args.gemv_in * args.gemv_out) / g.mean_launch_microseconds / 1e3}),
@@ -366,7 +371,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                             "achieved": GEMV_BYTES / gemv_s / 1e9, "peak": hbm_peak, "unit": "GB/s",
                             "frac": GEMV_BYTES / gemv_s / 1e9 / hbm_peak, "peak_kind": peak_kind,
                             "frac_of_8TBs": GEMV_BYTES / gemv_s / 8.0e12,
-                            "us_per_launch": g.mean_launch_microseconds, "traffic": None,
+                            "us_per_launch": g.mean_launch_microseconds, "traffic": 12626944,  # dram__bytes_read+write per launch, ncu capture of this kernel (profiles/)
                             "bytes_per_launch": GEMV_BYTES}
         if world == 1 and not args.no_cpu_baseline:
             frame_cpu, threads, sample = cpu_frame_seconds()
@@ -386,6 +391,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--chain", type=int, default=1,
+                    help="gemv leg: GEMVs per persistent chained launch (1 = one launch per GEMV)")
     ap.add_argument("--leg", choices=["all", "b64", "b1", "gemv"], default="all",
                     help="profiling aid: run one leg only and print a short JSON line")
     ap.add_argument("--gemv-in", type=int, default=2048)

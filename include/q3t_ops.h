@@ -91,6 +91,21 @@ QWEN3_TTS_API int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t inpu
                                               Qwen3TtsGemvBenchmark* output, char* error,
                                               size_t error_capacity);
 
+/* A chain of 1..8 dependent batch-1 GEMVs (rows == 1, in_features a multiple of 1024 up to 6144)
+ * in one persistent cooperative launch: op i+1 may read what op i wrote.  Bit-identical to issuing
+ * the same descriptors one by one through q3t_launch_int8_gemm_ex.  Launches through this entry
+ * point share one set of barrier counters per device and must be ordered (one stream).  No
+ * reference counterpart (it issues one launch per projection, talker.cu:2054-2333). */
+QWEN3_TTS_API int32_t q3t_launch_int8_gemv_chain(const Q3tGemmDesc* descs, int32_t count, void* stream);
+
+/* q3t_benchmark_int8_gemv for chained launches: `chain` GEMVs per launch, each on its own weight
+ * image; the reported mean is per GEMV (launch time / chain). */
+QWEN3_TTS_API int32_t q3t_benchmark_int8_gemv_chain(int32_t device_index, int32_t input_features,
+                                                    int32_t output_features, int32_t chain,
+                                                    int32_t buffers, int32_t iterations,
+                                                    Qwen3TtsGemvBenchmark* output, char* error,
+                                                    size_t error_capacity);
+
 /* ---- norms, RoPE, KV append, glue (talker_kernels.cu) --------------------------------- */
 
 QWEN3_TTS_API int32_t q3t_launch_rms_norm_rows(const uint16_t* input, const uint16_t* weight,

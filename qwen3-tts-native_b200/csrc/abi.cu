@@ -37,6 +37,7 @@ cudaError_t configure_device() {
     e = configure_gemv_kernels();
     if (e == cudaSuccess) e = configure_gemv_b1_kernels();
     if (e == cudaSuccess) e = configure_tc_kernels();
+    if (e == cudaSuccess) e = configure_gemv_chain_kernels();
     if (e == cudaSuccess) e = configure_sampler_kernels();
     if (e == cudaSuccess && device >= 0 && device < 64) done[device] = true;
     return e;
@@ -584,16 +585,74 @@ int32_t q3t_launch_int8_gemm_ex(const Q3tGemmDesc* d, void* stream) {
     return static_cast<int32_t>(launch_int8_gemm(a, S(stream)));
 }
 
+int32_t q3t_launch_int8_gemv_chain(const Q3tGemmDesc* descs, int32_t count, void* stream) {
+    if (descs == nullptr || count < 1 || count > kMaxChainOps) return cudaErrorInvalidValue;
+    if (const int32_t e = ready()) return e;
+    GemvArgs ops[kMaxChainOps];
+    for (int i = 0; i < count; ++i) {
+        const Q3tGemmDesc* d = descs + i;
+        if (d->struct_size != sizeof(Q3tGemmDesc) || d->epilogue < Q3T_EPI_PLAIN
+            || d->epilogue > Q3T_EPI_GATE_UP_SILU) {
+            return cudaErrorInvalidValue;
+        }
+        GemvArgs& a = ops[i];
+        a.w = d->weight; a.scales = d->scales; a.x = B(d->input); a.y = B(d->output);
+        a.y32 = d->output_f32; a.norm_w = B(d->norm_weight); a.norm_out = B(d->norm_output);
+        a.bias = B(d->bias); a.resid = B(d->residual);
+        a.in_features = d->in_features; a.out_features = d->out_features; a.rows = d->rows;
+        a.epilogue = d->epilogue;
+        a.eps = d->epsilon > 0.0f ? d->epsilon : kRmsEps;
+        if (!gemv_chain_supports(a)) return cudaErrorInvalidValue;
+    }
+    return static_cast<int32_t>(launch_gemv_chain(ops, count, nullptr, S(stream)));
+}
+
 int32_t q3t_launch_quantize_weight_rows(const uint16_t* weight, int8_t* quantized, float* scales,
                                         int32_t in_features, int32_t out_features, void* stream) {
     return static_cast<int32_t>(launch_quantize_weight_rows(B(weight), quantized, scales, in_features,
                                                             out_features, S(stream)));
 }
 
+}  // extern "C"
+
+namespace {
+int32_t benchmark_gemv(int32_t device_index, int32_t input_features, int32_t output_features, int32_t rows,
+                       int32_t buffers, int32_t iterations, int32_t chain, Qwen3TtsGemvBenchmark* output,
+                       char* error, size_t error_capacity);
+}
+
+extern "C" {
+
 int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t input_features,
                                 int32_t output_features, int32_t rows, int32_t buffers,
                                 int32_t iterations, Qwen3TtsGemvBenchmark* output, char* error,
                                 size_t error_capacity) {
+    return benchmark_gemv(device_index, input_features, output_features, rows, buffers, iterations, 1, output,
+                          error, error_capacity);
+}
+
+int32_t q3t_benchmark_int8_gemv_chain(int32_t device_index, int32_t input_features,
+                                      int32_t output_features, int32_t chain, int32_t buffers,
+                                      int32_t iterations, Qwen3TtsGemvBenchmark* output, char* error,
+                                      size_t error_capacity) {
+    if (chain < 1 || chain > kMaxChainOps || buffers < chain) {
+        write_error(error, error_capacity, "chain length must be 1..8 and not exceed the buffer count");
+        return QWEN3_TTS_TALKER_STATUS_INVALID_ARGUMENT;
+    }
+    return benchmark_gemv(device_index, input_features, output_features, 1, buffers, iterations, -chain, output,
+                          error, error_capacity);
+}
+
+}  // extern "C"
+
+namespace {
+
+// chain > 0: `chain` is ignored (single launches through the dispatcher); chain < 0: launches of
+// -chain chained GEMVs, each on its own weight image, iterations counted in GEMVs
+int32_t benchmark_gemv(int32_t device_index, int32_t input_features, int32_t output_features, int32_t rows,
+                       int32_t buffers, int32_t iterations, int32_t chain, Qwen3TtsGemvBenchmark* output,
+                       char* error, size_t error_capacity) {
+    const int links = chain < 0 ? -chain : 0;
     if (output == nullptr || input_features <= 0 || input_features % 16 != 0 || output_features <= 0
         || rows < 1 || rows > kMaxRows || buffers < 1 || iterations < 1) {
         write_error(error, error_capacity, "int8 GEMV benchmark arguments are out of range");
@@ -616,12 +675,23 @@ int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t input_features,
         check_cuda(cudaEventCreate(&t1), "cudaEventCreate");
         auto run = [&](int i) {
             GemvArgs a;
-            a.w = w.as<int8_t>() + (size_t)(i % buffers) * wbytes;
             a.scales = s.as<float>(); a.x = x.as<bf16>(); a.y = y.as<bf16>();
             a.in_features = input_features; a.out_features = output_features; a.rows = rows;
-            check_cuda(launch_int8_gemm(a, stream), "int8 GEMV");
+            if (links == 0) {
+                a.w = w.as<int8_t>() + (size_t)(i % buffers) * wbytes;
+                check_cuda(launch_int8_gemm(a, stream), "int8 GEMV");
+                return;
+            }
+            GemvArgs ops[kMaxChainOps];
+            for (int c = 0; c < links; ++c) {
+                ops[c] = a;
+                ops[c].w = w.as<int8_t>() + (size_t)((i * links + c) % buffers) * wbytes;
+                if (!gemv_chain_supports(ops[c])) throw std::runtime_error("shape not supported by the GEMV chain");
+            }
+            check_cuda(launch_gemv_chain(ops, links, nullptr, stream), "int8 GEMV chain");
         };
         float cold_ms = 0.0f, total_ms = 0.0f;
+        int iterations_per_launch = 1;
         try {
             check_cuda(cudaEventRecord(t0, stream), "cudaEventRecord");
             run(0);
@@ -630,7 +700,7 @@ int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t input_features,
             check_cuda(cudaEventElapsedTime(&cold_ms, t0, t1), "cudaEventElapsedTime");
             // The timed launches replay a captured graph (4 passes over the weight images), so
             // that the figure is the kernel's and not the host's launch rate.
-            const int per_graph = buffers * 4;
+            const int per_graph = links == 0 ? buffers * 4 : (buffers * 4 + links - 1) / links;
             cudaGraph_t graph = nullptr;
             check_cuda(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal),
                        "cudaStreamBeginCapture");
@@ -646,7 +716,8 @@ int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t input_features,
             const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
             cudaGraphDestroy(graph);
             check_cuda(ie, "cudaGraphInstantiate");
-            const int replays = (iterations + per_graph - 1) / per_graph;
+            const int per_replay = per_graph * (links == 0 ? 1 : links);
+            const int replays = (iterations + per_replay - 1) / per_replay;
             cudaError_t le = cudaGraphLaunch(exec, stream);
             if (le == cudaSuccess) le = cudaStreamSynchronize(stream);
             if (le == cudaSuccess) le = cudaEventRecord(t0, stream);
@@ -656,7 +727,8 @@ int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t input_features,
             if (le == cudaSuccess) le = cudaEventElapsedTime(&total_ms, t0, t1);
             cudaGraphExecDestroy(exec);
             check_cuda(le, "timed GEMV graph replays");
-            iterations = replays * per_graph;
+            iterations = replays * per_graph * (links == 0 ? 1 : links);
+            if (links != 0) iterations_per_launch = links;
         } catch (...) {
             cudaEventDestroy(t0); cudaEventDestroy(t1); cudaStreamDestroy(stream);
             throw;
@@ -667,13 +739,17 @@ int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t input_features,
         b.output_features = output_features;
         b.iterations = iterations;
         b.weight_bytes = wbytes;
-        b.cold_launch_microseconds = cold_ms * 1000.0f;
-        b.mean_launch_microseconds = total_ms * 1000.0f / iterations;
+        b.cold_launch_microseconds = cold_ms * 1000.0f / iterations_per_launch;
+        b.mean_launch_microseconds = total_ms * 1000.0f / iterations;     // per GEMV
         b.tera_operations_per_second = static_cast<float>(
             2.0 * input_features * output_features * rows / (b.mean_launch_microseconds * 1.0e-6) / 1.0e12);
         *output = b;
     }, QWEN3_TTS_TALKER_STATUS_CUDA, error, error_capacity);
 }
+
+}  // namespace
+
+extern "C" {
 
 int32_t q3t_launch_rms_norm_rows(const uint16_t* input, const uint16_t* weight, uint16_t* output,
                                  int32_t rows, int32_t width, float epsilon, void* stream) {
@@ -902,7 +978,9 @@ int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle session, int32_t pos
                    QWEN3_TTS_TALKER_STATUS_STATE, error, error_capacity);
 }
 
-uint32_t q3t_kernel_error_count(void) { return gemv_b1_error_count() + gemm_tc_error_count(); }
+uint32_t q3t_kernel_error_count(void) {
+    return gemv_b1_error_count() + gemm_tc_error_count() + gemv_chain_error_count();
+}
 
 int32_t q3t_session_current_token(Qwen3TtsSessionHandle session, uint16_t* token, char* error,
                                   size_t error_capacity) {

@@ -47,6 +47,14 @@ cudaError_t launch_int8_gemm_simt(const GemvArgs& args, cudaStream_t stream);
 bool gemv_b1_supports(const GemvArgs& args);
 cudaError_t launch_int8_gemv_b1(const GemvArgs& args, cudaStream_t stream);
 cudaError_t configure_gemv_b1_kernels();
+// chain of dependent batch-1 GEMVs in one persistent cooperative launch (gemv_chain.cu):
+// rows == 1, K a multiple of 1024 up to 6144; bit-identical to the SIMT kernel
+constexpr int kMaxChainOps = 8;
+constexpr int kChainSyncWords = 4;       // barrier arrivals, exit tickets, errors, spare (zeroed once)
+bool gemv_chain_supports(const GemvArgs& args);
+cudaError_t launch_gemv_chain(const GemvArgs* ops, int count, unsigned int* sync, cudaStream_t stream);
+cudaError_t configure_gemv_chain_kernels();   // also allocates the default counters of the device
+unsigned int gemv_chain_error_count();
 // tensor-core path (tcgen05, TMEM accumulators): rows >= tc_min_rows() and K % 64 == 0
 bool gemm_tc_supports(const GemvArgs& args);
 cudaError_t launch_int8_gemm_tc(const GemvArgs& args, cudaStream_t stream);

@@ -102,6 +102,7 @@ EXPORTED_SYMBOLS = (
     "q3t_launch_int8_gemm_rows", "q3t_launch_int8_gemm_rows_add",
     "q3t_launch_int8_gate_up_silu_rows", "q3t_launch_int8_gemm_ex",
     "q3t_launch_quantize_weight_rows", "q3t_benchmark_int8_gemv", "q3t_launch_rms_norm_rows",
+    "q3t_launch_int8_gemv_chain", "q3t_benchmark_int8_gemv_chain",
     "q3t_launch_head_rms_norm_rows", "q3t_launch_rope_rows_at", "q3t_launch_kv_scatter_rows",
     "q3t_launch_bias_activation_rows", "q3t_launch_add_in_place", "q3t_launch_silu_gate",
     "q3t_launch_gather_embedding_rows", "q3t_launch_add_embedding_rows",
@@ -539,6 +540,16 @@ def probe_device(device_index: int = 0) -> DeviceInfoC:
     out = DeviceInfoC()
     err = C.create_string_buffer(_ERR_CAP)
     _check(library().qwen3_tts_probe_device(device_index, C.byref(out), err, _ERR_CAP), err)
+    return out
+
+
+def benchmark_int8_gemv_chain(device_index: int, in_features: int, out_features: int, chain: int = 8,
+                              buffers: int = 16, iterations: int = 2000) -> GemvBenchmarkC:
+    """GEMVs chained `chain` to a persistent launch; the mean is per GEMV."""
+    out = GemvBenchmarkC()
+    err = C.create_string_buffer(_ERR_CAP)
+    _check(library().q3t_benchmark_int8_gemv_chain(device_index, in_features, out_features, chain, buffers,
+                                                   iterations, C.byref(out), err, _ERR_CAP), err)
     return out
 
 
