@@ -48,7 +48,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 template <int HD, int G, bool PAGED>
-__global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const AttentionArgs a) {
+__global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const AttentionArgs a) {
     constexpr int LPT = HD / 8;            // lanes per token
     constexpr int TPI = kWarp / LPT;       // tokens per warp iteration
     constexpr int ITERS = kWarpTokens / TPI;
@@ -126,9 +126,15 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
 #pragma unroll
                 for (int j = 0; j < DPL / 2; ++j) {
                     const int d = lane + 32 * j;
-                    const float angle = static_cast<float>(pos) * rope_inv_freq(d, HD, a.theta);
                     float o1, o2;
-                    rope_pair(y[j], y[j + DPL / 2], angle, o1, o2);
+                    if (a.rope_table != nullptr && pos < a.rope_positions) {
+                        // cos | sin of this (position, pair) as two bf16, made by the same code below
+                        const uint32_t cs = a.rope_table[(size_t)pos * (HD / 2) + d];
+                        rope_pair_cs(y[j], y[j + DPL / 2], bf_lo(cs), bf_hi(cs), o1, o2);
+                    } else {
+                        const float angle = static_cast<float>(pos) * rope_inv_freq(d, HD, a.theta);
+                        rope_pair(y[j], y[j + DPL / 2], angle, o1, o2);
+                    }
                     y[j] = o1;
                     y[j + DPL / 2] = o2;
                 }
@@ -503,6 +509,28 @@ cudaError_t launch_hd(const AttentionArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+namespace {
+__global__ void rope_table_kernel(uint32_t* table, int positions, int head_dim, float theta) {
+    const int half = head_dim / 2;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= positions * half) return;
+    const int pos = i / half;
+    const int d = i % half;
+    const float angle = static_cast<float>(pos) * rope_inv_freq(d, head_dim, theta);
+    const uint32_t c = __bfloat16_as_ushort(f2bf(cosf(angle)));
+    const uint32_t sn = __bfloat16_as_ushort(f2bf(sinf(angle)));
+    table[i] = c | (sn << 16);
+}
+}  // namespace
+
+cudaError_t launch_build_rope_table(uint32_t* table, int positions, int head_dim, float theta,
+                                    cudaStream_t stream) {
+    if (table == nullptr || positions < 1 || head_dim < 2 || head_dim % 2 != 0) return cudaErrorInvalidValue;
+    const int total = positions * (head_dim / 2);
+    rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(table, positions, head_dim, theta);
+    return cudaGetLastError();
+}
 
 size_t attention_scratch_floats(int rows, int q_heads, int head_dim, int max_splits) {
     return (size_t)rows * q_heads * max_splits * (head_dim + 2);

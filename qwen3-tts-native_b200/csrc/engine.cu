@@ -380,6 +380,19 @@ void Model::finalize(uint64_t* weight_bytes, uint32_t* tensor_count) {
                           kResidualCodebooks * sizeof(const bf16*), cudaMemcpyHostToDevice),
                "cudaMemcpy(embedding table)");
     predictor_embedding_table = embedding_ptrs_.as<const bf16*>();
+    talker_rope_ = DeviceBuffer((size_t)kRopePositions * (talker.head_dim / 2) * sizeof(uint32_t));
+    check_cuda(launch_build_rope_table(talker_rope_.as<uint32_t>(), kRopePositions, talker.head_dim,
+                                       kRopeTheta, upload_stream_), "rope table");
+    talker_rope = talker_rope_.as<uint32_t>();
+    if (predictor.head_dim == talker.head_dim) {
+        predictor_rope = talker_rope;
+    } else {
+        predictor_rope_ = DeviceBuffer((size_t)kRopePositions * (predictor.head_dim / 2) * sizeof(uint32_t));
+        check_cuda(launch_build_rope_table(predictor_rope_.as<uint32_t>(), kRopePositions, predictor.head_dim,
+                                           kRopeTheta, upload_stream_), "rope table");
+        predictor_rope = predictor_rope_.as<uint32_t>();
+    }
+    check_cuda(cudaStreamSynchronize(upload_stream_), "cudaStreamSynchronize(rope tables)");
     talker_pool.reset(new KvPool(talker.layers, talker.kv_width, 8));
     predictor_pool.reset(new KvPool(predictor.layers, predictor.kv_width, 6));
     finalized_ = true;
@@ -398,7 +411,7 @@ Workspace& Model::batch_workspace() {
 namespace {
 
 void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWeights>& layers,
-                    const KvPool& pool, const int* page_table, int table_stride,
+                    const uint32_t* rope_table, const KvPool& pool, const int* page_table, int table_stride,
                     const int* positions, int n, int splits, cudaStream_t s) {
     const int qkv_width = d.q_width + 2 * d.kv_width;
     for (size_t l = 0; l < layers.size(); ++l) {
@@ -423,6 +436,7 @@ void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWei
         a.counters = w.counters.as<unsigned int>();
         a.rows = n; a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.head_dim = d.head_dim;
         a.max_splits = splits; a.fused = 1;
+        a.rope_table = rope_table; a.rope_positions = Model::kRopePositions;
         check_cuda(launch_decode_attention(a, s), "decode attention");
 
         GemvArgs o;
@@ -461,7 +475,7 @@ void enqueue_predictor(Workspace& w, Model& m, int n, cudaStream_t s) {
         g.x = w.x_in.as<bf16>(); g.y = w.hidden.as<bf16>(); g.bias = m.small_to_mtp_bias;
         g.in_features = H; g.out_features = PH; g.rows = n; g.epilogue = EPI_BIAS;
         check_cuda(launch_int8_gemm(g, s), "predictor input projection");
-        enqueue_layers(w, m.predictor, m.predictor_layers, *m.predictor_pool,
+        enqueue_layers(w, m.predictor, m.predictor_layers, m.predictor_rope, *m.predictor_pool,
                        w.predictor_pages.as<int>(), 1,
                        w.predictor_positions.as<int>() + (size_t)p * kMaxRows, n, 1, s);
         if (p >= 1) {
@@ -519,7 +533,7 @@ void enqueue_talker(Workspace& w, Model& m, int n, int splits, cudaStream_t s) {
                                    m.text_embedding, kTextVocab, w.hidden.as<bf16>(),
                                    w.x_in.as<bf16>(), H, n, s), "talker input");
     enqueue_text_projection(w, m, n, true, s);
-    enqueue_layers(w, m.talker, m.talker_layers, *m.talker_pool, w.talker_pages.as<int>(),
+    enqueue_layers(w, m.talker, m.talker_layers, m.talker_rope, *m.talker_pool, w.talker_pages.as<int>(),
                    Workspace::kMaxPagesPerRow, table->position, n, splits, s);
     enqueue_talker_head(w, m, n, 1, s);
 }
@@ -534,7 +548,7 @@ void enqueue_prompt_step(Workspace& w, Model& m, const int* text_ids, const int*
     enqueue_text_projection(w, m, 1, false, s);
     check_cuda(launch_prompt_combine(table, text_ids, codec_ids, m.codec_embedding, kTalkerVocab,
                                      w.hidden.as<bf16>(), H, s), "prompt combine");
-    enqueue_layers(w, m.talker, m.talker_layers, *m.talker_pool, w.talker_pages.as<int>(),
+    enqueue_layers(w, m.talker, m.talker_layers, m.talker_rope, *m.talker_pool, w.talker_pages.as<int>(),
                    Workspace::kMaxPagesPerRow, table->position, 1, splits, s);
     check_cuda(launch_advance_position(table, s), "advance position");
 }

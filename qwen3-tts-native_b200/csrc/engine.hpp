@@ -165,6 +165,10 @@ public:
     std::array<const bf16*, 15> predictor_embeddings{};
     const bf16* const* predictor_embedding_table = nullptr;   // device copy of the 15 pointers
     std::unique_ptr<KvPool> talker_pool, predictor_pool;
+    // bf16 cos | sin of every (position, rotary pair), one table per head_dim in use
+    static constexpr int kRopePositions = 8192;
+    const uint32_t* talker_rope = nullptr;
+    const uint32_t* predictor_rope = nullptr;
     std::mutex mutex;               // pools, workspaces
     int mask_eos = 0;
     int use_graphs = 1;
@@ -194,7 +198,7 @@ private:
     cudaStream_t upload_stream_ = nullptr;
     std::unordered_map<std::string, Spec> specs_;
     std::vector<DeviceBuffer> storage_;   // every resident tensor (int8 rows, scales, bf16)
-    DeviceBuffer staging_, embedding_ptrs_;
+    DeviceBuffer staging_, embedding_ptrs_, talker_rope_, predictor_rope_;
     size_t staging_bytes_ = 0;
     std::unique_ptr<Workspace> batch_;
 };

@@ -81,6 +81,17 @@ __device__ __forceinline__ void rope_pair(float first, float second, float angle
     out_second = rbf(sc + fs);
 }
 
+// the same with cos and sin given (already rounded to bf16)
+__device__ __forceinline__ void rope_pair_cs(float first, float second, float c, float s,
+                                             float& out_first, float& out_second) {
+    const float fc = rbf(first * c);
+    const float ss = rbf(second * s);
+    const float sc = rbf(second * c);
+    const float fs = rbf(first * s);
+    out_first = rbf(fc - ss);
+    out_second = rbf(sc + fs);
+}
+
 __device__ __forceinline__ float rope_inv_freq(int d, int head_dim, float theta) {
     const float exponent = static_cast<float>(2 * d) / static_cast<float>(head_dim);
     return powf(theta, -exponent);

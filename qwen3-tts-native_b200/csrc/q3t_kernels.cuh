@@ -113,6 +113,8 @@ struct AttentionArgs {
     bf16* out = nullptr;                // [rows][q_heads*head_dim]
     float* out32 = nullptr;             // optional fp32 value before the final round
     KvLayout kv;
+    const uint32_t* rope_table = nullptr;   // optional [rope_positions][head_dim/2] bf16 cos | sin << 16
+    int rope_positions = 0;                 //   (launch_build_rope_table); positions beyond it are computed
     float* scratch = nullptr;           // split-KV partials, see attention_scratch_floats()
     unsigned int* counters = nullptr;   // [rows*kv_heads], zero before the first launch
     int q_stride = 0;                   // elements between rows of q (0: q_heads*head_dim)
@@ -131,6 +133,10 @@ struct AttentionArgs {
 constexpr int kAttnChunk = 64;          // tokens per split
 size_t attention_scratch_floats(int rows, int q_heads, int head_dim, int max_splits);
 cudaError_t launch_decode_attention(const AttentionArgs& args, cudaStream_t stream);
+// cos/sin of every (position, rotary pair), rounded to bf16 as the fused prologue rounds them;
+// computed by the same device expressions, so using the table changes no bit
+cudaError_t launch_build_rope_table(uint32_t* table, int positions, int head_dim, float theta,
+                                    cudaStream_t stream);
 
 // ---------------------------------------------------------------- sampler
 struct SamplerRow {
