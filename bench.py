@@ -253,7 +253,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
     if args.leg == "gemv":
         # operator microbenchmark: no model needed (keeps ncu captures small)
-        if args.chain > 1:
+        if args.chain >= 1:
             g = native.benchmark_int8_gemv_chain(local_rank, args.gemv_in, args.gemv_out, chain=args.chain,
                                                  buffers=16, iterations=max(args.steps, 1))
         else:
@@ -391,8 +391,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--chain", type=int, default=1,
-                    help="gemv leg: GEMVs per persistent chained launch (1 = one launch per GEMV)")
+    ap.add_argument("--chain", type=int, default=0,
+                    help="gemv leg: GEMVs per persistent chained launch (0 = the dispatcher's single launches)")
     ap.add_argument("--leg", choices=["all", "b64", "b1", "gemv"], default="all",
                     help="profiling aid: run one leg only and print a short JSON line")
     ap.add_argument("--gemv-in", type=int, default=2048)

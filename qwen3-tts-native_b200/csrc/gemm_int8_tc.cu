@@ -207,16 +207,6 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                  ::"r"(smem_u32(bar)) : "memory");
 }
 
-__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
-    unsigned long long d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
 
 // four int8 (one word) -> four bf16 (two words), exact
 __device__ __forceinline__ void dequant4(uint32_t word, uint32_t& lo, uint32_t& hi) {

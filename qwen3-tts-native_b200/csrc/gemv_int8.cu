@@ -52,7 +52,10 @@ __device__ __forceinline__ float dot16(const int4& w, const int4& xa, const int4
     return sum;
 }
 
-template <int ROWS, bool GATEUP, bool NORM>
+// KPRE = weight vectors a lane has in flight at once (and requests before the activations are
+// staged): 4 covers a whole row up to K = 2048; the long rows of the batch-1 down projection use
+// 12 so that a row is one round trip to memory instead of three.
+template <int ROWS, bool GATEUP, bool NORM, int KPRE = 4>
 __global__ void __launch_bounds__(kThreads)
 gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ scales,
                  const bf16* __restrict__ input, bf16* __restrict__ output,
@@ -72,7 +75,7 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
     const int first_channel = blockIdx.x * kWarps + warp;
 
     // Weight loads of the first channel go out before the activations are staged.
-    constexpr int kPre = 4;
+    constexpr int kPre = KPRE;
     int4 pre[GATEUP ? 2 : 1][kPre];
     if (first_channel < out_features) {
         const int4* row0 = reinterpret_cast<const int4*>(weight + (size_t)first_channel * in_features);
@@ -91,6 +94,13 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
             }
         }
     }
+
+    // Launched with programmatic stream serialisation: this grid may start while the one before
+    // it in the stream is still running.  Everything above touches only the weights; from here on
+    // the previous grid's output is read, so wait for it to complete (a no-op when the launch
+    // was an ordinary one), and let the grid after this one start its own weight loads.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // ---- stage activations --------------------------------------------------------
     if (NORM) {
@@ -211,13 +221,30 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
     }
 }
 
+// overlap of a GEMV's weight prefetch with the tail of the kernel before it (QWEN3_TTS_PDL=0 disables)
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("QWEN3_TTS_PDL");
+        return v == nullptr || *v != '0';
+    }();
+    return on;
+}
+
 constexpr int kMaxInFeatures = 8192;   // 8 rows x 8192 x bf16 = 128 KB of staged activations
 
 template <int ROWS, bool GATEUP, bool NORM>
 cudaError_t configure_one() {
-    return cudaFuncSetAttribute(gemv_rows_kernel<ROWS, GATEUP, NORM>,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                ROWS * kMaxInFeatures * static_cast<int>(sizeof(bf16)));
+    cudaError_t e = cudaFuncSetAttribute(gemv_rows_kernel<ROWS, GATEUP, NORM>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         ROWS * kMaxInFeatures * static_cast<int>(sizeof(bf16)));
+    if constexpr (ROWS == 1 && !GATEUP) {
+        if (e == cudaSuccess) {
+            e = cudaFuncSetAttribute(gemv_rows_kernel<ROWS, GATEUP, NORM, 12>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     ROWS * kMaxInFeatures * static_cast<int>(sizeof(bf16)));
+        }
+    }
+    return e;
 }
 
 template <bool GATEUP, bool NORM>
@@ -233,18 +260,31 @@ cudaError_t configure_rows() {
     return e;
 }
 
-template <int ROWS, bool GATEUP, bool NORM>
+template <int ROWS, bool GATEUP, bool NORM, int KPRE = 4>
 cudaError_t launch_one(const GemvArgs& a, const bf16* x, bf16* y, float* y32, bf16* norm_out,
                        bf16* resid, cudaStream_t stream) {
+    if constexpr (ROWS == 1 && !GATEUP && KPRE == 4) {
+        if (a.in_features > 2048) {
+            return launch_one<ROWS, GATEUP, NORM, 12>(a, x, y, y32, norm_out, resid, stream);
+        }
+    }
     const size_t smem = (size_t)ROWS * a.in_features * sizeof(bf16);
-    auto kernel = gemv_rows_kernel<ROWS, GATEUP, NORM>;
+    auto kernel = gemv_rows_kernel<ROWS, GATEUP, NORM, KPRE>;
     int grid = (a.out_features + kWarps - 1) / kWarps;
     const int cap = 148 * 8;
     if (grid > cap) grid = cap;
-    kernel<<<grid, kThreads, smem, stream>>>(a.w, a.scales, x, y, y32, a.norm_w, norm_out, a.bias,
-                                             resid, a.in_features, a.out_features, a.epilogue,
-                                             a.eps);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, a.w, a.scales, x, y, y32, a.norm_w, norm_out, a.bias, resid,
+                              a.in_features, a.out_features, a.epilogue, a.eps);
 }
 
 template <bool GATEUP, bool NORM>

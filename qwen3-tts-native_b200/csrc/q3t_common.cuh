@@ -46,6 +46,65 @@ __device__ __forceinline__ float warp_sum_xor(float v) {
     return v;
 }
 
+// ---- packed fp32 pairs (one instruction, two ordinary IEEE operations) -----------------------
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
+                                                   unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+// Two weight vectors (16 int8 each) of one lane against their activations: returns the two vector
+// sums, each the 16 sequential FMAs of the reference's dot product.
+// xs4 points at this lane's first 16-byte group; groups of one pair are 32 * 16 bytes apart and
+// hold {xA[i], xB[i], xA[i+1], xB[i+1]}.
+__device__ __forceinline__ void dot16_pair(const int4& wa, const int4& wb, const float4* xs4, float& sum_a,
+                                           float& sum_b) {
+    const unsigned long long bias = pack2(-8388736.0f, -8388736.0f);
+    unsigned long long sum = pack2(0.0f, 0.0f);
+    const uint32_t a[4] = {(uint32_t)wa.x ^ 0x80808080u, (uint32_t)wa.y ^ 0x80808080u,
+                           (uint32_t)wa.z ^ 0x80808080u, (uint32_t)wa.w ^ 0x80808080u};
+    const uint32_t b[4] = {(uint32_t)wb.x ^ 0x80808080u, (uint32_t)wb.y ^ 0x80808080u,
+                           (uint32_t)wb.z ^ 0x80808080u, (uint32_t)wb.w ^ 0x80808080u};
+#pragma unroll
+    for (int ip = 0; ip < 8; ++ip) {
+        const float4 xx = xs4[ip * kWarp];
+        const int q = ip >> 1;                 // word of the vector
+        const int e0 = (ip & 1) * 2;           // byte of the word
+        const unsigned long long w0 = add2(
+            pack2(__uint_as_float(__byte_perm(a[q], 0x4B000000u, 0x7650 + e0)),
+                  __uint_as_float(__byte_perm(b[q], 0x4B000000u, 0x7650 + e0))), bias);
+        const unsigned long long w1 = add2(
+            pack2(__uint_as_float(__byte_perm(a[q], 0x4B000000u, 0x7651 + e0)),
+                  __uint_as_float(__byte_perm(b[q], 0x4B000000u, 0x7651 + e0))), bias);
+        sum = fma2(w0, pack2(xx.x, xx.y), sum);
+        sum = fma2(w1, pack2(xx.z, xx.w), sum);
+    }
+    unpack2(sum, sum_a, sum_b);
+}
+
+
+// Where element e of an activation row goes in the staged fp32 layout that dot16_pair reads:
+// vector v = e / 16 belongs to lane v % 32, the lane's vectors j = v / 32 are paired (j, j + 1).
+__device__ __forceinline__ int paired_index(int e) {
+    const int vec = e >> 4, i = e & 15;
+    const int l = vec & 31, j = vec >> 5;
+    return ((((j >> 1) * 8 + (i >> 1)) * kWarp + l) << 2) + ((i & 1) << 1) + (j & 1);
+}
+
 // 128-bit streaming load that does not allocate in L1 (weights are read once).
 __device__ __forceinline__ int4 ld_stream(const void* p) {
     int4 v;
