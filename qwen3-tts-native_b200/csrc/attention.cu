@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
     constexpr int TPI = kWarp / LPT;       // tokens per warp iteration
     constexpr int ITERS = kWarpTokens / TPI;
 
+    pdl_wait();        // positions, q/k/v and the KV cache come from the kernels before this one
+    pdl_trigger();
     const int kvh = blockIdx.y;
     const int row = blockIdx.z;
     const int pos = a.positions[row];
@@ -491,11 +493,9 @@ cudaError_t launch_hd_g(const AttentionArgs& a, cudaStream_t stream) {
     const int units = a.units_per_cta > 0 ? a.units_per_cta : 1;
     const dim3 grid((a.max_splits + units - 1) / units, a.kv_heads, a.rows);
     if (a.kv.page_table != nullptr) {
-        decode_attention_kernel<HD, G, true><<<grid, kAttnThreads, 0, stream>>>(a);
-    } else {
-        decode_attention_kernel<HD, G, false><<<grid, kAttnThreads, 0, stream>>>(a);
+        return launch_pdl(decode_attention_kernel<HD, G, true>, grid, dim3(kAttnThreads), 0, stream, a);
     }
-    return cudaGetLastError();
+    return launch_pdl(decode_attention_kernel<HD, G, false>, grid, dim3(kAttnThreads), 0, stream, a);
 }
 
 template <int HD>

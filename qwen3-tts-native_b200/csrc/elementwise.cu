@@ -15,6 +15,8 @@ constexpr int kThreads = 256;
 __global__ void __launch_bounds__(kThreads)
 rms_norm_rows_kernel(const bf16* __restrict__ input, const bf16* __restrict__ weight,
                      bf16* __restrict__ output, int width, float eps) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float partial[kThreads];
     const bf16* xr = input + (size_t)blockIdx.x * width;
     bf16* yr = output + (size_t)blockIdx.x * width;
@@ -154,8 +156,8 @@ int blocks_for(int n) {
 cudaError_t launch_rms_norm_rows(const bf16* input, const bf16* weight, bf16* output, int rows,
                                  int width, float eps, cudaStream_t stream) {
     if (rows < 1 || width < 1) return cudaErrorInvalidValue;
-    rms_norm_rows_kernel<<<rows, kThreads, 0, stream>>>(input, weight, output, width, eps);
-    return cudaGetLastError();
+    return launch_pdl(rms_norm_rows_kernel, dim3(rows), dim3(kThreads), 0, stream, input, weight, output, width,
+                      eps);
 }
 
 cudaError_t launch_head_rms_norm_rows(bf16* values, const bf16* weight, int rows, int heads,

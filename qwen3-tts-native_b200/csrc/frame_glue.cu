@@ -13,6 +13,8 @@ namespace {
 constexpr int kThreads = 256;
 
 __global__ void frame_begin_kernel(const FrameTable* t, int rows) {
+    pdl_wait();
+    pdl_trigger();
     const int row = blockIdx.x * blockDim.x + threadIdx.x;
     if (row < rows) t->frame_tokens[row][0] = *t->sampled[row];
 }
@@ -20,6 +22,8 @@ __global__ void frame_begin_kernel(const FrameTable* t, int rows) {
 __global__ void __launch_bounds__(kThreads)
 predictor_input_kernel(const FrameTable* t, int p, const bf16* __restrict__ codec_embedding,
                        const bf16* const* predictor_embeddings, bf16* __restrict__ x, int width) {
+    pdl_wait();
+    pdl_trigger();
     const int row = blockIdx.x;
     const bf16* src;
     if (p == 0) {
@@ -46,6 +50,8 @@ talker_input_kernel(const FrameTable* t, const bf16* __restrict__ codec_embeddin
                     const bf16* const* predictor_embeddings,
                     const bf16* __restrict__ text_embedding, int text_vocabulary,
                     bf16* __restrict__ hidden, bf16* __restrict__ text_in, int width) {
+    pdl_wait();
+    pdl_trigger();
     const int row = blockIdx.x;
     const int* tokens = t->frame_tokens[row];
     __shared__ int tok[kCodebooks];
@@ -75,6 +81,8 @@ talker_input_kernel(const FrameTable* t, const bf16* __restrict__ codec_embeddin
 }
 
 __global__ void pack_codes_kernel(const FrameTable* t, int rows) {
+    pdl_wait();
+    pdl_trigger();
     const int row = blockIdx.x;
     const int i = threadIdx.x;
     if (row < rows && i < kCodebooks) {
@@ -87,6 +95,8 @@ __global__ void pack_codes_kernel(const FrameTable* t, int rows) {
 __global__ void __launch_bounds__(kThreads)
 frame_end_kernel(FrameTable* t, const bf16* __restrict__ normalized, int width,
                  int advance_position) {
+    pdl_wait();
+    pdl_trigger();
     const int row = blockIdx.x;
     const int4* s4 = reinterpret_cast<const int4*>(normalized + (size_t)row * width);
     int4* d4 = reinterpret_cast<int4*>(t->last_hidden[row]);
@@ -174,37 +184,32 @@ __global__ void advance_position_kernel(FrameTable* t) {
 }  // namespace
 
 cudaError_t launch_frame_begin(const FrameTable* table, int rows, cudaStream_t stream) {
-    frame_begin_kernel<<<1, kMaxRows, 0, stream>>>(table, rows);
-    return cudaGetLastError();
+    return launch_pdl(frame_begin_kernel, dim3(1), dim3(kMaxRows), 0, stream, table, rows);
 }
 
 cudaError_t launch_predictor_input(const FrameTable* table, int p, const bf16* codec_embedding,
                                    const bf16* const* predictor_embeddings, bf16* x, int width,
                                    int rows, cudaStream_t stream) {
-    predictor_input_kernel<<<rows, kThreads, 0, stream>>>(table, p, codec_embedding,
-                                                          predictor_embeddings, x, width);
-    return cudaGetLastError();
+    return launch_pdl(predictor_input_kernel, dim3(rows), dim3(kThreads), 0, stream, table, p, codec_embedding,
+                      predictor_embeddings, x, width);
 }
 
 cudaError_t launch_talker_input(const FrameTable* table, const bf16* codec_embedding,
                                 const bf16* const* predictor_embeddings, const bf16* text_embedding,
                                 int text_vocabulary, bf16* hidden, bf16* text_in, int width, int rows,
                                 cudaStream_t stream) {
-    talker_input_kernel<<<rows, kThreads, 0, stream>>>(table, codec_embedding, predictor_embeddings,
-                                                       text_embedding, text_vocabulary, hidden,
-                                                       text_in, width);
-    return cudaGetLastError();
+    return launch_pdl(talker_input_kernel, dim3(rows), dim3(kThreads), 0, stream, table, codec_embedding,
+                      predictor_embeddings, text_embedding, text_vocabulary, hidden, text_in, width);
 }
 
 cudaError_t launch_pack_codes(const FrameTable* table, int rows, cudaStream_t stream) {
-    pack_codes_kernel<<<rows, 32, 0, stream>>>(table, rows);
-    return cudaGetLastError();
+    return launch_pdl(pack_codes_kernel, dim3(rows), dim3(32), 0, stream, table, rows);
 }
 
 cudaError_t launch_frame_end(FrameTable* table, const bf16* normalized, int width, int rows,
                              int advance_position, cudaStream_t stream) {
-    frame_end_kernel<<<rows, kThreads, 0, stream>>>(table, normalized, width, advance_position);
-    return cudaGetLastError();
+    return launch_pdl(frame_end_kernel, dim3(rows), dim3(kThreads), 0, stream, table, normalized, width,
+                      advance_position);
 }
 
 cudaError_t launch_prompt_gather(const FrameTable* table, const int* text_ids,

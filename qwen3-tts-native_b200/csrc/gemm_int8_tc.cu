@@ -328,6 +328,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     if (tid == 0) TC_TRACE(1);
+    // The weight copies (warp 0) start at once: weights never depend on the kernel before this
+    // one.  Everyone else first waits for that kernel to complete (activations, residual).
+    pdl_trigger();
+    if (warp != 0) pdl_wait();
 
     if (warp == 0) {
         if (elect_one()) {
@@ -469,6 +473,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
 
     // ---- the K-slices of a channel tile live in the CTAs of one cluster; CTA s owns rows
     // [s * rows_share, (s + 1) * rows_share) and sums them over all slices in slice order ----------
+    if (warp == 0) pdl_wait();
     constexpr int kPerRow = GATEUP ? 64 : kTileN;
     const int c = tid % kPerRow;                       // kTcThreads is a multiple of kPerRow
     const int channel = tile * kPerRow + c;
@@ -625,13 +630,15 @@ cudaError_t launch_mt(const CUtensorMap& wm, const CUtensorMap& xm, const TcPara
     cfg.blockDim = dim3(kTcThreads, 1, 1);
     cfg.dynamicSmemBytes = tc_smem_bytes<MT, GATEUP>();
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)p.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, GATEUP>, wm, xm, p);
 }
 

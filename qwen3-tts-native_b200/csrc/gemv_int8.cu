@@ -99,8 +99,8 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
     // it in the stream is still running.  Everything above touches only the weights; from here on
     // the previous grid's output is read, so wait for it to complete (a no-op when the launch
     // was an ordinary one), and let the grid after this one start its own weight loads.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_wait();
+    pdl_trigger();
 
     // ---- stage activations --------------------------------------------------------
     if (NORM) {
@@ -221,15 +221,6 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
     }
 }
 
-// overlap of a GEMV's weight prefetch with the tail of the kernel before it (QWEN3_TTS_PDL=0 disables)
-bool pdl_enabled() {
-    static const bool on = [] {
-        const char* v = std::getenv("QWEN3_TTS_PDL");
-        return v == nullptr || *v != '0';
-    }();
-    return on;
-}
-
 constexpr int kMaxInFeatures = 8192;   // 8 rows x 8192 x bf16 = 128 KB of staged activations
 
 template <int ROWS, bool GATEUP, bool NORM>
@@ -312,6 +303,15 @@ cudaError_t configure_gemv_kernels() {
     if (e == cudaSuccess) e = configure_rows<true, false>();
     if (e == cudaSuccess) e = configure_rows<true, true>();
     return e;
+}
+
+// overlap of a kernel's preamble with the tail of the kernel before it
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("QWEN3_TTS_PDL");
+        return v == nullptr || *v != '0';
+    }();
+    return on;
 }
 
 cudaError_t launch_int8_gemm(const GemvArgs& a, cudaStream_t stream) {

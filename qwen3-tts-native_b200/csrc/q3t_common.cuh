@@ -46,6 +46,14 @@ __device__ __forceinline__ float warp_sum_xor(float v) {
     return v;
 }
 
+// ---- programmatic dependent launch --------------------------------------------------------
+// A kernel launched with programmatic stream serialisation may start while its predecessor in
+// the stream still runs.  pdl_wait() returns once the predecessor has completed and its writes
+// are visible (at once when the launch was an ordinary one); nothing the predecessor wrote may
+// be read before it.  pdl_trigger() lets the successor start its own preamble.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- packed fp32 pairs (one instruction, two ordinary IEEE operations) -----------------------
 __device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
     unsigned long long r;

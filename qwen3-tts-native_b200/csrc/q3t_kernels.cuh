@@ -40,6 +40,25 @@ struct GemvArgs {
     float eps = kRmsEps;
 };
 
+// Launch with programmatic stream serialisation (QWEN3_TTS_PDL=0 turns it into an ordinary
+// launch).  Only for kernels that call pdl_wait() before they read anything a predecessor wrote.
+bool pdl_enabled();
+template <typename... Params, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 // Dispatcher: 1..8 rows run the SIMT kernel; more rows run it in passes of 8 rows.
 cudaError_t launch_int8_gemm(const GemvArgs& args, cudaStream_t stream);
 cudaError_t launch_int8_gemm_simt(const GemvArgs& args, cudaStream_t stream);

@@ -296,6 +296,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const Sampl
 __global__ void __launch_bounds__(kSampleThreads)
 sample_table_kernel(const FrameTable* table, const bf16* logits, int logits_stride, int vocabulary,
                     int talker, int store_index, int mask_eos, int eos) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int row = blockIdx.x;
     const SamplingParams p = talker ? table->talker[row] : table->predictor[row];
@@ -375,7 +377,7 @@ cudaError_t launch_sample_table(const FrameTable* table, const bf16* logits, int
         || vocabulary > kMaxVocab) {
         return cudaErrorInvalidValue;
     }
-    sample_table_kernel<<<rows, kSampleThreads, kSampleSmem, stream>>>(
+    return launch_pdl(sample_table_kernel, dim3(rows), dim3(kSampleThreads), kSampleSmem, stream, 
         table, logits, logits_stride, vocabulary, talker, store_index, mask_eos, eos);
     return cudaGetLastError();
 }
