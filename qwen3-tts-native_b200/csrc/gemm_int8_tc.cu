@@ -294,6 +294,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     const int row_a = GATEUP ? tile * 64 : tile * kTileN;          // first W row of the tile
     const int row_b = N + tile * 64;                               // GATEUP: first row of the "up" half
 
+    // the channel this thread finishes in the K-slice sum, and its scales: asked for now, so that
+    // the (cold) loads are long back when the epilogue needs them
+    constexpr int kPerRow = GATEUP ? 64 : kTileN;
+    const int c = tid % kPerRow;                       // kTcThreads is a multiple of kPerRow
+    const int channel = tile * kPerRow + c;
+    float scale = 0.0f, scale_up = 0.0f;
+    if (channel < N) {
+        scale = p.scales[channel];
+        if (GATEUP) scale_up = p.scales[N + channel];
+    }
+
     if (tid == 0) TC_TRACE(0);
     if (tid == 0) TC_SPAN(0);
     Guard guard;
@@ -474,14 +485,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     // ---- the K-slices of a channel tile live in the CTAs of one cluster; CTA s owns rows
     // [s * rows_share, (s + 1) * rows_share) and sums them over all slices in slice order ----------
     if (warp == 0) pdl_wait();
-    constexpr int kPerRow = GATEUP ? 64 : kTileN;
-    const int c = tid % kPerRow;                       // kTcThreads is a multiple of kPerRow
-    const int channel = tile * kPerRow + c;
-    float scale = 0.0f, scale_up = 0.0f;
-    if (channel < N) {
-        scale = p.scales[channel];
-        if (GATEUP) scale_up = p.scales[N + channel];
-    }
     __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     if (tid == 0) TC_TRACE(57);
