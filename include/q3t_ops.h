@@ -91,6 +91,19 @@ QWEN3_TTS_API int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t inpu
                                               Qwen3TtsGemvBenchmark* output, char* error,
                                               size_t error_capacity);
 
+/* The reference host's per-frame call sequence as a compiled loop, for end-to-end timing without
+ * an interpreter between the calls: qwen3_tts_model_batch_next_frame_begin_v2 + one
+ * qwen3_tts_session_next_frame_finish_v2 per session (native_talker.rs:314-380), or
+ * qwen3_tts_session_next_frame when session_count is 1.  Uses only exported functions.
+ * wall_milliseconds: host clock around the loop; last_tokens: [session_count] next semantic tokens. */
+QWEN3_TTS_API int32_t q3t_host_pump_frames(Qwen3TtsModelHandle model, Qwen3TtsSessionHandle* sessions,
+                                           int32_t session_count, int32_t frames,
+                                           int32_t trailing_text_token_id,
+                                           Qwen3TtsSamplingConfig talker_sampling,
+                                           Qwen3TtsSamplingConfig predictor_sampling,
+                                           uint16_t* last_tokens, double* wall_milliseconds,
+                                           char* error, size_t error_capacity);
+
 /* A chain of 1..8 dependent batch-1 GEMVs (rows == 1, in_features a multiple of 1024 up to 6144)
  * in one persistent cooperative launch: op i+1 may read what op i wrote.  Bit-identical to issuing
  * the same descriptors one by one through q3t_launch_int8_gemm_ex.  Launches through this entry

@@ -102,7 +102,7 @@ EXPORTED_SYMBOLS = (
     "q3t_launch_int8_gemm_rows", "q3t_launch_int8_gemm_rows_add",
     "q3t_launch_int8_gate_up_silu_rows", "q3t_launch_int8_gemm_ex",
     "q3t_launch_quantize_weight_rows", "q3t_benchmark_int8_gemv", "q3t_launch_rms_norm_rows",
-    "q3t_launch_int8_gemv_chain", "q3t_benchmark_int8_gemv_chain",
+    "q3t_launch_int8_gemv_chain", "q3t_benchmark_int8_gemv_chain", "q3t_host_pump_frames",
     "q3t_launch_head_rms_norm_rows", "q3t_launch_rope_rows_at", "q3t_launch_kv_scatter_rows",
     "q3t_launch_bias_activation_rows", "q3t_launch_add_in_place", "q3t_launch_silu_gate",
     "q3t_launch_gather_embedding_rows", "q3t_launch_add_embedding_rows",
@@ -375,6 +375,28 @@ class NativeTalkerModel:
             copy = DeviceFrameViewV2C.from_buffer_copy(v)
             out.append(PendingTalkerFrame(s, copy))
         return out
+
+    def host_pump_frames(self, sessions: Sequence["NativeTalkerSession"], frames: int,
+                         trailing_text_id: int = 0) -> float:
+        """The reference host's per-frame ABI call sequence as a compiled loop; returns wall ms."""
+        n = len(sessions)
+        handles = (C.c_void_p * n)(*[s._handle for s in sessions])
+        last = (C.c_uint16 * n)()
+        wall = C.c_double(0.0)
+        err = C.create_string_buffer(_ERR_CAP)
+        lib = library()
+        lib.q3t_host_pump_frames.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32,
+                                             SamplingConfigC, SamplingConfigC, C.POINTER(C.c_uint16),
+                                             C.POINTER(C.c_double), C.c_char_p, C.c_size_t]
+        lib.q3t_host_pump_frames.restype = C.c_int32
+        _check(lib.q3t_host_pump_frames(self._handle, handles, n, frames, trailing_text_id,
+                                        sessions[0].talker_sampling.to_c(), sessions[0].predictor_sampling.to_c(),
+                                        last, C.byref(wall), err, _ERR_CAP), err)
+        for s, tok in zip(sessions, last):
+            s.current_semantic_token = int(tok)
+            s.frames_emitted += frames
+            s.ended = s.current_semantic_token == EOS
+        return float(wall.value)
 
     def run_frames(self, sessions: Sequence["NativeTalkerSession"], frames: int,
                    trailing_text_id: int = 0, want_frame_ms: bool = False):

@@ -286,6 +286,28 @@ def test_run_frames_equals_stepping(q3t, model):
     b.close()
 
 
+def test_host_pump_equals_stepping(q3t, model):
+    """The compiled host loop over the exported ABI produces what the same calls made one by one do."""
+    for n in (1, 3):
+        a = [start(q3t, model, 900 + i) for i in range(n)]
+        b = [start(q3t, model, 900 + i) for i in range(n)]
+        for f in range(3):
+            if n == 1:
+                a[0].next_frame(9)
+            else:
+                for p in model.batch_begin_device_frames(a, [9] * n):
+                    p.finish_without_consumer()
+        wall_ms = model.host_pump_frames(b, 3, trailing_text_id=9)
+        assert wall_ms > 0
+        for x, y in zip(a, b):
+            hx, tx, rx = x.read_state()
+            hy, ty, ry = y.read_state()
+            assert np.array_equal(tx, ty) and rx == ry and np.array_equal(hx, hy)
+            assert x.current_semantic_token == y.current_semantic_token
+        for s_ in a + b:
+            s_.close()
+
+
 def test_device_frame_lease_protocol(q3t, model):
     s = start(q3t, model, 55)
     err = C.create_string_buffer(256)
