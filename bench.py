@@ -5,7 +5,7 @@
 
 One "step" is one codec frame (16 code-predictor positions + one talker decode step) for
 every session of the batch.  Workload: 64 concurrent sessions per GPU with ragged KV lengths
-uniform in [64, 2048] over a paged bf16 KV cache (BASELINE.json configs[3]/[4] shapes),
+uniform in [64, 2048] over a paged bf16 KV cache (the batched configurations of the benchmark spec),
 synthetic int8 per-channel weights of the real architecture, sampling T=0.9 / top-k 50 /
 top-p 0.9.  Prints ONE JSON line:
 
@@ -14,7 +14,7 @@ top-p 0.9.  Prints ONE JSON line:
   e2e        the same metric through the drop-in C ABI the reference's host calls
              (qwen3_tts_model_batch_next_frame_begin_v2 + ..._finish_v2 per frame) with a host
              round trip per frame: frame table up, next tokens and codes down
-  b1         the B=1 numbers (one session at KV length 512, BASELINE.json configs[1]/[2])
+  b1         the B=1 numbers (one session at KV length 512, the single-session configurations of the benchmark spec)
   roofline   the batch-1 int8 GEMV (configs[0], 2048 -> 6144) against the measured HBM peak
   cpu_baseline  the oracle's CPU restatement timed on this host's cores on a bounded sample
 

@@ -1,4 +1,4 @@
-"""GPU parity of the split-KV decode attention (SURVEY rows A1, A2, K1, N2, R1 fused).
+"""GPU parity of the split-KV decode attention (stand-alone and with head-norm, RoPE and KV append fused).
 
 Semantic reference: the reference's fast kernel (fp32 scores).  The split-KV kernel sums in a
 different order, so the comparison is the north-star tolerance: the fp32 value before the final

@@ -1,4 +1,4 @@
-"""GPU parity of the int8 weight-only GEMV / skinny GEMM through the
+"""GPU parity of the int8 weight-only GEMV / skinny GEMM (plain, residual, gate/up/SiLU and norm-fused forms) through the
 operator-level C ABI, against the CPU oracle, against fp64 truth, and against the reference's
 own kernels compiled for sm_100a when oracle/_ref is present.
 

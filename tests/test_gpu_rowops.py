@@ -1,4 +1,4 @@
-"""GPU parity of the row operators: RMSNorm, per-head
+"""GPU parity of the row operators (norms, RoPE, KV append, elementwise glue): RMSNorm, per-head
 RMSNorm, RoPE, KV append, bias/activation, SiLU gate, residual add, embedding gather/add,
 plus the reference's four closed-form known-answer cases run through this library.
 

@@ -1,4 +1,4 @@
-"""GPU parity of the sampler: token IDs and the post-call RNG state must be
+"""GPU parity of the sampler (temperature / top-k / top-p / repetition penalty / EOS suppression): token IDs and the post-call RNG state must be
 bit-exact given identical logits, history and seed -- against the CPU oracle and, when
 oracle/_ref is present, against the reference's own sample_logits_kernel on the same GPU."""
 import itertools
@@ -63,7 +63,7 @@ def test_config_defaults_paths(orc, ops):
     """The three configurations the product uses, many seeds each."""
     rng = np.random.default_rng(1)
     configs = [
-        (3072, True, dict(do_sample=1, top_k=50, top_p=0.9, temperature=0.9, penalty=1.0)),    # BASELINE cfg 1
+        (3072, True, dict(do_sample=1, top_k=50, top_p=0.9, temperature=0.9, penalty=1.0)),    # the talker configuration of the benchmark spec
         (3072, True, dict(do_sample=1, top_k=50, top_p=1.0, temperature=0.9, penalty=1.05)),   # official talker
         (2048, False, dict(do_sample=1, top_k=50, top_p=1.0, temperature=0.9, penalty=1.0)),   # official predictor
     ]
