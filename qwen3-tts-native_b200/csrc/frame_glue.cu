@@ -54,21 +54,34 @@ talker_input_kernel(const FrameTable* t, const bf16* __restrict__ codec_embeddin
     pdl_trigger();
     const int row = blockIdx.x;
     const int* tokens = t->frame_tokens[row];
-    __shared__ int tok[kCodebooks];
-    if (threadIdx.x < kCodebooks) tok[threadIdx.x] = tokens[threadIdx.x];
+    // the sixteen embedding rows of this frame (null: token out of range, nothing is added, as
+    // in the reference's gather)
+    __shared__ const bf16* rows_of[kCodebooks];
+    if (threadIdx.x < kCodebooks) {
+        const int r = threadIdx.x;
+        const int token = tokens[r];
+        const bf16* base = nullptr;
+        if (r == 0) {
+            if (token >= 0 && token < kMaxVocab) base = codec_embedding + (size_t)token * width;
+        } else if (token >= 0 && token < kPredictorVocab) {
+            base = predictor_embeddings[r - 1] + (size_t)token * width;
+        }
+        rows_of[r] = base;
+    }
     __syncthreads();
     for (int i = threadIdx.x; i < width; i += kThreads) {
-        // an out-of-range token leaves the previous content in place, as the reference's
-        // gather does
-        float acc = (tok[0] >= 0 && tok[0] < kMaxVocab)
-            ? bf2f(codec_embedding[(size_t)tok[0] * width + i])
-            : bf2f(hidden[(size_t)row * width + i]);
+        // all sixteen loads go out together; the sum is then formed in codebook order with the
+        // reference's rounding after every addition
+        float v[kCodebooks];
 #pragma unroll
-        for (int r = 0; r < kCodebooks - 1; ++r) {
-            const int token = tok[r + 1];
-            if (token >= 0 && token < kPredictorVocab) {
-                acc = rbf(acc + bf2f(predictor_embeddings[r][(size_t)token * width + i]));
-            }
+        for (int r = 0; r < kCodebooks; ++r) {
+            const bf16* base = rows_of[r];
+            v[r] = base != nullptr ? bf2f(base[i]) : 0.0f;
+        }
+        float acc = rows_of[0] != nullptr ? v[0] : bf2f(hidden[(size_t)row * width + i]);
+#pragma unroll
+        for (int r = 1; r < kCodebooks; ++r) {
+            if (rows_of[r] != nullptr) acc = rbf(acc + v[r]);
         }
         hidden[(size_t)row * width + i] = f2bf(acc);
     }
