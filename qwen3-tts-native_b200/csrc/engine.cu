@@ -690,6 +690,7 @@ Session::~Session() {
 }
 
 void Session::reset(uint64_t seed) {
+    own_stream_busy_ = true;
     check_cuda(cudaSetDevice(device_), "cudaSetDevice(reset)");
     if (frame_in_flight_) throw std::runtime_error("cannot reset while a device frame lease is in flight");
     position_ = 0;
@@ -793,6 +794,7 @@ void Session::launch_frame(Workspace& w, Model& m, Session** s, int n, bool uplo
     int max_length = 1;
     for (int i = 0; i < n; ++i) max_length = std::max(max_length, w.host_table->position[i] + 1);
     const int splits = split_bucket(max_length);
+    ++w.frame_serial;
     if (w.option_epoch != m.option_epoch) {
         check_cuda(cudaStreamSynchronize(w.stream), "cudaStreamSynchronize(options)");
         w.destroy_graphs();
@@ -847,6 +849,7 @@ uint64_t Session::take_lease(Workspace* w, bool host_codes) {
     pending_lease_ = lease;
     pending_position_ = static_cast<uint32_t>(position_);
     pending_workspace_ = w;
+    pending_frame_serial_ = w != nullptr ? w->frame_serial + 1 : 0;    // the frame about to be launched
     return lease;
 }
 
@@ -863,6 +866,7 @@ FrameView Session::begin_frame(uint16_t semantic_token, int trailing_text, const
     check_cuda(cudaSetDevice(device_), "cudaSetDevice(begin frame)");
     validate_begin(semantic_token, trailing_text, talker, predictor);
     Workspace& w = *solo_;
+    own_stream_busy_ = true;
     const uint64_t lease = take_lease(&w, host_codes);
     try {
         check_cuda(cudaEventSynchronize(w.table_uploaded), "cudaEventSynchronize(table)");
@@ -911,8 +915,10 @@ void Session::batch_begin(Model* model, Session** s, int n, const int* trailing_
         }
         // order the batch stream after each session's earlier work
         for (int i = 0; i < n; ++i) {
+            if (!s[i]->own_stream_busy_) continue;      // nothing of its own since the last lockstep frame
             check_cuda(cudaEventRecord(w.join_events[i], s[i]->stream_), "cudaEventRecord(join)");
             check_cuda(cudaStreamWaitEvent(w.stream, w.join_events[i], 0), "cudaStreamWaitEvent(join)");
+            s[i]->own_stream_busy_ = false;
         }
         launch_frame(w, *model, s, n, true, true);
         for (int i = 0; i < n; ++i) {
@@ -945,6 +951,7 @@ FrameResult Session::finish_frame(uint64_t lease_id, cudaEvent_t consumer_done) 
     }
     if (consumer_done != nullptr) {
         check_cuda(cudaStreamWaitEvent(stream_, consumer_done, 0), "cudaStreamWaitEvent(consumer done)");
+        own_stream_busy_ = true;
     }
     check_cuda(cudaEventSynchronize(semantic_ready_), "cudaEventSynchronize(semantic ready)");
     ++host_sync_count;
@@ -955,13 +962,20 @@ FrameResult Session::finish_frame(uint64_t lease_id, cudaEvent_t consumer_done) 
     FrameResult r{};
     r.talker_position = pending_position_;
     Workspace* w = pending_workspace_;
-    if (w == nullptr
-        || cudaEventElapsedTime(&r.predictor_ms, w->predictor_start, w->predictor_stop) != cudaSuccess
-        || cudaEventElapsedTime(&r.talker_ms, w->talker_start, w->talker_stop) != cudaSuccess) {
+    if (w != nullptr && w->timed_frame == pending_frame_serial_ && pending_frame_serial_ != 0) {
+        r.predictor_ms = w->timed_predictor_ms;      // a sibling of this lockstep frame already asked
+        r.talker_ms = w->timed_talker_ms;
+    } else if (w == nullptr || w->frame_serial != pending_frame_serial_
+               || cudaEventElapsedTime(&r.predictor_ms, w->predictor_start, w->predictor_stop) != cudaSuccess
+               || cudaEventElapsedTime(&r.talker_ms, w->talker_start, w->talker_stop) != cudaSuccess) {
         // a later frame of a shared workspace has re-recorded the timing events
         cudaGetLastError();
         r.predictor_ms = 0.0f;
         r.talker_ms = 0.0f;
+    } else {
+        w->timed_frame = pending_frame_serial_;
+        w->timed_predictor_ms = r.predictor_ms;
+        w->timed_talker_ms = r.talker_ms;
     }
     if (pending_host_codes_) std::copy_n(h_codes_, kCodebooks, r.codes);
     r.next_semantic = static_cast<uint16_t>(next);
@@ -978,6 +992,7 @@ FrameResult Session::finish_frame(uint64_t lease_id, cudaEvent_t consumer_done) 
 
 void Session::prefill(const int32_t* text_ids, const int32_t* codec_ids, int count,
                       const SamplingParams& sampling, uint16_t* first_token, float* gpu_ms) {
+    own_stream_busy_ = true;
     check_cuda(cudaSetDevice(device_), "cudaSetDevice(prefill)");
     if (poisoned_) throw std::runtime_error("talker session is poisoned and must be destroyed");
     if (frame_in_flight_) throw std::runtime_error("cannot prefill while a device frame lease is in flight");
@@ -1125,6 +1140,7 @@ void Session::run_frames(Model* model, Session** s, int n, int frames, int trail
 }
 
 void Session::synthetic_prefill(int position, uint64_t seed) {
+    own_stream_busy_ = true;
     check_cuda(cudaSetDevice(device_), "cudaSetDevice(synthetic prefill)");
     if (poisoned_) throw std::runtime_error("talker session is poisoned and must be destroyed");
     if (frame_in_flight_) throw std::runtime_error("a device frame lease is in flight");

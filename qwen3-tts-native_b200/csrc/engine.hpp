@@ -131,6 +131,10 @@ struct Workspace {
     };
     std::map<std::pair<int, int>, Graphs> graphs;   // (rows, talker splits) -> graphs
     cudaEvent_t predictor_start = nullptr, predictor_stop = nullptr;
+    // frames launched on this workspace, and the GPU times of the frame `timed_frame` (every
+    // session of a lockstep frame reports the same two numbers: they are read from the events once)
+    uint64_t frame_serial = 0, timed_frame = 0;
+    float timed_predictor_ms = 0.0f, timed_talker_ms = 0.0f;
     cudaEvent_t talker_start = nullptr, talker_stop = nullptr;
     cudaEvent_t table_uploaded = nullptr;   // the pinned host table may be rewritten after this
     std::array<cudaEvent_t, kMaxRows> join_events{};
@@ -286,6 +290,10 @@ private:
     uint64_t pending_lease_ = 0;
     uint32_t pending_position_ = 0;
     Workspace* pending_workspace_ = nullptr;   // whose timing events belong to the pending frame
+    uint64_t pending_frame_serial_ = 0;
+    // true while this session's own stream may hold work a lockstep frame has to be ordered after
+    // (prompt, solo frame, reset, a consumer's event); lockstep frames themselves leave it false
+    bool own_stream_busy_ = true;
     cudaStream_t stream_ = nullptr;
     cudaEvent_t codes_ready_ = nullptr, semantic_ready_ = nullptr;
     std::unique_ptr<Workspace> solo_;
