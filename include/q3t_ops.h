@@ -246,7 +246,9 @@ QWEN3_TTS_API int32_t q3t_launch_sample_logits_at(
  * "batch_host_codes" (1: lockstep batches also mirror each frame's 16 codes to host memory),
  * "tc_min_rows" (process-wide: projections with at least this many rows run on the tensor
  * cores, default 9; 65 keeps every row count on the SIMT kernels, whose results do not depend on
- * the batch size). */
+ * the batch size), "prefill_chunk" (prompt positions per decoder pass, 1..64, default 64: a
+ * prompt runs as the rows of skinny GEMMs instead of position by position (talker.cu:2750-3249
+ * is the reference's prompt path); 1 restores the position-by-position path). */
 QWEN3_TTS_API int32_t q3t_model_set_option(Qwen3TtsModelHandle model, const char* key,
                                            int32_t value, char* error, size_t error_capacity);
 

@@ -939,6 +939,8 @@ int32_t q3t_model_set_option(Qwen3TtsModelHandle model, const char* key, int32_t
             m->use_graphs = value != 0;
         } else if (std::strcmp(key, "batch_host_codes") == 0) {
             m->batch_host_codes = value != 0;
+        } else if (std::strcmp(key, "prefill_chunk") == 0) {
+            m->prefill_chunk = value < 1 ? 1 : (value > kMaxRows ? kMaxRows : value);
         } else if (std::strcmp(key, "tc_min_rows") == 0) {
             set_tc_min_rows(value);     // process-wide: rows at or above this use the tensor cores
         } else {

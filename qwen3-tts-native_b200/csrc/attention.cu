@@ -101,7 +101,8 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
             // warps 0..G-1: query heads; warp G%4: the new key (last split only)
             for (int job = warp; job <= G; job += kAttnWarps) {
                 const bool is_key = job == G;
-                if (is_key && split_end != nsplits) continue;
+                if (is_key && (split_end != nsplits || a.append_mode == 2)) continue;
+                if (!is_key && a.append_mode == 1) continue;
                 const bf16* src = is_key ? a.k_new + (size_t)row * kn_stride + (size_t)kvh * HD
                                          : a.q + (size_t)row * q_stride + (size_t)(kvh * G + job) * HD;
                 const bf16* nw = is_key ? a.k_norm_w : a.q_norm_w;
@@ -163,6 +164,7 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
         }
     }
     __syncthreads();   // qs ready; this CTA's K/V append is visible to its own loads
+    if (a.fused && a.append_mode == 1) return;
 
     const int sub = lane / LPT;
     const int j8 = (lane % LPT) * 8;

@@ -121,6 +121,7 @@ Workspace::Workspace(int capacity_, int device_) : capacity(capacity_), device(d
     talker_pages = DeviceBuffer(c * kMaxPagesPerRow * sizeof(int));
     predictor_pages = DeviceBuffer(c * sizeof(int));
     predictor_positions = DeviceBuffer((size_t)kPredictorSequence * kMaxRows * sizeof(int));
+    prompt_positions = DeviceBuffer((size_t)kMaxRows * sizeof(int));
     counters = DeviceBuffer(c * 16 * sizeof(unsigned int));
     try {
         check_cuda(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreate");
@@ -406,13 +407,19 @@ Workspace& Model::batch_workspace() {
     return *batch_;
 }
 
+Workspace& Model::prefill_workspace() {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!prefill_) prefill_.reset(new Workspace(kMaxRows, device_));
+    return *prefill_;
+}
+
 // ------------------------------------------------------------------ frame enqueue
 
 namespace {
 
 void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWeights>& layers,
                     const uint32_t* rope_table, const KvPool& pool, const int* page_table, int table_stride,
-                    const int* positions, int n, int splits, cudaStream_t s) {
+                    const int* positions, int n, int splits, cudaStream_t s, bool shared_cache = false) {
     const int qkv_width = d.q_width + 2 * d.kv_width;
     for (size_t l = 0; l < layers.size(); ++l) {
         const LayerWeights& lw = layers[l];
@@ -437,6 +444,13 @@ void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWei
         a.rows = n; a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.head_dim = d.head_dim;
         a.max_splits = splits; a.fused = 1;
         a.rope_table = rope_table; a.rope_positions = Model::kRopePositions;
+        if (shared_cache) {
+            // the rows are consecutive positions of one session: every row's K/V goes into the
+            // cache first, then every row attends up to its own position
+            a.append_mode = 1;
+            check_cuda(launch_decode_attention(a, s), "prompt KV append");
+            a.append_mode = 2;
+        }
         check_cuda(launch_decode_attention(a, s), "decode attention");
 
         GemvArgs o;
@@ -551,6 +565,20 @@ void enqueue_prompt_step(Workspace& w, Model& m, const int* text_ids, const int*
     enqueue_layers(w, m.talker, m.talker_layers, m.talker_rope, *m.talker_pool, w.talker_pages.as<int>(),
                    Workspace::kMaxPagesPerRow, table->position, 1, splits, s);
     check_cuda(launch_advance_position(table, s), "advance position");
+}
+
+// prompt positions base .. base + rows - 1 of row 0's session as the rows of one decoder pass
+void enqueue_prompt_chunk(Workspace& w, Model& m, const int* text_ids, const int* codec_ids, int base,
+                          int rows, int splits, cudaStream_t s) {
+    const int H = m.talker.hidden;
+    check_cuda(launch_prompt_rows(text_ids, codec_ids, base, rows, m.text_embedding, kTextVocab,
+                                  w.x_in.as<bf16>(), w.prompt_positions.as<int>(), H, s), "prompt rows");
+    enqueue_text_projection(w, m, rows, false, s);
+    check_cuda(launch_prompt_combine_rows(text_ids, codec_ids, base, rows, m.codec_embedding, kTalkerVocab,
+                                          w.hidden.as<bf16>(), H, s), "prompt combine");
+    // page-table stride 0: every row reads and writes the cache of the session bound to row 0
+    enqueue_layers(w, m.talker, m.talker_layers, m.talker_rope, *m.talker_pool, w.talker_pages.as<int>(), 0,
+                   w.prompt_positions.as<int>(), rows, splits, s, true);
 }
 
 int count_kernel_nodes(cudaGraph_t graph) {
@@ -1009,8 +1037,15 @@ void Session::prefill(const int32_t* text_ids, const int32_t* codec_ids, int cou
         }
     }
     validate_sampling_params(sampling);
-    Workspace& w = *solo_;
     Model& m = *model_;
+    // A prompt runs as chunks of up to prefill_chunk positions per decoder pass (the rows of a
+    // skinny GEMM) on the model's prompt workspace, one prompt at a time; with prefill_chunk = 1,
+    // or a prompt of one position, it runs position by position on the session's own workspace.
+    const int chunk = std::min(std::max(m.prefill_chunk, 1), kMaxRows);
+    const bool chunked = chunk > 1 && count > 1;
+    std::unique_lock<std::mutex> one_prompt(m.prefill_mutex, std::defer_lock);
+    if (chunked) one_prompt.lock();
+    Workspace& w = chunked ? m.prefill_workspace() : *solo_;
     position_ = 0;
     generated_ = 0;
     try {
@@ -1031,9 +1066,22 @@ void Session::prefill(const int32_t* text_ids, const int32_t* codec_ids, int cou
                                    cudaMemcpyHostToDevice, w.stream), "upload frame table");
         check_cuda(cudaEventRecord(w.table_uploaded, w.stream), "cudaEventRecord(table)");
         check_cuda(cudaEventRecord(w.talker_start, w.stream), "cudaEventRecord");
-        // The prompt ids live in a buffer of this call, so the captured step graph is rebuilt
-        // per prefill; capture costs far less than the steps it replays.
-        if (m.use_graphs) {
+        if (chunked) {
+            int last_rows = 0;
+            for (int base = 0; base < count; base += chunk) {
+                last_rows = std::min(chunk, count - base);
+                enqueue_prompt_chunk(w, m, d_text, d_codec, base, last_rows, splits, w.stream);
+            }
+            if (last_rows > 1) {
+                // the head and the sampler read row 0: bring the last position's hidden state there
+                const size_t row_bytes = (size_t)m.talker.hidden * sizeof(bf16);
+                check_cuda(cudaMemcpyAsync(w.hidden.as<bf16>(),
+                                           w.hidden.as<bf16>() + (size_t)(last_rows - 1) * m.talker.hidden,
+                                           row_bytes, cudaMemcpyDeviceToDevice, w.stream), "last prompt row");
+            }
+        } else if (m.use_graphs) {
+            // The prompt ids live in a buffer of this call, so the captured step graph is rebuilt
+            // per prefill; capture costs far less than the steps it replays.
             cudaGraphExec_t step = capture(w.stream, [&] {
                 enqueue_prompt_step(w, m, d_text, d_codec, splits, w.stream);
             });

@@ -118,6 +118,7 @@ struct Workspace {
     DeviceBuffer predictor_pages;    // [capacity][1]
     int* host_pages = nullptr;       // pinned staging for the two page tables
     DeviceBuffer predictor_positions;   // [16][kMaxRows], slot p filled with p
+    DeviceBuffer prompt_positions;      // [kMaxRows], positions of the rows of a prompt chunk
     DeviceBuffer scratch;
     DeviceBuffer counters;
     int scratch_splits = 0;
@@ -154,6 +155,9 @@ public:
     bool finalized() const { return finalized_; }
     int device() const { return device_; }
     Workspace& batch_workspace();
+    Workspace& prefill_workspace();     // rows of a prompt chunk; one prompt at a time (prefill_mutex)
+    std::mutex prefill_mutex;
+    int prefill_chunk = kMaxRows;       // prompt positions per pass (1: one position at a time)
     Workspace* batch_workspace_if_any() {
         std::lock_guard<std::mutex> lock(mutex);
         return batch_.get();
@@ -204,7 +208,7 @@ private:
     std::vector<DeviceBuffer> storage_;   // every resident tensor (int8 rows, scales, bf16)
     DeviceBuffer staging_, embedding_ptrs_, talker_rope_, predictor_rope_;
     size_t staging_bytes_ = 0;
-    std::unique_ptr<Workspace> batch_;
+    std::unique_ptr<Workspace> batch_, prefill_;
 };
 
 struct FrameResult {

@@ -154,6 +154,41 @@ prompt_combine_kernel(const FrameTable* t, const int* __restrict__ text_ids,
     }
 }
 
+// ---- a chunk of prompt positions as the rows of one pass ------------------------------------------
+// Row r is prompt position base + r: the text embedding row goes to text_in (left as it is when
+// the position has no text, as in the single-position kernel) and the position to positions[r].
+__global__ void __launch_bounds__(kThreads)
+prompt_rows_kernel(const int* __restrict__ text_ids, const int* __restrict__ codec_ids, int base,
+                   const bf16* __restrict__ text_embedding, int text_vocabulary,
+                   bf16* __restrict__ text_in, int* __restrict__ positions, int width) {
+    const int row = blockIdx.x;
+    if (threadIdx.x == 0) positions[row] = base + row;
+    const int text = text_ids[base + row];
+    if (text < 0 || text >= text_vocabulary) return;
+    const int4* s4 = reinterpret_cast<const int4*>(text_embedding + (size_t)text * width);
+    int4* d4 = reinterpret_cast<int4*>(text_in + (size_t)row * width);
+    for (int i = threadIdx.x; i < width / 8; i += kThreads) d4[i] = s4[i];
+    (void)codec_ids;
+}
+
+// text part (or zeros) plus the codec embedding, one rounded add, per row (talker.cu:2721-2748)
+__global__ void __launch_bounds__(kThreads)
+prompt_combine_rows_kernel(const int* __restrict__ text_ids, const int* __restrict__ codec_ids, int base,
+                           const bf16* __restrict__ codec_embedding, int codec_vocabulary,
+                           bf16* __restrict__ hidden, int width) {
+    const int row = blockIdx.x;
+    const int text = text_ids[base + row];
+    const int codec = codec_ids[base + row];
+    bf16* h = hidden + (size_t)row * width;
+    for (int i = threadIdx.x; i < width; i += kThreads) {
+        float v = text >= 0 ? bf2f(h[i]) : 0.0f;
+        if (codec >= 0 && codec < codec_vocabulary) {
+            v = rbf(v + bf2f(codec_embedding[(size_t)codec * width + i]));
+        }
+        h[i] = f2bf(v);
+    }
+}
+
 // ---- benchmark harness: seeded pseudo-random N(0,1) fills ------------------------------------
 
 __device__ __forceinline__ float hashed_normal(unsigned long long index, unsigned long long seed) {
@@ -238,6 +273,24 @@ cudaError_t launch_prompt_combine(const FrameTable* table, const int* text_ids, 
                                   int width, cudaStream_t stream) {
     prompt_combine_kernel<<<4, kThreads, 0, stream>>>(table, text_ids, codec_ids, codec_embedding,
                                                       codec_vocabulary, hidden, width);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prompt_rows(const int* text_ids, const int* codec_ids, int base, int rows,
+                               const bf16* text_embedding, int text_vocabulary, bf16* text_in,
+                               int* positions, int width, cudaStream_t stream) {
+    if (rows < 1 || rows > kMaxRows) return cudaErrorInvalidValue;
+    prompt_rows_kernel<<<rows, kThreads, 0, stream>>>(text_ids, codec_ids, base, text_embedding,
+                                                      text_vocabulary, text_in, positions, width);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prompt_combine_rows(const int* text_ids, const int* codec_ids, int base, int rows,
+                                       const bf16* codec_embedding, int codec_vocabulary, bf16* hidden,
+                                       int width, cudaStream_t stream) {
+    if (rows < 1 || rows > kMaxRows) return cudaErrorInvalidValue;
+    prompt_combine_rows_kernel<<<rows, kThreads, 0, stream>>>(text_ids, codec_ids, base, codec_embedding,
+                                                              codec_vocabulary, hidden, width);
     return cudaGetLastError();
 }
 

@@ -144,6 +144,9 @@ struct AttentionArgs {
     int head_dim = 0;                   // 64 or 128 (32 allowed when not fused)
     int max_splits = 0;                 // grid.x; >= ceil(max length / kAttnChunk)
     int fused = 0;                      // 1: head-norm + RoPE on q/k_new, append k/v at position
+    int append_mode = 0;                // fused only.  0: append, then attend (decode).  1: append only.
+                                        // 2: attend only.  Rows that share one cache (a prompt chunk)
+                                        // need every row's K/V in place before any row attends: 1, then 2.
     int units_per_cta = 0;              // splits one CTA walks (0: chosen from the grid size); no effect on results
     float eps = kRmsEps;
     float theta = kRopeTheta;
@@ -254,6 +257,13 @@ cudaError_t launch_fill_kv_pages(bf16* const* slabs, int slab_shift, long long p
                                  unsigned long long seed, cudaStream_t stream);
 // position[0] += 1 (prompt rows advance one KV slot per step)
 cudaError_t launch_advance_position(FrameTable* table, cudaStream_t stream);
+// prompt positions base .. base + rows - 1 as rows of one pass (chunked prefill)
+cudaError_t launch_prompt_rows(const int* text_ids, const int* codec_ids, int base, int rows,
+                               const bf16* text_embedding, int text_vocabulary, bf16* text_in,
+                               int* positions, int width, cudaStream_t stream);
+cudaError_t launch_prompt_combine_rows(const int* text_ids, const int* codec_ids, int base, int rows,
+                                       const bf16* codec_embedding, int codec_vocabulary, bf16* hidden,
+                                       int width, cudaStream_t stream);
 
 cudaError_t launch_pack_frame_codes_rows(const int* const* tokens, unsigned short* const* codes,
                                          int rows, cudaStream_t stream);

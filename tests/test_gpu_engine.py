@@ -286,6 +286,47 @@ def test_run_frames_equals_stepping(q3t, model):
     b.close()
 
 
+def test_chunked_prompt_equals_position_by_position(q3t, orc, model):
+    """A prompt run as rows of one decoder pass (64 positions per pass) leaves the session where the
+    position-by-position path leaves it: bit for bit while every GEMM stays on the SIMT kernels,
+    and within bf16 noise when the 9+ row passes go to the tensor cores."""
+    rng = np.random.default_rng(5)
+    n = 75                                  # two passes: 64 + 11 rows
+    text = [int(t) for t in rng.integers(0, 1000, size=n)]
+    codec = [int(c) if i % 3 else -1 for i, c in enumerate(rng.integers(0, 2048, size=n))]
+    text = [t if i % 5 else -1 for i, t in enumerate(text)]
+    text[0], codec[0] = 17, 5               # every position needs text or codec
+    for i in range(n):
+        if text[i] < 0 and codec[i] < 0:
+            codec[i] = 7
+
+    def run(chunk, tc_min_rows):
+        model.set_option("prefill_chunk", chunk)
+        model.set_option("tc_min_rows", tc_min_rows)
+        try:
+            s = start(q3t, model, 31, max_seq=128, prompt=(text, codec))
+            first = s.current_semantic_token
+            hidden, _, rng_state = s.read_state()
+            frames = [s.next_frame(3).codes for _ in range(2)]
+            s.close()
+            return first, hidden, rng_state, frames
+        finally:
+            model.set_option("prefill_chunk", 64)
+            model.set_option("tc_min_rows", 9)
+
+    one = run(1, 65)
+    rows = run(64, 65)
+    assert rows[0] == one[0] and rows[2] == one[2]
+    assert np.array_equal(rows[1], one[1])
+    assert rows[3] == one[3]                # the KV cache they left behind is the same too
+    tc = run(64, 9)
+    again = run(64, 9)
+    assert tc[0] == again[0] and np.array_equal(tc[1], again[1]) and tc[3] == again[3]
+    a, b = orc.from_bf16(tc[1]).ravel(), orc.from_bf16(one[1]).ravel()
+    assert float(a @ b / np.sqrt((a @ a) * (b @ b))) > 0.995
+    assert q3t.library().q3t_kernel_error_count() == 0
+
+
 def test_host_pump_equals_stepping(q3t, model):
     """The compiled host loop over the exported ABI produces what the same calls made one by one do."""
     for n in (1, 3):
