@@ -370,6 +370,19 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                       "frac_of_8TBs": b1_bytes / (ms1 * 1e-3 / k1) / 8.0e12,
                       "api": "qwen3_tts_session_next_frame"}
         one[0].close()
+        # ---- a 128-position prompt (time to the first semantic token), 64 positions per pass ----
+        ids = [int(t) for t in np.random.default_rng(4).integers(0, 151936, size=128)]
+        prompt_ms = []
+        for _ in range(3):
+            ps = model.create_session(2048, 5)
+            ps.talker_sampling, ps.predictor_sampling = talker_cfg, predictor_cfg
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            ps.prefill(ids, [-1] * 128)
+            prompt_ms.append((time.perf_counter() - t0) * 1e3)
+            ps.close()
+        line["prefill"] = {"positions": 128, "ms": min(prompt_ms), "positions_per_pass": 64,
+                           "api": "qwen3_tts_session_prefill"}
         # ---- batch-1 int8 GEMV, configs[0]: 16 weight images (201 MB > L2) round-robin --------------
         g = native.benchmark_int8_gemv(local_rank, 2048, 6144, rows=1, buffers=16, iterations=4000)
         gemv_s = g.mean_launch_microseconds * 1e-6
