@@ -68,6 +68,32 @@ typedef struct Qwen3TtsGemvBenchmark {
     float tera_operations_per_second;
 } Qwen3TtsGemvBenchmark;
 
+/* reference header :39-46; filled by qwen3_tts_benchmark_bf16_argmax */
+typedef struct Qwen3TtsArgmaxBenchmark {
+    int32_t vocabulary_size;
+    int32_t iterations;
+    int32_t selected_token;
+    int32_t expected_token;
+    float cold_launch_microseconds;
+    float mean_launch_microseconds;
+} Qwen3TtsArgmaxBenchmark;
+
+/* reference header :59 and :61-72: a device arena filled by sequential uploads through pinned
+ * staging memory (the host's weight loader, src/device_weights.rs) */
+typedef struct Qwen3TtsDeviceBuffer Qwen3TtsDeviceBuffer;
+typedef struct Qwen3TtsWeightUploadMetrics {
+    int32_t device_index;
+    int32_t reserved;
+    uint64_t allocation_bytes;
+    uint64_t pinned_staging_bytes;
+    uint64_t uploaded_bytes;
+    uint64_t upload_calls;
+    uint64_t free_before_bytes;
+    uint64_t free_after_allocation_bytes;
+    float allocation_microseconds;
+    float upload_microseconds;
+} Qwen3TtsWeightUploadMetrics;
+
 /* reference header :74-79 */
 typedef struct Qwen3TtsPrimitiveParity {
     float rms_norm_max_absolute_error;
@@ -161,6 +187,42 @@ QWEN3_TTS_API uint32_t qwen3_tts_talker_abi_version(void);
 /* reference header :166-171 (runtime.cu) */
 QWEN3_TTS_API int32_t qwen3_tts_probe_device(int32_t device_index, Qwen3TtsDeviceInfo* output,
                                              char* error, size_t error_capacity);
+
+/* reference header :173-180 (runtime.cu:127-255): one-block argmax over a bf16 logit vector whose
+ * maximum is planted at token min(1729, V - 1); fails if another token comes back.  CLI only. */
+QWEN3_TTS_API int32_t qwen3_tts_benchmark_bf16_argmax(int32_t device_index, int32_t vocabulary_size,
+                                                      int32_t iterations,
+                                                      Qwen3TtsArgmaxBenchmark* output, char* error,
+                                                      size_t error_capacity);
+
+/* reference header :182-190 (gemv.cu:88-270, cuBLAS there): bf16 matrix-vector product on zero-filled
+ * operands with a zero-output check, here on this library's own kernel.  CLI only; the int8
+ * figure of the decode path is q3t_benchmark_int8_gemv. */
+QWEN3_TTS_API int32_t qwen3_tts_benchmark_bf16_gemv(int32_t device_index, int32_t input_features,
+                                                    int32_t output_features, int32_t iterations,
+                                                    Qwen3TtsGemvBenchmark* output, char* error,
+                                                    size_t error_capacity);
+
+/* reference header :192-240 (weights.cu:98-340).  Return codes are the reference's: 0, or -1..-4
+ * for the argument checks in the order they are made, or the CUDA error number. */
+QWEN3_TTS_API int32_t qwen3_tts_device_buffer_create(int32_t device_index, uint64_t capacity_bytes,
+                                                     uint64_t staging_bytes,
+                                                     Qwen3TtsDeviceBuffer** output,
+                                                     Qwen3TtsWeightUploadMetrics* metrics,
+                                                     char* error, size_t error_capacity);
+QWEN3_TTS_API int32_t qwen3_tts_device_buffer_upload(Qwen3TtsDeviceBuffer* buffer,
+                                                     uint64_t offset_bytes, const void* source,
+                                                     uint64_t bytes, char* error,
+                                                     size_t error_capacity);
+QWEN3_TTS_API int32_t qwen3_tts_device_buffer_finish(Qwen3TtsDeviceBuffer* buffer,
+                                                     Qwen3TtsWeightUploadMetrics* metrics,
+                                                     char* error, size_t error_capacity);
+QWEN3_TTS_API int32_t qwen3_tts_device_buffer_read(Qwen3TtsDeviceBuffer* buffer,
+                                                   uint64_t offset_bytes, void* destination,
+                                                   uint64_t bytes, char* error,
+                                                   size_t error_capacity);
+QWEN3_TTS_API const void* qwen3_tts_device_buffer_data(const Qwen3TtsDeviceBuffer* buffer);
+QWEN3_TTS_API void qwen3_tts_device_buffer_destroy(Qwen3TtsDeviceBuffer* buffer);
 
 /* reference header :202-207 (primitive_parity.cu:328): runs the four closed-form known-answer
  * cases (RMSNorm, RoPE, attention, SiLU gate) through this library's kernels */

@@ -93,6 +93,9 @@ class DeviceInfoC(C.Structure):
 # every symbol the headers in include/ declare
 EXPORTED_SYMBOLS = (
     "qwen3_tts_talker_abi_version", "qwen3_tts_probe_device",
+    "qwen3_tts_benchmark_bf16_argmax", "qwen3_tts_benchmark_bf16_gemv",
+    "qwen3_tts_device_buffer_create", "qwen3_tts_device_buffer_upload", "qwen3_tts_device_buffer_finish",
+    "qwen3_tts_device_buffer_read", "qwen3_tts_device_buffer_data", "qwen3_tts_device_buffer_destroy",
     "qwen3_tts_validate_transformer_primitives", "qwen3_tts_model_create",
     "qwen3_tts_model_destroy", "qwen3_tts_model_upload_tensor", "qwen3_tts_model_finalize",
     "qwen3_tts_session_create", "qwen3_tts_session_destroy", "qwen3_tts_session_reset",
@@ -582,3 +585,76 @@ def benchmark_int8_gemv(device_index: int, in_features: int, out_features: int, 
     _check(library().q3t_benchmark_int8_gemv(device_index, in_features, out_features, rows, buffers,
                                              iterations, C.byref(out), err, _ERR_CAP), err)
     return out
+
+
+# ---- entry points only the reference's command-line tools use (cli_compat.cu) -----------------
+
+class ArgmaxBenchmarkC(C.Structure):        # qwen3_tts_native.h Qwen3TtsArgmaxBenchmark
+    _fields_ = [("vocabulary_size", C.c_int32), ("iterations", C.c_int32), ("selected_token", C.c_int32),
+                ("expected_token", C.c_int32), ("cold_launch_microseconds", C.c_float),
+                ("mean_launch_microseconds", C.c_float)]
+
+
+class WeightUploadMetricsC(C.Structure):    # qwen3_tts_native.h Qwen3TtsWeightUploadMetrics
+    _fields_ = [("device_index", C.c_int32), ("reserved", C.c_int32), ("allocation_bytes", C.c_uint64),
+                ("pinned_staging_bytes", C.c_uint64), ("uploaded_bytes", C.c_uint64),
+                ("upload_calls", C.c_uint64), ("free_before_bytes", C.c_uint64),
+                ("free_after_allocation_bytes", C.c_uint64), ("allocation_microseconds", C.c_float),
+                ("upload_microseconds", C.c_float)]
+
+
+def benchmark_bf16_argmax(device_index: int, vocabulary_size: int, iterations: int = 100):
+    out = ArgmaxBenchmarkC()
+    err = C.create_string_buffer(_ERR_CAP)
+    rc = library().qwen3_tts_benchmark_bf16_argmax(C.c_int32(device_index), C.c_int32(vocabulary_size),
+                                                   C.c_int32(iterations), C.byref(out), err, C.c_size_t(_ERR_CAP))
+    return rc, out, err.value.decode()
+
+
+def benchmark_bf16_gemv(device_index: int, in_features: int, out_features: int, iterations: int = 100):
+    out = GemvBenchmarkC()
+    err = C.create_string_buffer(_ERR_CAP)
+    rc = library().qwen3_tts_benchmark_bf16_gemv(C.c_int32(device_index), C.c_int32(in_features),
+                                                 C.c_int32(out_features), C.c_int32(iterations), C.byref(out),
+                                                 err, C.c_size_t(_ERR_CAP))
+    return rc, out, err.value.decode()
+
+
+class DeviceWeightBuffer:
+    """The upload arena of the reference's weight loader (src/device_weights.rs)."""
+
+    def __init__(self, device_index: int, capacity_bytes: int, staging_bytes: int):
+        lib = library()
+        lib.qwen3_tts_device_buffer_data.restype = C.c_void_p
+        lib.qwen3_tts_device_buffer_data.argtypes = [C.c_void_p]
+        lib.qwen3_tts_device_buffer_destroy.restype = None
+        lib.qwen3_tts_device_buffer_destroy.argtypes = [C.c_void_p]
+        self._lib = lib
+        self._handle = C.c_void_p()
+        self.metrics = WeightUploadMetricsC()
+        self.error = C.create_string_buffer(_ERR_CAP)
+        self.status = lib.qwen3_tts_device_buffer_create(
+            C.c_int32(device_index), C.c_uint64(capacity_bytes), C.c_uint64(staging_bytes), C.byref(self._handle),
+            C.byref(self.metrics), self.error, C.c_size_t(_ERR_CAP))
+
+    def upload(self, offset: int, data: bytes) -> int:
+        return self._lib.qwen3_tts_device_buffer_upload(self._handle, C.c_uint64(offset), data,
+                                                        C.c_uint64(len(data)), self.error, C.c_size_t(_ERR_CAP))
+
+    def finish(self) -> int:
+        return self._lib.qwen3_tts_device_buffer_finish(self._handle, C.byref(self.metrics), self.error,
+                                                        C.c_size_t(_ERR_CAP))
+
+    def read(self, offset: int, count: int):
+        out = C.create_string_buffer(count)
+        rc = self._lib.qwen3_tts_device_buffer_read(self._handle, C.c_uint64(offset), out, C.c_uint64(count),
+                                                    self.error, C.c_size_t(_ERR_CAP))
+        return rc, out.raw
+
+    def data(self) -> int:
+        return self._lib.qwen3_tts_device_buffer_data(self._handle) or 0
+
+    def close(self) -> None:
+        if self._handle:
+            self._lib.qwen3_tts_device_buffer_destroy(self._handle)
+            self._handle = C.c_void_p()

@@ -55,6 +55,8 @@ def test_struct_layouts(q3t):
     assert C.sizeof(n.SessionMemoryC) == 32
     assert C.sizeof(n.StateInfoC) == 40
     assert C.sizeof(n.DeviceFrameViewV2C) == 40 and C.alignment(n.DeviceFrameViewV2C) == 8
+    assert C.sizeof(n.ArgmaxBenchmarkC) == 24
+    assert C.sizeof(n.WeightUploadMetricsC) == 64
     assert n.DeviceFrameViewV2C.lease_id.offset == 24
     assert n.DeviceFrameViewV2C.device_index.offset == 32
 
