@@ -104,6 +104,31 @@ QWEN3_TTS_API int32_t q3t_host_pump_frames(Qwen3TtsModelHandle model, Qwen3TtsSe
                                            uint16_t* last_tokens, double* wall_milliseconds,
                                            char* error, size_t error_capacity);
 
+/* The host's lockstep rendezvous (BatchFramePump, native_talker.rs:267-401) in C++, for up to 64
+ * sessions: owner threads call q3t_pump_begin_frame; a worker thread gathers the requests of the
+ * registered (decoding) sessions, up to max_batch or until gather_window_microseconds after the
+ * first one (the reference waits 2 ms), and begins them with one
+ * qwen3_tts_model_batch_next_frame_begin_v2.  Each owner finishes its own lease with
+ * qwen3_tts_session_next_frame_finish_v2.  frames_emitted == 0 bypasses the rendezvous
+ * (native_talker.rs:1426-1431): the first frame is begun on the caller's thread. */
+typedef struct Q3tFramePump Q3tFramePump;
+QWEN3_TTS_API int32_t q3t_pump_create(Qwen3TtsModelHandle model, int32_t max_batch,
+                                      int32_t gather_window_microseconds, Q3tFramePump** output,
+                                      char* error, size_t error_capacity);
+QWEN3_TTS_API void q3t_pump_destroy(Q3tFramePump* pump);
+QWEN3_TTS_API void q3t_pump_register(Q3tFramePump* pump);
+QWEN3_TTS_API void q3t_pump_unregister(Q3tFramePump* pump);
+QWEN3_TTS_API int32_t q3t_pump_begin_frame(Q3tFramePump* pump, Qwen3TtsSessionHandle session,
+                                           int32_t frames_emitted, int32_t trailing_text_token_id,
+                                           Qwen3TtsSamplingConfig talker_sampling,
+                                           Qwen3TtsSamplingConfig predictor_sampling,
+                                           Qwen3TtsDeviceFrameViewV2* output, char* error,
+                                           size_t error_capacity);
+QWEN3_TTS_API int32_t q3t_pump_statistics(Q3tFramePump* pump, uint64_t* batches, uint64_t* frames);
+/* Placement of a new session over the GPUs of one host: fewest active sessions, lowest index
+ * first (sessions are pinned for life, docs/ARCHITECTURE.md:285 of the reference). */
+QWEN3_TTS_API int32_t q3t_pick_device(const int32_t* active_sessions_per_device, int32_t devices);
+
 /* A chain of 1..8 dependent batch-1 GEMVs (rows == 1, in_features a multiple of 1024 up to 6144)
  * in one persistent cooperative launch: op i+1 may read what op i wrote.  Bit-identical to issuing
  * the same descriptors one by one through q3t_launch_int8_gemm_ex.  Launches through this entry

@@ -106,6 +106,8 @@ EXPORTED_SYMBOLS = (
     "q3t_launch_int8_gate_up_silu_rows", "q3t_launch_int8_gemm_ex",
     "q3t_launch_quantize_weight_rows", "q3t_benchmark_int8_gemv", "q3t_launch_rms_norm_rows",
     "q3t_launch_int8_gemv_chain", "q3t_benchmark_int8_gemv_chain", "q3t_host_pump_frames",
+    "q3t_pump_create", "q3t_pump_destroy", "q3t_pump_register", "q3t_pump_unregister",
+    "q3t_pump_begin_frame", "q3t_pump_statistics", "q3t_pick_device",
     "q3t_launch_head_rms_norm_rows", "q3t_launch_rope_rows_at", "q3t_launch_kv_scatter_rows",
     "q3t_launch_bias_activation_rows", "q3t_launch_add_in_place", "q3t_launch_silu_gate",
     "q3t_launch_gather_embedding_rows", "q3t_launch_add_embedding_rows",
@@ -658,3 +660,57 @@ class DeviceWeightBuffer:
         if self._handle:
             self._lib.qwen3_tts_device_buffer_destroy(self._handle)
             self._handle = C.c_void_p()
+
+
+class BatchFramePump:
+    """The lockstep rendezvous of the reference's host (native_talker.rs:267-401), C++ side in
+    csrc/host_pump.cu.  Owner threads call begin(); each then finishes its own frame."""
+
+    def __init__(self, model: "NativeTalkerModel", max_batch: int = MAX_BATCH_SESSIONS, window_us: int = 2000):
+        lib = library()
+        lib.q3t_pump_begin_frame.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, SamplingConfigC,
+                                             SamplingConfigC, C.POINTER(DeviceFrameViewV2C), C.c_char_p, C.c_size_t]
+        lib.q3t_pump_begin_frame.restype = C.c_int32
+        lib.q3t_pump_destroy.argtypes = [C.c_void_p]
+        lib.q3t_pump_destroy.restype = None
+        lib.q3t_pump_register.argtypes = [C.c_void_p]
+        lib.q3t_pump_register.restype = None
+        lib.q3t_pump_unregister.argtypes = [C.c_void_p]
+        lib.q3t_pump_unregister.restype = None
+        self._lib = lib
+        self._handle = C.c_void_p()
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(lib.q3t_pump_create(model._handle, C.c_int32(max_batch), C.c_int32(window_us), C.byref(self._handle),
+                                   err, C.c_size_t(_ERR_CAP)), err)
+
+    def register(self) -> None:
+        self._lib.q3t_pump_register(self._handle)
+
+    def unregister(self) -> None:
+        self._lib.q3t_pump_unregister(self._handle)
+
+    def begin(self, session: "NativeTalkerSession", trailing_text_id: int) -> "PendingTalkerFrame":
+        view = DeviceFrameViewV2C()
+        view.struct_size = C.sizeof(DeviceFrameViewV2C)
+        view.reserved = 0
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(self._lib.q3t_pump_begin_frame(self._handle, session._handle, session.frames_emitted,
+                                              trailing_text_id, session.talker_sampling.to_c(),
+                                              session.predictor_sampling.to_c(), C.byref(view), err, _ERR_CAP), err)
+        return PendingTalkerFrame(session, view)
+
+    def statistics(self):
+        batches, frames = C.c_uint64(0), C.c_uint64(0)
+        self._lib.q3t_pump_statistics(self._handle, C.byref(batches), C.byref(frames))
+        return int(batches.value), int(frames.value)
+
+    def close(self) -> None:
+        if self._handle:
+            self._lib.q3t_pump_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+
+def pick_device(active_sessions_per_device: Sequence[int]) -> int:
+    n = len(active_sessions_per_device)
+    arr = (C.c_int32 * max(n, 1))(*[int(v) for v in active_sessions_per_device])
+    return int(library().q3t_pick_device(arr, C.c_int32(n)))

@@ -349,6 +349,53 @@ def test_host_pump_equals_stepping(q3t, model):
             s_.close()
 
 
+def test_frame_pump_batches_concurrent_owners(q3t, model):
+    """Twelve owner threads ask for frames through the C++ rendezvous: the first frame of each
+    bypasses it, later frames share lockstep batches, and every session ends where it ends when
+    stepped alone (SIMT kernels for every row count, so batching cannot change a bit)."""
+    import threading
+    n, frames = 12, 4
+    model.set_option("tc_min_rows", 65)
+    pump = q3t.native.BatchFramePump(model, max_batch=64, window_us=20000)
+    try:
+        solo = [run_solo(q3t, model, 400 + i, frames) for i in range(n)]
+        sessions = [start(q3t, model, 400 + i) for i in range(n)]
+        got = [[] for _ in range(n)]
+        errors = []
+
+        def owner(i):
+            try:
+                pump.register()
+                for f in range(frames):
+                    pending = pump.begin(sessions[i], 100 + f)
+                    fr = pending.finish_without_consumer()
+                    _, tokens, _ = sessions[i].read_state()
+                    got[i].append((tuple(int(t) for t in tokens), fr.next_semantic_token))
+            except Exception as exc:      # surfaced below, on the main thread
+                errors.append(exc)
+            finally:
+                pump.unregister()
+
+        threads = [threading.Thread(target=owner, args=(i,)) for i in range(n)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=120)
+        assert not errors, errors
+        for i in range(n):
+            assert [(tuple(c), nxt) for c, nxt in solo[i]] == got[i], i
+        batches, pumped = pump.statistics()
+        assert pumped == n * (frames - 1)              # first frames went around the pump
+        assert batches < pumped                        # and later ones were really shared
+        for s_ in sessions:
+            s_.close()
+    finally:
+        pump.close()
+        model.set_option("tc_min_rows", 9)
+    assert q3t.native.pick_device([3, 1, 1, 2]) == 1 and q3t.native.pick_device([0]) == 0
+    assert q3t.native.pick_device([]) == -1
+
+
 def test_device_frame_lease_protocol(q3t, model):
     s = start(q3t, model, 55)
     err = C.create_string_buffer(256)
