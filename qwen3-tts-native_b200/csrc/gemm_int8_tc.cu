@@ -31,6 +31,7 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 namespace q3t {
@@ -714,8 +715,13 @@ cudaError_t launch_int8_gemm_tc(const GemvArgs& a, cudaStream_t stream) {
     // K-slices per tile = cluster size: as many as still let every cluster be resident at once (a
     // second wave would double the time); slices and row shares may be ragged
     const int (&resident)[9] = scratch->resident_clusters[mt == 16 ? 0 : (mt == 32 ? 1 : 2)][gateup ? 1 : 0];
+    static const int split_cap = [] {
+        const char* v = std::getenv("QWEN3_TTS_TC_MAX_SPLITS");
+        const int n = v != nullptr ? std::atoi(v) : 8;
+        return n < 1 ? 1 : (n > 8 ? 8 : n);
+    }();
     int splits = 1;
-    for (int s = 2; s <= 8 && s <= nk; ++s) {
+    for (int s = 2; s <= split_cap && s <= nk; ++s) {
         if (p.tiles <= resident[s]) splits = s;
     }
     p.splits = splits;
