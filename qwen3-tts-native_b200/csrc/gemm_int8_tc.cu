@@ -45,9 +45,10 @@ constexpr int kTcThreads = 128 + 128 * kGroups;
 constexpr int kTileN = 128;            // output channels per CTA = TMEM lanes
 constexpr int kBK = 128;               // K elements per pipeline step
 constexpr int kWStages = 6;            // int8 ring in shared memory
-constexpr int kXStages = 4;            // activation ring in shared memory
+constexpr int kXStages = 4;            // activation ring in shared memory (stage i pairs with A stage i)
 constexpr int kAStages = 4;            // dequantised A stages in TMEM
 constexpr int kWStageBytes = kTileN * kBK;          // 16 KB
+static_assert(kXStages == kAStages, "activation stage i and TMEM A stage i share their barriers");
 constexpr int kAStageCols = kBK / 2;   // 64 TMEM columns: two bf16 per 32-bit column
 constexpr int kAccCols = 64;           // accumulators sit in columns [0, 64), A stages follow
 constexpr uint32_t kTmemCols = 512;    // 64 + 4 * 64 rounded up to a power of two
@@ -322,7 +323,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             mbar_init(&empty_x[s], 1);
         }
         for (int s = 0; s < kAStages; ++s) {
-            mbar_init(&full_a[s], 4);
+            mbar_init(&full_a[s], 4 + 1);     // four dequantiser warps + the activation copy (bytes)
             mbar_init(&empty_a[s], 1);
         }
         mbar_init(acc_done, 1);
@@ -366,11 +367,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             // ---- activation producer ------------------------------------------------------
             for (int i = 0; i < nk; ++i) {
                 const int sx = i % kXStages;
-                if (i >= kXStages && !guard.wait(&empty_x[sx], ((i / kXStages) - 1) & 1)) break;
-                mbar_expect_tx(&full_x[sx], kXStageBytes);
+                if (i >= kXStages && !guard.wait(&empty_a[sx], ((i / kXStages) - 1) & 1)) break;
+                // the activation tile lands on the same barrier the dequantisers arrive on, so
+                // that the MMA issuer has one thing to wait for per step
+                mbar_expect_tx(&full_a[sx], kXStageBytes);
                 unsigned char* dst = xs + sx * kXStageBytes;
-                tma_load_2d(dst, &x_map, k_first + i * kBK, 0, &full_x[sx]);
-                tma_load_2d(dst + kXAtomBytes, &x_map, k_first + i * kBK + 64, 0, &full_x[sx]);
+                tma_load_2d(dst, &x_map, k_first + i * kBK, 0, &full_a[sx]);
+                tma_load_2d(dst + kXAtomBytes, &x_map, k_first + i * kBK + 64, 0, &full_a[sx]);
             }
         }
     } else if (warp == 1) {
@@ -379,7 +382,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             for (int i = 0; i < nk; ++i) {
                 const int sa = i % kAStages;
                 const int sx = i % kXStages;
-                bool ok = guard.wait(&full_x[sx], (i / kXStages) & 1);
+                bool ok = true;
                 if (i < 16) TC_TRACE(64 + i);
                 ok = ok && guard.wait(&full_a[sa], (i / kAStages) & 1);
                 if (i < 16) TC_TRACE(80 + i);
@@ -394,8 +397,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                                 umma_desc(b_addr + (j / 4) * kXAtomBytes + 32 * (j % 4)), kIdesc,
                                 (i | j) != 0 ? 1u : 0u);
                 }
-                umma_commit(&empty_a[sa]);
-                umma_commit(&empty_x[sx]);
+                umma_commit(&empty_a[sa]);       // frees the TMEM stage and the activation stage
                 if (i < 16) TC_TRACE(8 + i);
             }
             umma_commit(acc_done);   // fires when every MMA issued above has completed
