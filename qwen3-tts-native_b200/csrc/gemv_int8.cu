@@ -95,6 +95,13 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
         }
     }
 
+    // ... and so do its scales, so that the epilogue of the first channel does not wait on memory.
+    float pre_scale = 0.0f, pre_scale_up = 0.0f;
+    if (first_channel < out_features) {
+        pre_scale = scales[first_channel];
+        if (GATEUP) pre_scale_up = scales[out_features + first_channel];
+    }
+
     // Launched with programmatic stream serialisation: this grid may start while the one before
     // it in the stream is still running.  Everything above touches only the weights; from here on
     // the previous grid's output is read, so wait for it to complete (a no-op when the launch
@@ -186,32 +193,34 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
             if (GATEUP) b = warp_sum_down(acc_up[r]);
             if (lane == 0) {
                 const size_t o = (size_t)r * out_features + channel;
+                const bool first = channel == first_channel;
+                const float scale = first ? pre_scale : scales[channel];
                 if (GATEUP) {
-                    const float gate = a * scales[channel];
-                    const float up = b * scales[out_features + channel];
+                    const float gate = a * scale;
+                    const float up = b * (first ? pre_scale_up : scales[out_features + channel]);
                     const float activated = gate / (1.0f + expf(-gate));
                     const float val = activated * up;
                     if (output32 != nullptr) output32[o] = val;
                     output[o] = f2bf(val);
                 } else if (epilogue == EPI_PLAIN) {
-                    const float val = a * scales[channel];
+                    const float val = a * scale;
                     if (output32 != nullptr) output32[o] = val;
                     output[o] = f2bf(val);
                 } else if (epilogue == EPI_ADD) {
-                    const float val = fmaf(a, scales[channel], bf2f(output[o]));
+                    const float val = fmaf(a, scale, bf2f(output[o]));
                     if (output32 != nullptr) output32[o] = val;
                     output[o] = f2bf(val);
                 } else if (epilogue == EPI_BIAS) {
-                    const float val = rbf(a * scales[channel]) + bf2f(bias[channel]);
+                    const float val = rbf(a * scale) + bf2f(bias[channel]);
                     if (output32 != nullptr) output32[o] = val;
                     output[o] = f2bf(val);
                 } else if (epilogue == EPI_BIAS_SILU) {
-                    float val = rbf(a * scales[channel]) + bf2f(bias[channel]);
+                    float val = rbf(a * scale) + bf2f(bias[channel]);
                     val *= 1.0f / (1.0f + expf(-val));
                     if (output32 != nullptr) output32[o] = val;
                     output[o] = f2bf(val);
                 } else {  // EPI_BIAS_ADD
-                    const float t = rbf(rbf(a * scales[channel]) + bf2f(bias[channel]));
+                    const float t = rbf(rbf(a * scale) + bf2f(bias[channel]));
                     const float val = bf2f(resid[o]) + t;
                     if (output32 != nullptr) output32[o] = val;
                     resid[o] = f2bf(val);

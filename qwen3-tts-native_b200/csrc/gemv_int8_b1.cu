@@ -31,6 +31,33 @@ constexpr int kWaitLimit = 1 << 22;          // mbarrier try_wait attempts befor
 
 __device__ unsigned int g_gemv_b1_errors = 0;
 
+// Optional phase timestamps for study builds (-DQ3T_B1_TRACE): lane 0 of every warp of the first
+// CTAs writes %globaltimer at the marked points.  Compiled out otherwise.
+#ifdef Q3T_B1_TRACE
+__device__ unsigned long long g_b1_trace[8 * 8 * 16];
+__device__ unsigned long long g_b1_cta_times[1024 * 2];     // per CTA: dependency wait returned, last warp done
+#define B1_TRACE_CTA(which)                                                                     \
+    do {                                                                                        \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x < 1024) {                                       \
+            unsigned long long t_;                                                              \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+            if (which) atomicMax(&g_b1_cta_times[blockIdx.x * 2 + 1], t_);                        \
+            else if (threadIdx.x == 0) g_b1_cta_times[blockIdx.x * 2] = t_;                      \
+        }                                                                                       \
+    } while (0)
+#define B1_TRACE(slot)                                                                          \
+    do {                                                                                        \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x < 8 && (slot) < 16) {                           \
+            unsigned long long t_;                                                              \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+            g_b1_trace[(blockIdx.x * 8 + threadIdx.x / 32) * 16 + (slot)] = t_;                   \
+        }                                                                                       \
+    } while (0)
+#else
+#define B1_TRACE(slot) do { } while (0)
+#define B1_TRACE_CTA(which) do { } while (0)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -96,8 +123,7 @@ struct B1Params {
     float eps;
 };
 
-__device__ __forceinline__ void store_result(const B1Params& p, int channel, float acc) {
-    const float scale = p.scales[channel];
+__device__ __forceinline__ void store_result(const B1Params& p, int channel, float acc, float scale) {
     float val;
     if (p.epilogue == EPI_PLAIN) {
         val = acc * scale;
@@ -131,10 +157,12 @@ struct Ring {
 };
 
 template <int VPL, bool GATEUP, bool NORM>
-__global__ void __launch_bounds__(kThreads, 1) gemv_b1_kernel(const B1Params p) {
+__global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(const B1Params p) {
     using R = Ring<VPL>;
     constexpr int K = R::kK;
     constexpr int STAGES = R::kStages;
+    pdl_trigger();   // the successor may become resident (and fetch its own weights) right away
+    B1_TRACE(0);
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* ring = smem;
     bf16* xs = reinterpret_cast<bf16*>(smem + R::kRingBytes);
@@ -180,7 +208,37 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_b1_kernel(const B1Params p) 
     }
     __syncwarp();
 
-    // ---- stage the activation row (normalised if asked) ---------------------------------
+    // The scales of this warp's rows are constants too: lane 2i (+1) fetches the scale of the
+    // first (second) row of the warp's i-th pair now, so that no epilogue waits on memory.
+    constexpr int kScaleSlots = kWarp / 2;
+    float my_scale = 0.0f;
+    {
+        const int pr = p0 + warp + kWarps * (lane >> 1);
+        if (pr < p1) {
+            if (GATEUP) {
+                my_scale = p.scales[(lane & 1) ? N + pr : pr];
+            } else if (2 * pr + (lane & 1) < N) {
+                my_scale = p.scales[2 * pr + (lane & 1)];
+            }
+        }
+    }
+
+    // Two of these CTAs fit on an SM, so under programmatic stream serialisation the next GEMV of
+    // the stream is resident while this one computes: its weight slice is already in its rings
+    // when this grid completes.  Only the weights were touched so far; the activations below
+    // are the predecessor's output.
+    B1_TRACE(1);
+    pdl_wait();
+    B1_TRACE(2);
+    B1_TRACE_CTA(0);
+
+    // ---- the activations of this lane, as fp32 in registers ------------------------------
+    // Lane l owns the 16-byte weight vectors l, l+32, ... of every row, so it needs the same
+    // 16 * VPL activations for every row.  kVectorPairs: two vectors' FMA chains run as one
+    // packed fp32x2 chain and the activations are kept as fp32 pairs (x of vector 2j, x of
+    // vector 2j+1); otherwise (long rows, not enough registers) two rows share a packed chain and
+    // the activations stay packed bf16.
+    constexpr bool kVectorPairs = VPL <= 4;
     if (NORM) {
         float ss = 0.0f;
         for (int i = tid; i < K; i += kThreads) {
@@ -197,61 +255,118 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_b1_kernel(const B1Params p) 
             xs[i] = o;
             if (p.norm_out != nullptr && blockIdx.x == 0) p.norm_out[i] = o;
         }
-    } else {
-        const int4* src = reinterpret_cast<const int4*>(p.x);
-        int4* dst = reinterpret_cast<int4*>(xs);
-        for (int i = tid; i < K / 8; i += kThreads) dst[i] = src[i];
+        __syncthreads();
     }
-    __syncthreads();
-
+    const bf16* xsrc = NORM ? xs : p.x;          // shared or global: plain loads either way
     uint32_t xr[VPL][8];   // 16 activations per owned vector, packed bf16 pairs
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
-        const int4* v4 = reinterpret_cast<const int4*>(xs + (size_t)(lane + 32 * j) * 16);
+        const int4* v4 = reinterpret_cast<const int4*>(xsrc + (size_t)(lane + 32 * j) * 16);
         const int4 a = v4[0];
         const int4 b = v4[1];
         xr[j][0] = a.x; xr[j][1] = a.y; xr[j][2] = a.z; xr[j][3] = a.w;
         xr[j][4] = b.x; xr[j][5] = b.y; xr[j][6] = b.z; xr[j][7] = b.w;
     }
+    unsigned long long xp[kVectorPairs ? VPL / 2 : 1][16];
+    if (kVectorPairs) {
+#pragma unroll
+        for (int jp = 0; jp < VPL / 2; ++jp) {
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                xp[jp][2 * h] = pack2(bf_lo(xr[2 * jp][h]), bf_lo(xr[2 * jp + 1][h]));
+                xp[jp][2 * h + 1] = pack2(bf_hi(xr[2 * jp][h]), bf_hi(xr[2 * jp + 1][h]));
+            }
+        }
+    }
 
     const unsigned long long neg_bias = pack2(-8388736.0f, -8388736.0f);   // -(2^23 + 128)
+    B1_TRACE(3);
+    // The warp reductions of up to kGroup consecutive pairs run together: their shuffle chains
+    // are independent, so a group pays the five-step latency once.
+    constexpr int kGroup = 4;
     bool failed = false;
     int it = 0;
     int pair = p0 + warp;
-    for (; pair < p1; pair += kWarps, ++it) {
+    while (pair < p1 && !failed) {
+      const int base_pair = pair;
+      const int base_it = it;
+      int done = 0;
+      float pa[kGroup], pb[kGroup];
+#pragma unroll
+      for (int gi = 0; gi < kGroup; ++gi) {
+        pa[gi] = 0.0f;
+        pb[gi] = 0.0f;
+        if (pair >= p1 || failed) continue;
         const int stage = it % STAGES;
         const uint32_t parity = (it / STAGES) & 1;
         if (!mbar_wait_bounded(&my_bars[stage], parity)) {
             failed = true;
-            break;
+            continue;
         }
         const unsigned char* a = my_ring + (size_t)stage * R::kPairBytes;
-        unsigned long long acc = pack2(0.0f, 0.0f);
+        B1_TRACE(4 + 3 * it);
+        float ra, rb;
+        if (kVectorPairs) {
+            float row_acc[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int j = 0; j < VPL; ++j) {
-            const int4 wa = *reinterpret_cast<const int4*>(a + (size_t)(lane + 32 * j) * 16);
-            const int4 wb = *reinterpret_cast<const int4*>(a + K + (size_t)(lane + 32 * j) * 16);
-            const uint32_t ua[4] = {(uint32_t)wa.x ^ 0x80808080u, (uint32_t)wa.y ^ 0x80808080u,
-                                    (uint32_t)wa.z ^ 0x80808080u, (uint32_t)wa.w ^ 0x80808080u};
-            const uint32_t ub[4] = {(uint32_t)wb.x ^ 0x80808080u, (uint32_t)wb.y ^ 0x80808080u,
-                                    (uint32_t)wb.z ^ 0x80808080u, (uint32_t)wb.w ^ 0x80808080u};
-            unsigned long long sum = pack2(0.0f, 0.0f);
+            for (int r = 0; r < 2; ++r) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float x0 = bf_lo(xr[j][2 * q]);
-                const float x1 = bf_hi(xr[j][2 * q]);
-                const float x2 = bf_lo(xr[j][2 * q + 1]);
-                const float x3 = bf_hi(xr[j][2 * q + 1]);
-                sum = fma2(add2(pack2(biased_byte<0>(ua[q]), biased_byte<0>(ub[q])), neg_bias),
-                           pack2(x0, x0), sum);
-                sum = fma2(add2(pack2(biased_byte<1>(ua[q]), biased_byte<1>(ub[q])), neg_bias),
-                           pack2(x1, x1), sum);
-                sum = fma2(add2(pack2(biased_byte<2>(ua[q]), biased_byte<2>(ub[q])), neg_bias),
-                           pack2(x2, x2), sum);
-                sum = fma2(add2(pack2(biased_byte<3>(ua[q]), biased_byte<3>(ub[q])), neg_bias),
-                           pack2(x3, x3), sum);
+                for (int jp = 0; jp < VPL / 2; ++jp) {
+                    const int4 w0 = *reinterpret_cast<const int4*>(a + (size_t)r * K + (size_t)(lane + 64 * jp) * 16);
+                    const int4 w1 = *reinterpret_cast<const int4*>(a + (size_t)r * K + (size_t)(lane + 64 * jp + 32) * 16);
+                    const uint32_t u0[4] = {(uint32_t)w0.x ^ 0x80808080u, (uint32_t)w0.y ^ 0x80808080u,
+                                            (uint32_t)w0.z ^ 0x80808080u, (uint32_t)w0.w ^ 0x80808080u};
+                    const uint32_t u1[4] = {(uint32_t)w1.x ^ 0x80808080u, (uint32_t)w1.y ^ 0x80808080u,
+                                            (uint32_t)w1.z ^ 0x80808080u, (uint32_t)w1.w ^ 0x80808080u};
+                    unsigned long long sum = pack2(0.0f, 0.0f);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        sum = fma2(add2(pack2(biased_byte<0>(u0[q]), biased_byte<0>(u1[q])), neg_bias),
+                                   xp[jp][4 * q], sum);
+                        sum = fma2(add2(pack2(biased_byte<1>(u0[q]), biased_byte<1>(u1[q])), neg_bias),
+                                   xp[jp][4 * q + 1], sum);
+                        sum = fma2(add2(pack2(biased_byte<2>(u0[q]), biased_byte<2>(u1[q])), neg_bias),
+                                   xp[jp][4 * q + 2], sum);
+                        sum = fma2(add2(pack2(biased_byte<3>(u0[q]), biased_byte<3>(u1[q])), neg_bias),
+                                   xp[jp][4 * q + 3], sum);
+                    }
+                    float s0, s1;
+                    unpack2(sum, s0, s1);
+                    row_acc[r] += s0;      // vector sums join the lane accumulator in vector order
+                    row_acc[r] += s1;
+                }
             }
-            acc = add2(acc, sum);
+            ra = row_acc[0];
+            rb = row_acc[1];
+        } else {
+            unsigned long long acc = pack2(0.0f, 0.0f);
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+                const int4 wa = *reinterpret_cast<const int4*>(a + (size_t)(lane + 32 * j) * 16);
+                const int4 wb = *reinterpret_cast<const int4*>(a + K + (size_t)(lane + 32 * j) * 16);
+                const uint32_t ua[4] = {(uint32_t)wa.x ^ 0x80808080u, (uint32_t)wa.y ^ 0x80808080u,
+                                        (uint32_t)wa.z ^ 0x80808080u, (uint32_t)wa.w ^ 0x80808080u};
+                const uint32_t ub[4] = {(uint32_t)wb.x ^ 0x80808080u, (uint32_t)wb.y ^ 0x80808080u,
+                                        (uint32_t)wb.z ^ 0x80808080u, (uint32_t)wb.w ^ 0x80808080u};
+                unsigned long long sum = pack2(0.0f, 0.0f);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float x0 = bf_lo(xr[j][2 * q]);
+                    const float x1 = bf_hi(xr[j][2 * q]);
+                    const float x2 = bf_lo(xr[j][2 * q + 1]);
+                    const float x3 = bf_hi(xr[j][2 * q + 1]);
+                    sum = fma2(add2(pack2(biased_byte<0>(ua[q]), biased_byte<0>(ub[q])), neg_bias),
+                               pack2(x0, x0), sum);
+                    sum = fma2(add2(pack2(biased_byte<1>(ua[q]), biased_byte<1>(ub[q])), neg_bias),
+                               pack2(x1, x1), sum);
+                    sum = fma2(add2(pack2(biased_byte<2>(ua[q]), biased_byte<2>(ub[q])), neg_bias),
+                               pack2(x2, x2), sum);
+                    sum = fma2(add2(pack2(biased_byte<3>(ua[q]), biased_byte<3>(ub[q])), neg_bias),
+                               pack2(x3, x3), sum);
+                }
+                acc = add2(acc, sum);
+            }
+            unpack2(acc, ra, rb);
         }
         __syncwarp();   // every lane has read the stage
         const int next = pair + kWarps * STAGES;
@@ -259,25 +374,51 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_b1_kernel(const B1Params p) 
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue(stage, next);
         }
-        float ra, rb;
-        unpack2(acc, ra, rb);
-        ra = warp_sum_down(ra);
-        rb = warp_sum_down(rb);
-        if (lane == 0) {
+        B1_TRACE(5 + 3 * it);
+        pa[gi] = ra;
+        pb[gi] = rb;
+        pair += kWarps;
+        ++it;
+        done = gi + 1;
+      }
+      B1_TRACE(12);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int gi = 0; gi < kGroup; ++gi) {
+            pa[gi] += __shfl_down_sync(0xffffffffu, pa[gi], o);
+            pb[gi] += __shfl_down_sync(0xffffffffu, pb[gi], o);
+        }
+      }
+      B1_TRACE(13);
+#pragma unroll
+      for (int gi = 0; gi < kGroup; ++gi) {
+        const int git = base_it + gi;
+        const int gpair = base_pair + kWarps * gi;
+        float scale_a = __shfl_sync(0xffffffffu, my_scale, (2 * git) & 31);
+        float scale_b = __shfl_sync(0xffffffffu, my_scale, (2 * git + 1) & 31);
+        if (gi < done && lane == 0) {
+            if (git >= kScaleSlots) {     // slices longer than the prefetched slots
+                scale_a = GATEUP ? p.scales[gpair] : p.scales[2 * gpair];
+                scale_b = GATEUP ? p.scales[N + gpair] : (2 * gpair + 1 < N ? p.scales[2 * gpair + 1] : 0.0f);
+            }
             if (GATEUP) {
-                const float gate = ra * p.scales[pair];
-                const float up = rb * p.scales[N + pair];
+                const float gate = pa[gi] * scale_a;
+                const float up = pb[gi] * scale_b;
                 const float activated = gate / (1.0f + expf(-gate));
                 const float val = activated * up;
-                if (p.y32 != nullptr) p.y32[pair] = val;
-                p.y[pair] = f2bf(val);
+                if (p.y32 != nullptr) p.y32[gpair] = val;
+                p.y[gpair] = f2bf(val);
             } else {
-                const int c = 2 * pair;
-                store_result(p, c, ra);
-                if (c + 1 < N) store_result(p, c + 1, rb);
+                const int c = 2 * gpair;
+                store_result(p, c, pa[gi], scale_a);
+                if (c + 1 < N) store_result(p, c + 1, pb[gi], scale_b);
             }
         }
+      }
+      B1_TRACE(14);
     }
+    B1_TRACE_CTA(1);
     if (failed) {
         // record, then give the copies already issued a bounded chance to land before leaving
         if (lane == 0) atomicAdd(&g_gemv_b1_errors, 1u);
@@ -308,9 +449,8 @@ cudaError_t launch_vpl(const B1Params& p, cudaStream_t stream) {
     const long long pairs = GATEUP ? p.out_features : (p.out_features + 1) / 2;
     long long grid = sm_count();
     if (grid > pairs) grid = pairs;
-    gemv_b1_kernel<VPL, GATEUP, NORM>
-        <<<static_cast<unsigned int>(grid), kThreads, Ring<VPL>::kSmemBytes, stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(gemv_b1_kernel<VPL, GATEUP, NORM>, dim3(static_cast<unsigned int>(grid)), dim3(kThreads),
+                      Ring<VPL>::kSmemBytes, stream, p);
 }
 
 template <int VPL>
