@@ -47,32 +47,17 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return r;
 }
 
-template <int HD, int G, bool PAGED>
-__global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const AttentionArgs a) {
+// EARLY: the launcher has checked AttentionArgs::inputs_settled (plain decode step, head_dim 128,
+// a grid that is resident at once); a separate instantiation, because holding the prefetched
+// fragments across the query prologue costs registers.
+template <int HD, int G, bool PAGED, bool EARLY>
+__global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_kernel(const AttentionArgs a) {
     constexpr int LPT = HD / 8;            // lanes per token
     constexpr int TPI = kWarp / LPT;       // tokens per warp iteration
     constexpr int ITERS = kWarpTokens / TPI;
 
-    pdl_wait();        // positions, q/k/v and the KV cache come from the kernels before this one
-    pdl_trigger();
     const int kvh = blockIdx.y;
     const int row = blockIdx.z;
-    const int pos = a.positions[row];
-    const int len = pos + 1;
-    const int nsplits = (len + kAttnChunk - 1) / kAttnChunk;
-    // A CTA walks `units` consecutive 64-token splits.  Each split still produces its own
-    // (max, sum, weighted V) partial, so the result does not depend on how many a CTA takes.
-    const int units = a.units_per_cta > 0 ? a.units_per_cta : 1;
-    const int split_first = blockIdx.x * units;
-    if (split_first >= nsplits) return;
-    const int split_end = min(nsplits, split_first + units);
-
-    __shared__ float qs[G][HD];
-    __shared__ float wm[kAttnWarps][G];
-    __shared__ float wl[kAttnWarps][G];
-    __shared__ __align__(16) float wacc[kAttnWarps][G][HD];
-    __shared__ int is_last;
-
     const int tid = threadIdx.x;
     const int lane = tid % kWarp;
     const int warp = tid / kWarp;
@@ -80,6 +65,10 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
     const int qw = a.q_heads * HD;
     const int q_stride = a.q_stride > 0 ? a.q_stride : qw;
     const int kn_stride = a.kv_new_stride > 0 ? a.kv_new_stride : kvw;
+    const int units = a.units_per_cta > 0 ? a.units_per_cta : 1;
+    const int split_first = blockIdx.x * units;
+    const int gid = lane >> 2;
+    const int tig = lane & 3;
 
     // ---- K/V row addressing ---------------------------------------------------------
     auto kv_row = [&](int token, bool value) -> bf16* {
@@ -93,6 +82,95 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
         bf16* base = value ? a.kv.v_bases[row] : a.kv.k_bases[row];
         return base + (size_t)token * kvw + (size_t)kvh * HD;
     };
+    // head_dim 128: the K and V fragments of one warp's 16 tokens (the main loop explains the
+    // layout); tokens at or past `bound` read as zero
+    int4 kr[2][4];
+    int4 vr[2][2][2];
+    auto load_kv = [&](int w0, int bound) {
+        const bf16* kpage = kv_row(w0, false);   // the 16 tokens of a warp share one page
+        const bf16* vpage = kv_row(w0, true);
+        const int4 zero4 = make_int4(0, 0, 0, 0);
+        // K: token 8 nt + gid, dims 32 jj + 8 tig .. + 7
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int t = 8 * nt + gid;
+            const bool valid = w0 + t < bound;
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                kr[nt][jj] = valid ? *reinterpret_cast<const int4*>(kpage + (size_t)t * kvw + 32 * jj + 8 * tig)
+                                   : zero4;
+            }
+        }
+        // V: tokens 8 h + 2 tig + p, dims 64 jb + 8 gid .. + 7.  Tokens past the end read as
+        // zero: their probability is zero, but 0 * (stale bits that decode as NaN) is not.
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int pp = 0; pp < 2; ++pp) {
+                const int t = 8 * h + 2 * tig + pp;
+                const bool valid = w0 + t < bound;
+#pragma unroll
+                for (int jb = 0; jb < 2; ++jb) {
+                    vr[h][pp][jb] = valid ? *reinterpret_cast<const int4*>(vpage + (size_t)t * kvw + 64 * jb + 8 * gid)
+                                          : zero4;
+                }
+            }
+    };
+
+    // ---- ahead of the dependency wait ---------------------------------------------------
+    // Constants (the per-head norm weights) always; with inputs_settled also the position, its
+    // cos/sin and the first split's K/V rows older than this step's token: what remains after the
+    // wait is one round trip for q / k_new / v_new.
+    constexpr int DPLN = HD >= 64 ? HD / 32 : 2;
+    bf16 nwq[DPLN], nwk[DPLN];
+    if (a.fused && HD >= 64) {
+#pragma unroll
+        for (int j = 0; j < DPLN; ++j) {
+            nwq[j] = a.q_norm_w[lane + 32 * j];
+            nwk[j] = a.k_norm_w[lane + 32 * j];
+        }
+    }
+    constexpr bool early = EARLY && HD == 128;
+    int pos = 0;
+    uint32_t cs_pre[DPLN / 2];
+    bool cs_ready = false;
+    if (early) {
+        pos = a.positions[row];
+        if (a.rope_table != nullptr && pos < a.rope_positions) {
+            cs_ready = true;
+#pragma unroll
+            for (int j = 0; j < DPLN / 2; ++j) cs_pre[j] = a.rope_table[(size_t)pos * (HD / 2) + lane + 32 * j];
+        }
+        const int w0e = split_first * kAttnChunk + warp * kWarpTokens;
+        if (w0e < pos) {
+            load_kv(w0e, pos);
+        } else {
+            const int4 zero4 = make_int4(0, 0, 0, 0);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    kr[i][j] = zero4;
+                    vr[i][j >> 1][j & 1] = zero4;
+                }
+        }
+    }
+
+    pdl_wait();        // q / k_new / v_new (and, unless settled, everything else) come from the kernel before
+    pdl_trigger();
+    if (!early) pos = a.positions[row];
+    const int len = pos + 1;
+    const int nsplits = (len + kAttnChunk - 1) / kAttnChunk;
+    // A CTA walks `units` consecutive 64-token splits.  Each split still produces its own
+    // (max, sum, weighted V) partial, so the result does not depend on how many a CTA takes.
+    if (split_first >= nsplits) return;
+    const int split_end = min(nsplits, split_first + units);
+
+    __shared__ float qs[G][HD];
+    __shared__ float wm[kAttnWarps][G];
+    __shared__ float wl[kAttnWarps][G];
+    __shared__ __align__(16) float wacc[kAttnWarps][G][HD];
+    __shared__ int is_last;
 
     // ---- query heads (and, in fused mode, the new K/V row) ----------------------------
     if (a.fused) {
@@ -105,7 +183,6 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
                 if (!is_key && a.append_mode == 1) continue;
                 const bf16* src = is_key ? a.k_new + (size_t)row * kn_stride + (size_t)kvh * HD
                                          : a.q + (size_t)row * q_stride + (size_t)(kvh * G + job) * HD;
-                const bf16* nw = is_key ? a.k_norm_w : a.q_norm_w;
                 float x[DPL];
                 float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -122,7 +199,7 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
 #pragma unroll
                 for (int j = 0; j < DPL; ++j) {
                     const float normalized = rbf(x[j] * inv);
-                    y[j] = rbf(normalized * bf2f(nw[lane + 32 * j]));
+                    y[j] = rbf(normalized * bf2f(is_key ? nwk[j] : nwq[j]));
                 }
                 // rotate-half pairs (d, d + HD/2): with dims l+32j per lane both members of a
                 // pair sit in the same lane (j and j + DPL/2)
@@ -132,7 +209,7 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
                     float o1, o2;
                     if (a.rope_table != nullptr && pos < a.rope_positions) {
                         // cos | sin of this (position, pair) as two bf16, made by the same code below
-                        const uint32_t cs = a.rope_table[(size_t)pos * (HD / 2) + d];
+                        const uint32_t cs = cs_ready ? cs_pre[j] : a.rope_table[(size_t)pos * (HD / 2) + d];
                         rope_pair_cs(y[j], y[j + DPL / 2], bf_lo(cs), bf_hi(cs), o1, o2);
                     } else {
                         const float angle = static_cast<float>(pos) * rope_inv_freq(d, HD, a.theta);
@@ -181,8 +258,6 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
     // index in any order as long as both operands agree, so a lane loads 16 contiguous bytes of
     // K (8 dims of one token) and feeds them to two MMAs as they come; qa[] holds the query in
     // the matching order: MMA (jj, m) of lane (gid, tig) covers dims 32 jj + 8 tig + 4 m + 0..3.
-    const int gid = lane >> 2;
-    const int tig = lane & 3;
     uint32_t qa[4][2][2];
     if constexpr (HD == 128) {
 #pragma unroll
@@ -211,36 +286,33 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
 #pragma unroll
                 for (int e = 0; e < 4; ++e) o[jb][x][e] = 0.0f;
         if (w0 < c1) {
-            const bf16* kpage = kv_row(w0, false);   // the 16 tokens of a warp share one page
-            const bf16* vpage = kv_row(w0, true);
-            const int4 zero4 = make_int4(0, 0, 0, 0);
-            // K: token 8 nt + gid, dims 32 jj + 8 tig .. + 7
-            int4 kr[2][4];
+            if (early && split == split_first) {
+                // fetched ahead of the wait, except this step's own token (appended above by the
+                // CTA of the last split, visible since the barrier)
+                const int t_new = pos - w0;
+                if (t_new >= 0 && t_new < kWarpTokens) {
+                    const bf16* krow = kv_row(pos, false);
+                    const bf16* vrow = kv_row(pos, true);
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                const int t = 8 * nt + gid;
-                const bool valid = w0 + t < c1;
+                    for (int nt = 0; nt < 2; ++nt)
+                        if (8 * nt + gid == t_new) {
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                    kr[nt][jj] = valid ? *reinterpret_cast<const int4*>(kpage + (size_t)t * kvw + 32 * jj + 8 * tig)
-                                       : zero4;
+                            for (int jj = 0; jj < 4; ++jj)
+                                kr[nt][jj] = *reinterpret_cast<const int4*>(krow + 32 * jj + 8 * tig);
+                        }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int pp = 0; pp < 2; ++pp)
+                            if (8 * h + 2 * tig + pp == t_new) {
+#pragma unroll
+                                for (int jb = 0; jb < 2; ++jb)
+                                    vr[h][pp][jb] = *reinterpret_cast<const int4*>(vrow + 64 * jb + 8 * gid);
+                            }
                 }
+            } else {
+                load_kv(w0, c1);
             }
-            // V: tokens 8 h + 2 tig + p, dims 64 jb + 8 gid .. + 7.  Tokens past the end read as
-            // zero: their probability is zero, but 0 * (stale bits that decode as NaN) is not.
-            int4 vr[2][2][2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int pp = 0; pp < 2; ++pp) {
-                    const int t = 8 * h + 2 * tig + pp;
-                    const bool valid = w0 + t < c1;
-#pragma unroll
-                    for (int jb = 0; jb < 2; ++jb) {
-                        vr[h][pp][jb] = valid ? *reinterpret_cast<const int4*>(vpage + (size_t)t * kvw + 64 * jb + 8 * gid)
-                                              : zero4;
-                    }
-                }
             // scores: s[nt][0..1] = head gid, tokens 8 nt + 2 tig + {0, 1}
             float sc[2][4];
 #pragma unroll
@@ -490,14 +562,32 @@ __global__ void __launch_bounds__(kAttnThreads, 5) decode_attention_kernel(const
     if (tid == 0) a.counters[row * a.kv_heads + kvh] = 0u;   // ready for the next launch
 }
 
+int attention_sm_count() {
+    static int cached[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+    if (cached[device] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n < 1) n = 148;
+        cached[device] = n;
+    }
+    return cached[device];
+}
+
 template <int HD, int G>
 cudaError_t launch_hd_g(const AttentionArgs& a, cudaStream_t stream) {
     const int units = a.units_per_cta > 0 ? a.units_per_cta : 1;
     const dim3 grid((a.max_splits + units - 1) / units, a.kv_heads, a.rows);
+    // fetching ahead of the dependency wait pays when every CTA is resident while the kernel before
+    // this one still runs: one wave of 4 CTAs per SM
+    const bool early = HD == 128 && a.inputs_settled != 0 && a.fused != 0 && a.append_mode == 0
+                       && (size_t)grid.x * grid.y * grid.z <= (size_t)attention_sm_count() * 4;
     if (a.kv.page_table != nullptr) {
-        return launch_pdl(decode_attention_kernel<HD, G, true>, grid, dim3(kAttnThreads), 0, stream, a);
+        if (early) return launch_pdl(decode_attention_kernel<HD, G, true, true>, grid, dim3(kAttnThreads), 0, stream, a);
+        return launch_pdl(decode_attention_kernel<HD, G, true, false>, grid, dim3(kAttnThreads), 0, stream, a);
     }
-    return launch_pdl(decode_attention_kernel<HD, G, false>, grid, dim3(kAttnThreads), 0, stream, a);
+    if (early) return launch_pdl(decode_attention_kernel<HD, G, false, true>, grid, dim3(kAttnThreads), 0, stream, a);
+    return launch_pdl(decode_attention_kernel<HD, G, false, false>, grid, dim3(kAttnThreads), 0, stream, a);
 }
 
 template <int HD>

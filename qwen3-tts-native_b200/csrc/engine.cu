@@ -444,6 +444,10 @@ void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWei
         a.rows = n; a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.head_dim = d.head_dim;
         a.max_splits = splits; a.fused = 1;
         a.rope_table = rope_table; a.rope_positions = Model::kRopePositions;
+        // The kernel directly before attention is the qkv projection; positions, page table and
+        // the older cache rows all date from earlier launches (the kernel ignores this outside
+        // plain decode steps).
+        a.inputs_settled = 1;
         if (shared_cache) {
             // the rows are consecutive positions of one session: every row's K/V goes into the
             // cache first, then every row attends up to its own position
@@ -457,6 +461,7 @@ void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWei
         o.w = lw.o.data; o.scales = lw.o.scales;
         o.x = w.attention.as<bf16>(); o.y = w.hidden.as<bf16>();
         o.in_features = d.q_width; o.out_features = d.hidden; o.rows = n; o.epilogue = EPI_ADD;
+        o.residual_settled = true;     // hidden was last written before the qkv projection
         check_cuda(launch_int8_gemm(o, s), "attention output projection");
 
         GemvArgs u;
@@ -472,6 +477,7 @@ void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWei
         dn.x = w.gate.as<bf16>(); dn.y = w.hidden.as<bf16>();
         dn.in_features = d.intermediate; dn.out_features = d.hidden; dn.rows = n;
         dn.epilogue = EPI_ADD;
+        dn.residual_settled = true;    // hidden was last written by the output projection, two launches up
         check_cuda(launch_int8_gemm(dn, s), "down projection");
     }
 }

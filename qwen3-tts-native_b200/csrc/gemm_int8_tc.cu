@@ -342,9 +342,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     if (tid == 0) TC_TRACE(1);
     // The weight copies (warp 0) start at once: weights never depend on the kernel before this
-    // one.  Everyone else first waits for that kernel to complete (activations, residual).
-    pdl_trigger();
-    if (warp != 0) pdl_wait();
+    // one.  Everyone else first waits for that kernel to complete (activations, residual), and
+    // only then is the kernel after this one let in: every kernel of the library signals its
+    // dependents after its own wait, so that a kernel may read, ahead of its wait, whatever was
+    // written two or more launches upstream.
+    if (warp != 0) {
+        pdl_wait();
+        if (warp == 1) pdl_trigger();
+    }
 
     if (warp == 0) {
         if (elect_one()) {

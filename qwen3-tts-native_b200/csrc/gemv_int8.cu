@@ -62,7 +62,7 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
                  float* __restrict__ output32, const bf16* __restrict__ norm_w,
                  bf16* __restrict__ norm_out, const bf16* __restrict__ bias,
                  bf16* __restrict__ resid, int in_features, int out_features, int epilogue,
-                 float eps) {
+                 float eps, int residual_settled) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* xs = reinterpret_cast<bf16*>(smem_raw);                  // [ROWS][K]
     __shared__ float partial[NORM ? ROWS * kThreads : 1];
@@ -102,6 +102,29 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
         if (GATEUP) pre_scale_up = scales[out_features + first_channel];
     }
 
+    // The RMSNorm weights of the elements this thread normalises (constants, like the weights).
+    constexpr int kNormPre = 8;                       // covers K <= 2048
+    bf16 nw_pre[NORM ? kNormPre : 1];
+    const bool nw_ready = NORM && in_features <= kNormPre * kThreads;
+    if (NORM && nw_ready) {
+#pragma unroll
+        for (int u = 0; u < kNormPre; ++u) {
+            const int i = tid + u * kThreads;
+            if (i < in_features) nw_pre[u] = norm_w[i];
+        }
+    }
+    // The value a residual epilogue adds to, when its writer is known to be long done.
+    float pre_resid[ROWS];
+    const bool resid_ready = !GATEUP && residual_settled != 0 && lane == 0 && first_channel < out_features
+                             && (epilogue == EPI_ADD || epilogue == EPI_BIAS_ADD);
+    if (resid_ready) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const size_t o = (size_t)r * out_features + first_channel;
+            pre_resid[r] = bf2f(epilogue == EPI_ADD ? output[o] : resid[o]);
+        }
+    }
+
     // Launched with programmatic stream serialisation: this grid may start while the one before
     // it in the stream is still running.  Everything above touches only the weights; from here on
     // the previous grid's output is read, so wait for it to complete (a no-op when the launch
@@ -127,9 +150,17 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
             const float total = tree_sum_256(partial + r * kThreads, lane);
             const float inv = rsqrtf(total / static_cast<float>(in_features) + eps);
             const bf16* xr = input + (size_t)r * in_features;
-            for (int i = tid; i < in_features; i += kThreads) {
+            for (int i = tid, u = 0; i < in_features; i += kThreads, ++u) {
                 const float normalized = rbf(bf2f(xr[i]) * inv);
-                const bf16 o = f2bf(normalized * bf2f(norm_w[i]));
+                bf16 nw;
+                if (nw_ready) {
+                    nw = nw_pre[0];
+#pragma unroll
+                    for (int k = 1; k < kNormPre; ++k) nw = (u == k) ? nw_pre[NORM ? k : 0] : nw;
+                } else {
+                    nw = norm_w[i];
+                }
+                const bf16 o = f2bf(normalized * bf2f(nw));
                 xs[(size_t)r * in_features + i] = o;
                 if (norm_out != nullptr && blockIdx.x == 0) norm_out[(size_t)r * in_features + i] = o;
             }
@@ -207,7 +238,8 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
                     if (output32 != nullptr) output32[o] = val;
                     output[o] = f2bf(val);
                 } else if (epilogue == EPI_ADD) {
-                    const float val = fmaf(a, scale, bf2f(output[o]));
+                    const float base = (first && resid_ready) ? pre_resid[r] : bf2f(output[o]);
+                    const float val = fmaf(a, scale, base);
                     if (output32 != nullptr) output32[o] = val;
                     output[o] = f2bf(val);
                 } else if (epilogue == EPI_BIAS) {
@@ -221,7 +253,7 @@ gemv_rows_kernel(const int8_t* __restrict__ weight, const float* __restrict__ sc
                     output[o] = f2bf(val);
                 } else {  // EPI_BIAS_ADD
                     const float t = rbf(rbf(a * scale) + bf2f(bias[channel]));
-                    const float val = bf2f(resid[o]) + t;
+                    const float val = ((first && resid_ready) ? pre_resid[r] : bf2f(resid[o])) + t;
                     if (output32 != nullptr) output32[o] = val;
                     resid[o] = f2bf(val);
                 }
@@ -284,7 +316,7 @@ cudaError_t launch_one(const GemvArgs& a, const bf16* x, bf16* y, float* y32, bf
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, a.w, a.scales, x, y, y32, a.norm_w, norm_out, a.bias, resid,
-                              a.in_features, a.out_features, a.epilogue, a.eps);
+                              a.in_features, a.out_features, a.epilogue, a.eps, a.residual_settled ? 1 : 0);
 }
 
 template <bool GATEUP, bool NORM>
@@ -324,14 +356,29 @@ bool pdl_enabled() {
 }
 
 cudaError_t launch_int8_gemm(const GemvArgs& a, cudaStream_t stream) {
-    // The bulk-copy batch-1 kernel is opt-in (QWEN3_TTS_B1_GEMV=bulk): alone it matches the SIMT
-    // kernel, inside a captured frame it measured slower, so the SIMT kernel stays the default.
-    static const bool b1_enabled = [] {
+    // The bulk-copy batch-1 kernel is opt-in.  Alone, in a chain of its own kind, it is the
+    // faster one on matrices that come from HBM (its weights are on their way into shared memory
+    // while the kernel before it still runs: 4.46 us against 4.85 us on 6144 x 2048); inside a
+    // captured frame, between attention and glue kernels and on matrices that sit in L2, the SIMT
+    // kernel's many warps win, so that one is the default.  QWEN3_TTS_B1_GEMV = "bulk": every
+    // supported shape; "large": rows of at most 2048 weights over at least
+    // QWEN3_TTS_B1_BULK_MIN_MB (default 8) megabytes.
+    static const int b1_mode = [] {
         const char* v = std::getenv("QWEN3_TTS_B1_GEMV");
-        return v != nullptr && std::strcmp(v, "bulk") == 0;
+        if (v != nullptr && std::strcmp(v, "bulk") == 0) return 2;
+        if (v != nullptr && std::strcmp(v, "large") == 0) return 1;
+        return 0;
+    }();
+    static const size_t b1_min_bytes = [] {
+        const char* v = std::getenv("QWEN3_TTS_B1_BULK_MIN_MB");
+        const long mb = v != nullptr ? std::strtol(v, nullptr, 10) : 8;
+        return static_cast<size_t>(mb < 0 ? 0 : mb) << 20;
     }();
     if (gemm_tc_supports(a)) return launch_int8_gemm_tc(a, stream);
-    if (b1_enabled && gemv_b1_supports(a)) return launch_int8_gemv_b1(a, stream);
+    if (b1_mode != 0 && gemv_b1_supports(a)) {
+        const size_t bytes = (size_t)a.in_features * a.out_features * (a.epilogue == EPI_GATE_UP_SILU ? 2 : 1);
+        if (b1_mode == 2 || (a.in_features <= 2048 && bytes >= b1_min_bytes)) return launch_int8_gemv_b1(a, stream);
+    }
     return launch_int8_gemm_simt(a, stream);
 }
 

@@ -31,26 +31,38 @@ constexpr int kWaitLimit = 1 << 22;          // mbarrier try_wait attempts befor
 
 __device__ unsigned int g_gemv_b1_errors = 0;
 
-// Optional phase timestamps for study builds (-DQ3T_B1_TRACE): lane 0 of every warp of the first
-// CTAs writes %globaltimer at the marked points.  Compiled out otherwise.
+// Optional phase timestamps for study builds (-DQ3T_B1_TRACE): lane 0 of every warp of every
+// 37th CTA writes %globaltimer at the marked points.  Compiled out otherwise.
 #ifdef Q3T_B1_TRACE
 __device__ unsigned long long g_b1_trace[8 * 8 * 16];
-__device__ unsigned long long g_b1_cta_times[1024 * 2];     // per CTA: dependency wait returned, last warp done
-#define B1_TRACE_CTA(which)                                                                     \
-    do {                                                                                        \
-        if ((threadIdx.x & 31) == 0 && blockIdx.x < 1024) {                                       \
-            unsigned long long t_;                                                              \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
-            if (which) atomicMax(&g_b1_cta_times[blockIdx.x * 2 + 1], t_);                        \
-            else if (threadIdx.x == 0) g_b1_cta_times[blockIdx.x * 2] = t_;                      \
-        }                                                                                       \
-    } while (0)
 #define B1_TRACE(slot)                                                                          \
     do {                                                                                        \
-        if ((threadIdx.x & 31) == 0 && blockIdx.x < 8 && (slot) < 16) {                           \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x % 37 == 0 && (slot) < 16) {                     \
             unsigned long long t_;                                                              \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
-            g_b1_trace[(blockIdx.x * 8 + threadIdx.x / 32) * 16 + (slot)] = t_;                   \
+            g_b1_trace[(blockIdx.x / 37 * 8 + threadIdx.x / 32) * 16 + (slot)] = t_;              \
+        }                                                                                       \
+    } while (0)
+__device__ unsigned long long g_b1_cta_times[8 * 256 * 2];   // [launch % 8][CTA]: dependency wait returned, last warp done
+__device__ unsigned int g_b1_smid[8 * 256];
+__device__ unsigned long long g_b1_start[8 * 256];
+__device__ unsigned int g_b1_launches;                        // launches completed (CTA 0 counts at exit)
+#define B1_TRACE_CTA(which)                                                                     \
+    do {                                                                                        \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x < 256) {                                        \
+            unsigned long long t_;                                                              \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+            if (!(which)) trace_launch_ = *reinterpret_cast<volatile unsigned int*>(&g_b1_launches); \
+            unsigned long long* e_ = &g_b1_cta_times[((trace_launch_ & 7) * 256 + blockIdx.x) * 2]; \
+            if (which) atomicMax(e_ + 1, t_);                                                    \
+            else if (threadIdx.x == 0) {                                                         \
+                e_[0] = t_;                                                                      \
+                unsigned int sm_;                                                                \
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_));                                 \
+                g_b1_smid[(trace_launch_ & 7) * 256 + blockIdx.x] = sm_;                           \
+                g_b1_start[(trace_launch_ & 7) * 256 + blockIdx.x] = trace_start_;                 \
+            }                                                                                    \
+            if ((which) && blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_b1_launches, 1u);     \
         }                                                                                       \
     } while (0)
 #else
@@ -161,7 +173,11 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
     using R = Ring<VPL>;
     constexpr int K = R::kK;
     constexpr int STAGES = R::kStages;
-    pdl_trigger();   // the successor may become resident (and fetch its own weights) right away
+#ifdef Q3T_B1_TRACE
+    unsigned int trace_launch_ = 0;
+    unsigned long long trace_start_;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(trace_start_));
+#endif
     B1_TRACE(0);
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* ring = smem;
@@ -225,10 +241,12 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
 
     // Two of these CTAs fit on an SM, so under programmatic stream serialisation the next GEMV of
     // the stream is resident while this one computes: its weight slice is already in its rings
-    // when this grid completes.  Only the weights were touched so far; the activations below
-    // are the predecessor's output.
+    // when this grid completes.  Only the weights and scales were touched so far; the activations
+    // below are the predecessor's output.
     B1_TRACE(1);
     pdl_wait();
+    pdl_trigger();   // after the wait, as everywhere in the library; the successor's CTAs move in as this
+                     // grid's predecessors' CTAs leave and fetch their weights while this one computes
     B1_TRACE(2);
     B1_TRACE_CTA(0);
 
@@ -281,8 +299,10 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
 
     const unsigned long long neg_bias = pack2(-8388736.0f, -8388736.0f);   // -(2^23 + 128)
     B1_TRACE(3);
-    // The warp reductions of up to kGroup consecutive pairs run together: their shuffle chains
-    // are independent, so a group pays the five-step latency once.
+    // The warp reductions of up to kGroup consecutive pairs run together (their shuffle chains
+    // are independent, so a group pays the five-step latency once), and the group's results are
+    // then spread over lanes 0..2*kGroup-1, which run the epilogue side by side.  The pair loop
+    // itself is not unrolled: one copy of the arithmetic in the instruction cache.
     constexpr int kGroup = 4;
     bool failed = false;
     int it = 0;
@@ -296,12 +316,15 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
       for (int gi = 0; gi < kGroup; ++gi) {
         pa[gi] = 0.0f;
         pb[gi] = 0.0f;
-        if (pair >= p1 || failed) continue;
+      }
+#pragma unroll 1
+      for (int gi = 0; gi < kGroup; ++gi) {
+        if (pair >= p1) break;
         const int stage = it % STAGES;
         const uint32_t parity = (it / STAGES) & 1;
         if (!mbar_wait_bounded(&my_bars[stage], parity)) {
             failed = true;
-            continue;
+            break;
         }
         const unsigned char* a = my_ring + (size_t)stage * R::kPairBytes;
         B1_TRACE(4 + 3 * it);
@@ -375,8 +398,13 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
             issue(stage, next);
         }
         B1_TRACE(5 + 3 * it);
-        pa[gi] = ra;
-        pb[gi] = rb;
+#pragma unroll
+        for (int k = 0; k < kGroup; ++k) {      // static indices keep the partials in registers
+            if (gi == k) {
+                pa[k] = ra;
+                pb[k] = rb;
+            }
+        }
         pair += kWarps;
         ++it;
         done = gi + 1;
@@ -391,29 +419,36 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
         }
       }
       B1_TRACE(13);
+      // lane 2g takes the first row of the group's pair g, lane 2g+1 its second row
+      float mine = 0.0f;
 #pragma unroll
       for (int gi = 0; gi < kGroup; ++gi) {
-        const int git = base_it + gi;
-        const int gpair = base_pair + kWarps * gi;
-        float scale_a = __shfl_sync(0xffffffffu, my_scale, (2 * git) & 31);
-        float scale_b = __shfl_sync(0xffffffffu, my_scale, (2 * git + 1) & 31);
-        if (gi < done && lane == 0) {
-            if (git >= kScaleSlots) {     // slices longer than the prefetched slots
-                scale_a = GATEUP ? p.scales[gpair] : p.scales[2 * gpair];
-                scale_b = GATEUP ? p.scales[N + gpair] : (2 * gpair + 1 < N ? p.scales[2 * gpair + 1] : 0.0f);
-            }
-            if (GATEUP) {
-                const float gate = pa[gi] * scale_a;
-                const float up = pb[gi] * scale_b;
-                const float activated = gate / (1.0f + expf(-gate));
-                const float val = activated * up;
-                if (p.y32 != nullptr) p.y32[gpair] = val;
-                p.y[gpair] = f2bf(val);
-            } else {
-                const int c = 2 * gpair;
-                store_result(p, c, pa[gi], scale_a);
-                if (c + 1 < N) store_result(p, c + 1, pb[gi], scale_b);
-            }
+        const float a0 = __shfl_sync(0xffffffffu, pa[gi], 0);
+        const float b0 = __shfl_sync(0xffffffffu, pb[gi], 0);
+        if (lane == 2 * gi) mine = a0;
+        if (lane == 2 * gi + 1) mine = b0;
+      }
+      const int slot = 2 * base_it + lane;                 // which prefetched scale is this lane's
+      float scale = __shfl_sync(0xffffffffu, my_scale, slot & 31);
+      const bool active = lane < 2 * done;
+      const int gpair = base_pair + kWarps * (lane >> 1);
+      const int second = lane & 1;
+      if (GATEUP) {
+        if (active && slot >= 2 * kScaleSlots) scale = p.scales[second ? N + gpair : gpair];
+        const float scaled = mine * scale;
+        const float up = __shfl_down_sync(0xffffffffu, scaled, 1);
+        if (active && !second) {
+            const float gate = scaled;
+            const float activated = gate / (1.0f + expf(-gate));
+            const float val = activated * up;
+            if (p.y32 != nullptr) p.y32[gpair] = val;
+            p.y[gpair] = f2bf(val);
+        }
+      } else {
+        const int c = 2 * gpair + second;
+        if (active && c < N) {
+            if (slot >= 2 * kScaleSlots) scale = p.scales[c];
+            store_result(p, c, mine, scale);
         }
       }
       B1_TRACE(14);

@@ -51,6 +51,10 @@ __device__ __forceinline__ float warp_sum_xor(float v) {
 // the stream still runs.  pdl_wait() returns once the predecessor has completed and its writes
 // are visible (at once when the launch was an ordinary one); nothing the predecessor wrote may
 // be read before it.  pdl_trigger() lets the successor start its own preamble.
+// Library-wide rule: a kernel calls pdl_trigger() only after its own pdl_wait() has returned (in
+// the calling thread).  When a grid starts, every grid two or more launches upstream of it has
+// therefore completed, and what those wrote may be read ahead of the wait; only the immediate
+// predecessor's output has to wait.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

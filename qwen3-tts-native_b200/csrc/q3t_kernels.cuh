@@ -38,6 +38,11 @@ struct GemvArgs {
     int rows = 0;                    // 1..kMaxRows
     int epilogue = EPI_PLAIN;
     float eps = kRmsEps;
+    // EPI_ADD / EPI_BIAS_ADD: the accumulated-into values (y, resid) were last written two or more
+    // launches upstream of this one in its stream (never by the launch directly before it), so
+    // they may be fetched ahead of the dependency wait.  Set only by callers that build the whole
+    // launch sequence; false is always correct.
+    bool residual_settled = false;
 };
 
 // Launch with programmatic stream serialisation (QWEN3_TTS_PDL=0 turns it into an ordinary
@@ -147,6 +152,11 @@ struct AttentionArgs {
     int append_mode = 0;                // fused only.  0: append, then attend (decode).  1: append only.
                                         // 2: attend only.  Rows that share one cache (a prompt chunk)
                                         // need every row's K/V in place before any row attends: 1, then 2.
+    // Decode steps only (fused, append_mode 0): positions, the page table and every cache row older
+    // than this step's token were written two or more launches upstream in the stream, so the kernel
+    // may fetch them ahead of its dependency wait (only q / k_new / v_new come from the launch directly
+    // before).  Set by callers that build the whole launch sequence; 0 is always correct.
+    int inputs_settled = 0;
     int units_per_cta = 0;              // splits one CTA walks (0: chosen from the grid size); no effect on results
     float eps = kRmsEps;
     float theta = kRopeTheta;
