@@ -356,28 +356,34 @@ bool pdl_enabled() {
 }
 
 cudaError_t launch_int8_gemm(const GemvArgs& a, cudaStream_t stream) {
-    // The bulk-copy batch-1 kernel is opt-in.  Alone, in a chain of its own kind, it is the
-    // faster one on matrices that come from HBM (its weights are on their way into shared memory
-    // while the kernel before it still runs: 4.46 us against 4.85 us on 6144 x 2048); inside a
-    // captured frame, between attention and glue kernels and on matrices that sit in L2, the SIMT
-    // kernel's many warps win, so that one is the default.  QWEN3_TTS_B1_GEMV = "bulk": every
-    // supported shape; "large": rows of at most 2048 weights over at least
-    // QWEN3_TTS_B1_BULK_MIN_MB (default 8) megabytes.
+    // Batch-1 dispatch between the SIMT kernel and the bulk-copy kernel.  The bulk kernel keeps a
+    // CTA's whole weight slice on its way into shared memory while the kernel before it still
+    // runs; it wins when the matrix comes from HBM and the slice of an SM fits its 96 KB of rings
+    // (6144 x 2048: 3.9 us against 4.9 us).  Larger matrices refill the rings behind eight warps and
+    // lose to the SIMT kernel's many warps, and matrices that sit in L2 during a frame gain nothing,
+    // so by default only plain and residual epilogues without the RMSNorm prologue, rows of at
+    // most 2048 weights and 8..14 MB take it.  QWEN3_TTS_B1_GEMV = "bulk": every supported shape;
+    // "simt": never; QWEN3_TTS_B1_BULK_MIN_MB moves the lower bound.
     static const int b1_mode = [] {
         const char* v = std::getenv("QWEN3_TTS_B1_GEMV");
         if (v != nullptr && std::strcmp(v, "bulk") == 0) return 2;
-        if (v != nullptr && std::strcmp(v, "large") == 0) return 1;
-        return 0;
+        if (v != nullptr && std::strcmp(v, "simt") == 0) return 0;
+        if (v != nullptr && std::strcmp(v, "fit") == 0) return 3;   // every epilogue, slice must fit the rings
+        return 1;
     }();
     static const size_t b1_min_bytes = [] {
         const char* v = std::getenv("QWEN3_TTS_B1_BULK_MIN_MB");
         const long mb = v != nullptr ? std::strtol(v, nullptr, 10) : 8;
         return static_cast<size_t>(mb < 0 ? 0 : mb) << 20;
     }();
+    constexpr size_t b1_max_bytes = (size_t)14 << 20;      // 148 SMs x 96 KB of rings
     if (gemm_tc_supports(a)) return launch_int8_gemm_tc(a, stream);
     if (b1_mode != 0 && gemv_b1_supports(a)) {
         const size_t bytes = (size_t)a.in_features * a.out_features * (a.epilogue == EPI_GATE_UP_SILU ? 2 : 1);
-        if (b1_mode == 2 || (a.in_features <= 2048 && bytes >= b1_min_bytes)) return launch_int8_gemv_b1(a, stream);
+        const bool plain = a.norm_w == nullptr && (a.epilogue == EPI_PLAIN || a.epilogue == EPI_ADD);
+        if (b1_mode == 2 || ((plain || b1_mode == 3) && a.in_features <= 2048 && bytes >= b1_min_bytes && bytes <= b1_max_bytes)) {
+            return launch_int8_gemv_b1(a, stream);
+        }
     }
     return launch_int8_gemm_simt(a, stream);
 }
