@@ -386,7 +386,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         # ---- batch-1 int8 GEMV, configs[0]: 16 weight images (201 MB > L2) round-robin --------------
         g = native.benchmark_int8_gemv(local_rank, 2048, 6144, rows=1, buffers=16, iterations=4000)
         gemv_s = g.mean_launch_microseconds * 1e-6
-        line["roofline"] = {"bound": "hbm", "kernel": "gemv_rows_kernel<1> 2048->6144 (configs[0])",
+        line["roofline"] = {"bound": "hbm", "kernel": "gemv_b1_kernel<4> 2048->6144 (configs[0])",
                             "achieved": GEMV_BYTES / gemv_s / 1e9, "peak": hbm_peak, "unit": "GB/s",
                             "frac": GEMV_BYTES / gemv_s / 1e9 / hbm_peak, "peak_kind": peak_kind,
                             "frac_of_8TBs": GEMV_BYTES / gemv_s / 8.0e12,
