@@ -15,23 +15,58 @@ constexpr int kThreads = 256;
 __global__ void __launch_bounds__(kThreads)
 rms_norm_rows_kernel(const bf16* __restrict__ input, const bf16* __restrict__ weight,
                      bf16* __restrict__ output, int width, float eps) {
+    // the norm weights are constants: requested before the wait for the rows' producer
+    constexpr int kPre = 8;                              // widths up to 2048 stay in registers
+    const bool in_registers = width <= kPre * kThreads;
+    bf16 wpre[kPre];
+    if (in_registers) {
+#pragma unroll
+        for (int u = 0; u < kPre; ++u) {
+            const int i = threadIdx.x + u * kThreads;
+            if (i < width) wpre[u] = weight[i];
+        }
+    }
     pdl_wait();
     pdl_trigger();
     __shared__ float partial[kThreads];
     const bf16* xr = input + (size_t)blockIdx.x * width;
     bf16* yr = output + (size_t)blockIdx.x * width;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < width; i += kThreads) {
-        const float v = bf2f(xr[i]);
-        ss = fmaf(v, v, ss);
+    float xpre[kPre];
+    if (in_registers) {
+#pragma unroll
+        for (int u = 0; u < kPre; ++u) {
+            const int i = threadIdx.x + u * kThreads;
+            xpre[u] = i < width ? bf2f(xr[i]) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < kPre; ++u) {
+            if (threadIdx.x + u * kThreads < width) ss = fmaf(xpre[u], xpre[u], ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += kThreads) {
+            const float v = bf2f(xr[i]);
+            ss = fmaf(v, v, ss);
+        }
     }
     partial[threadIdx.x] = ss;
     __syncthreads();
     const float total = tree_sum_256(partial, threadIdx.x % kWarp);
     const float inv = rsqrtf(total / static_cast<float>(width) + eps);
-    for (int i = threadIdx.x; i < width; i += kThreads) {
-        const float normalized = rbf(bf2f(xr[i]) * inv);
-        yr[i] = f2bf(normalized * bf2f(weight[i]));
+    if (in_registers) {
+#pragma unroll
+        for (int u = 0; u < kPre; ++u) {
+            const int i = threadIdx.x + u * kThreads;
+            if (i < width) {
+                const float normalized = rbf(xpre[u] * inv);
+                yr[i] = f2bf(normalized * bf2f(wpre[u]));
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += kThreads) {
+            const float normalized = rbf(bf2f(xr[i]) * inv);
+            yr[i] = f2bf(normalized * bf2f(weight[i]));
+        }
     }
 }
 

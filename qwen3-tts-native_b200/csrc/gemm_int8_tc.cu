@@ -82,6 +82,7 @@ struct TcParams {
     int splits;               // K-slices per channel tile = CTAs per cluster
     int chunks;               // K chunks of 64 in the whole contraction
     int tiles;
+    int residual_settled;     // GemvArgs::residual_settled
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -223,15 +224,16 @@ __device__ __forceinline__ void dequant4(uint32_t word, uint32_t& lo, uint32_t& 
     hi = __byte_perm(static_cast<uint32_t>(b), static_cast<uint32_t>(b >> 32), 0x7632);
 }
 
-__device__ __forceinline__ float finish(const TcParams& p, float acc, float scale, int channel, size_t o) {
+__device__ __forceinline__ float finish(const TcParams& p, float acc, float scale, int channel, size_t o,
+                                        bool have_base, float base) {
     switch (p.epilogue) {
-        case EPI_ADD: return fmaf(acc, scale, bf2f(p.y[o]));
+        case EPI_ADD: return fmaf(acc, scale, have_base ? base : bf2f(p.y[o]));
         case EPI_BIAS: return rbf(acc * scale) + bf2f(p.bias[channel]);
         case EPI_BIAS_SILU: {
             float v = rbf(acc * scale) + bf2f(p.bias[channel]);
             return __fdividef(v, 1.0f + __expf(-v));
         }
-        case EPI_BIAS_ADD: return bf2f(p.resid[o]) + rbf(rbf(acc * scale) + bf2f(p.bias[channel]));
+        case EPI_BIAS_ADD: return (have_base ? base : bf2f(p.resid[o])) + rbf(rbf(acc * scale) + bf2f(p.bias[channel]));
         default: return acc * scale;
     }
 }
@@ -346,7 +348,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     // only then is the kernel after this one let in: every kernel of the library signals its
     // dependents after its own wait, so that a kernel may read, ahead of its wait, whatever was
     // written two or more launches upstream.
-    if (warp != 0) {
+    // The dequantisers (warps 4..) touch only weights and tensor memory until the K-slice sum, so
+    // they too run ahead and wait there.
+    if (warp >= 1 && warp <= 3) {
         pdl_wait();
         if (warp == 1) pdl_trigger();
     }
@@ -492,7 +496,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
 
     // ---- the K-slices of a channel tile live in the CTAs of one cluster; CTA s owns rows
     // [s * rows_share, (s + 1) * rows_share) and sums them over all slices in slice order ----------
-    if (warp == 0) pdl_wait();
+    // The values a residual epilogue adds to, requested before the cluster barrier hides their
+    // latency (and, when their writer is known to be long done, before the dependency wait).
+    constexpr int kBasePre = 3;
+    float base_pre[kBasePre];
+    const bool base_wanted = !GATEUP && channel < N && (p.epilogue == EPI_ADD || p.epilogue == EPI_BIAS_ADD);
+    const bf16* base_src = p.epilogue == EPI_ADD ? p.y : p.resid;
+    auto fetch_bases = [&]() {
+        const int row0 = split * rows_share;
+        const int my_rows = min(rows_share, p.rows - row0);
+#pragma unroll
+        for (int u = 0; u < kBasePre; ++u) {
+            const int j = tid / kPerRow + u * (kTcThreads / kPerRow);
+            base_pre[u] = j < my_rows ? bf2f(base_src[(size_t)(row0 + j) * N + channel]) : 0.0f;
+        }
+    };
+    if (base_wanted && p.residual_settled != 0) fetch_bases();
+    if (warp == 0 || warp >= 4) pdl_wait();
+    if (base_wanted && p.residual_settled == 0) fetch_bases();
     __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     if (tid == 0) TC_TRACE(57);
@@ -501,8 +522,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     if (*abort_flag == 0 && channel < N) {
         const int row0 = split * rows_share;
         const int my_rows = min(rows_share, p.rows - row0);
+        int u = 0;
 #pragma unroll 2
-        for (int j = tid / kPerRow; j < my_rows; j += kTcThreads / kPerRow) {
+        for (int j = tid / kPerRow; j < my_rows; j += kTcThreads / kPerRow, ++u) {
             const float* at = red + j * kTileN + c;
             float acc = at[0], acc_up = GATEUP ? at[64] : 0.0f;
             if (p.splits > 1) {
@@ -530,7 +552,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 // hardware exp2/reciprocal (good to about 2^-21); this path is compared at bf16 tolerance
                 val = __fdividef(gate, 1.0f + __expf(-gate)) * up;
             } else {
-                val = finish(p, acc, scale, channel, out);
+                const float base = u == 0 ? base_pre[0] : (u == 1 ? base_pre[1] : base_pre[2]);
+                val = finish(p, acc, scale, channel, out, base_wanted && u < kBasePre, base);
             }
             if (p.y32 != nullptr) p.y32[out] = val;
             if (!GATEUP && p.epilogue == EPI_BIAS_ADD) p.resid[out] = f2bf(val);
@@ -718,6 +741,7 @@ cudaError_t launch_int8_gemm_tc(const GemvArgs& a, cudaStream_t stream) {
     p.scales = a.scales; p.y = a.y; p.y32 = a.y32; p.bias = a.bias; p.resid = a.resid;
     p.out_features = N; p.rows = a.rows; p.epilogue = a.epilogue;
     p.tiles = gateup ? (N + 63) / 64 : (N + kTileN - 1) / kTileN;
+    p.residual_settled = a.residual_settled ? 1 : 0;
     const int nk = K / kBK;
     // K-slices per tile = cluster size: as many as still let every cluster be resident at once (a
     // second wave would double the time); slices and row shares may be ragged
