@@ -353,6 +353,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     if (warp >= 1 && warp <= 3) {
         pdl_wait();
         if (warp == 1) pdl_trigger();
+        if (tid == 32) TC_TRACE(2);
     }
 
     if (warp == 0) {
@@ -491,6 +492,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                     }
                 }
             }
+            if (t == 0 && group == 0) TC_TRACE(62);
         }
     }
 
@@ -513,6 +515,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     };
     if (base_wanted && p.residual_settled != 0) fetch_bases();
     if (warp == 0 || warp >= 4) pdl_wait();
+    if (tid == 128) TC_TRACE(63);
     if (base_wanted && p.residual_settled == 0) fetch_bases();
     __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -545,6 +548,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 }
             }
             const size_t out = (size_t)(row0 + j) * N + channel;
+            if (tid == 0 && u < 3) TC_TRACE(100 + 3 * u);
             float val;
             if (GATEUP) {
                 const float gate = acc * scale;
@@ -556,8 +560,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 val = finish(p, acc, scale, channel, out, base_wanted && u < kBasePre, base);
             }
             if (p.y32 != nullptr) p.y32[out] = val;
+            if (tid == 0 && u < 3) TC_TRACE(101 + 3 * u);
             if (!GATEUP && p.epilogue == EPI_BIAS_ADD) p.resid[out] = f2bf(val);
             else p.y[out] = f2bf(val);
+            if (tid == 0 && u < 3) TC_TRACE(102 + 3 * u);
         }
     }
     if (tid == 0) TC_TRACE(59);
