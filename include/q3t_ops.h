@@ -129,6 +129,33 @@ QWEN3_TTS_API int32_t q3t_pump_statistics(Q3tFramePump* pump, uint64_t* batches,
  * first (sessions are pinned for life, docs/ARCHITECTURE.md:285 of the reference). */
 QWEN3_TTS_API int32_t q3t_pick_device(const int32_t* active_sessions_per_device, int32_t devices);
 
+/* ---- weight image -------------------------------------------------------------------------
+ * The reference quantizes every decode matrix on every GPU while the checkpoint is uploaded
+ * (talker.cu:564-668, int8_gemv.cu:20-52).  With one replica per GPU the work can be done once:
+ * the rank that received the bf16 checkpoint through qwen3_tts_model_upload_tensor exposes where
+ * each tensor lives on its device in decode form (int8 rows + fp32 row scales for the projection
+ * matrices, bf16 for norms, biases and embeddings); the other ranks ask their own, still empty,
+ * model for the same tensor's storage, fill it (ncclBroadcast, a peer copy, a file read) and
+ * declare it loaded.  qwen3_tts_model_finalize then accepts the model as if every tensor had been
+ * uploaded.  Stacked matrices (q/k/v, gate/up) are addressed by their checkpoint names; each
+ * name is a contiguous row range of the stacked storage. */
+typedef struct Q3tTensorImage {
+    uint32_t struct_size;      /* sizeof(Q3tTensorImage), set by the caller */
+    int32_t device_index;
+    void* data;                /* device pointer */
+    uint64_t data_bytes;
+    float* scales;             /* device pointer, null unless quantized */
+    uint64_t scales_bytes;
+    int32_t quantized;         /* 1: data is int8 [rows][cols], scales is fp32 [rows] */
+    int32_t loaded;            /* 1: uploaded or adopted already */
+} Q3tTensorImage;
+QWEN3_TTS_API int32_t q3t_model_tensor_image(Qwen3TtsModelHandle model, const char* name,
+                                             Q3tTensorImage* image, char* error, size_t error_capacity);
+/* Declares the tensor's device storage filled by the caller; counts like an upload (a second
+ * upload or adoption of the same name is an error, as in the reference's upload path). */
+QWEN3_TTS_API int32_t q3t_model_adopt_tensor(Qwen3TtsModelHandle model, const char* name, char* error,
+                                             size_t error_capacity);
+
 /* A chain of 1..8 dependent batch-1 GEMVs (rows == 1, in_features a multiple of 1024 up to 6144)
  * in one persistent cooperative launch: op i+1 may read what op i wrote.  Bit-identical to issuing
  * the same descriptors one by one through q3t_launch_int8_gemm_ex.  Launches through this entry

@@ -171,6 +171,30 @@ int32_t qwen3_tts_model_upload_tensor(Qwen3TtsModelHandle handle, const char* na
     }, QWEN3_TTS_TALKER_STATUS_MODEL, error, error_capacity);
 }
 
+int32_t q3t_model_tensor_image(Qwen3TtsModelHandle handle, const char* name, Q3tTensorImage* image,
+                               char* error, size_t error_capacity) {
+    if (image == nullptr || image->struct_size != sizeof(Q3tTensorImage)) {
+        write_error(error, error_capacity, "tensor image output is null or has the wrong struct_size");
+        return QWEN3_TTS_TALKER_STATUS_INVALID_ARGUMENT;
+    }
+    return protect([&] {
+        const Model::TensorImage t = model_of(handle)->tensor_image(name);
+        image->data = t.data;
+        image->data_bytes = t.data_bytes;
+        image->scales = t.scales;
+        image->scales_bytes = t.scales_bytes;
+        image->quantized = t.quantized ? 1 : 0;
+        image->loaded = t.loaded ? 1 : 0;
+        image->device_index = model_of(handle)->device();
+    }, QWEN3_TTS_TALKER_STATUS_MODEL, error, error_capacity);
+}
+
+int32_t q3t_model_adopt_tensor(Qwen3TtsModelHandle handle, const char* name, char* error,
+                               size_t error_capacity) {
+    return protect([&] { model_of(handle)->adopt_tensor(name); }, QWEN3_TTS_TALKER_STATUS_MODEL, error,
+                   error_capacity);
+}
+
 int32_t qwen3_tts_model_finalize(Qwen3TtsModelHandle handle, Qwen3TtsModelMemory* memory,
                                  char* error, size_t error_capacity) {
     if (memory == nullptr) {

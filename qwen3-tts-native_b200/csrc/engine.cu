@@ -362,6 +362,46 @@ void Model::upload_tensor(const char* name, const void* data, uint64_t bytes, in
     ++tensor_count_;
 }
 
+Model::TensorImage Model::tensor_image(const char* name) const {
+    if (name == nullptr) throw std::runtime_error("tensor name is null");
+    const auto found = specs_.find(name);
+    if (found == specs_.end()) {
+        throw std::runtime_error(std::string("tensor is not part of the talker checkpoint: ") + name);
+    }
+    const Spec& spec = found->second;
+    uint64_t elements = 1;
+    for (uint64_t d : spec.shape) elements *= d;
+    TensorImage image;
+    image.data = spec.destination;
+    image.quantized = spec.quantize;
+    image.loaded = spec.seen;
+    if (spec.quantize) {
+        image.data_bytes = elements;                          // one int8 per weight
+        image.scales = spec.scales;
+        image.scales_bytes = spec.shape[0] * sizeof(float);   // one scale per output row
+    } else {
+        image.data_bytes = elements * sizeof(bf16);
+    }
+    return image;
+}
+
+void Model::adopt_tensor(const char* name) {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(adopt)");
+    if (finalized_) throw std::runtime_error("model weights are already finalized");
+    if (name == nullptr) throw std::runtime_error("tensor name is null");
+    const auto found = specs_.find(name);
+    if (found == specs_.end()) {
+        throw std::runtime_error(std::string("tensor is not part of the talker checkpoint: ") + name);
+    }
+    Spec& spec = found->second;
+    if (spec.seen) throw std::runtime_error(std::string("duplicate tensor upload: ") + name);
+    uint64_t elements = 1;
+    for (uint64_t d : spec.shape) elements *= d;
+    spec.seen = true;
+    weight_bytes_ += elements * sizeof(bf16);     // counted as the checkpoint tensor it stands for
+    ++tensor_count_;
+}
+
 void Model::finalize(uint64_t* weight_bytes, uint32_t* tensor_count) {
     check_cuda(cudaSetDevice(device_), "cudaSetDevice(finalize)");
     if (finalized_) throw std::runtime_error("model weights are already finalized");

@@ -149,6 +149,19 @@ public:
     Model(const Model&) = delete;
     Model& operator=(const Model&) = delete;
 
+    // Where a checkpoint tensor lives on the device in the form the decode step reads (int8 rows
+    // + fp32 row scales for the projection matrices, bf16 otherwise), and a way to declare such
+    // storage filled by other means than upload_tensor (a broadcast from the rank that quantized).
+    struct TensorImage {
+        void* data = nullptr;
+        uint64_t data_bytes = 0;
+        float* scales = nullptr;
+        uint64_t scales_bytes = 0;
+        bool quantized = false;
+        bool loaded = false;
+    };
+    TensorImage tensor_image(const char* name) const;
+    void adopt_tensor(const char* name);
     void upload_tensor(const char* name, const void* data, uint64_t bytes, int rank,
                        const uint64_t* shape);
     void finalize(uint64_t* weight_bytes, uint32_t* tensor_count);

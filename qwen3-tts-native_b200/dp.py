@@ -88,3 +88,86 @@ def gather_rank_lines(line: dict, world: int) -> Sequence[dict]:
     out = [None] * world if dist.get_rank() == 0 else None
     dist.gather_object(line, out, dst=0)
     return out if out is not None else []
+
+
+# ---- weight image: quantize on one rank, hand the decode-form tensors to the others -----------
+#
+# The reference quantizes the decode matrices on every GPU as the checkpoint is uploaded
+# (talker.cu:564-668).  With one replica per GPU the bf16 checkpoint (3.8 GB) needs to reach only
+# one rank: the others receive the int8 rows, the row scales and the bf16 leftovers (2.6 GB in all)
+# straight into their own model's storage and adopt them.  This is a load-time edge, not a
+# data-path collective.
+
+class _DeviceSpan:
+    """A raw device pointer dressed up for torch.as_tensor (CUDA array interface, bytes)."""
+
+    def __init__(self, pointer: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1",
+                                         "data": (int(pointer), False), "version": 2}
+
+
+def device_bytes(pointer, nbytes: int, device_index: int):
+    """uint8 view of `nbytes` of device memory at `pointer` (no copy)."""
+    import torch
+    return torch.as_tensor(_DeviceSpan(pointer, nbytes), device=torch.device("cuda", device_index))
+
+
+def image_spans(image) -> List[tuple]:
+    """(pointer, bytes) of everything that makes up one tensor's decode form."""
+    spans = [(image.data, int(image.data_bytes))]
+    if image.quantized:
+        spans.append((image.scales, int(image.scales_bytes)))
+    return spans
+
+
+def _settle(tensor) -> None:
+    """The copies ran on torch's stream; the model reads the storage on its own streams."""
+    if tensor is not None and getattr(tensor, "is_cuda", False):
+        import torch
+        torch.cuda.synchronize(tensor.device)
+
+
+def broadcast_weight_image(model, names: Sequence[str], rank: int, src: int = 0, group=None,
+                           view=device_bytes) -> int:
+    """Rank `src` has uploaded (and thereby quantized) `names`; every other rank's model receives
+    the decode-form bytes into its own storage and adopts them.  Returns the bytes broadcast.
+
+    `view(pointer, nbytes, device_index)` turns a span into a tensor the backend can broadcast;
+    the default wraps device memory for NCCL."""
+    import torch.distributed as dist
+    total = 0
+    last = None
+    for name in names:
+        image = model.tensor_image(name)
+        if rank == src and not image.loaded:
+            raise RuntimeError(f"rank {src} has not uploaded {name}")
+        for pointer, nbytes in image_spans(image):
+            last = view(pointer, nbytes, image.device_index)
+            dist.broadcast(last, src, group=group)
+            total += nbytes
+        if rank != src:
+            model.adopt_tensor(name)
+    _settle(last)
+    return total
+
+
+def copy_weight_image(source, destination, names: Sequence[str], view=device_bytes) -> int:
+    """The same hand-over inside one process (two replicas, one or two GPUs): device-to-device
+    copies of the decode-form tensors, then adoption.  Returns the bytes copied."""
+    total = 0
+    last = None
+    for name in names:
+        src_image = source.tensor_image(name)
+        dst_image = destination.tensor_image(name)
+        if not src_image.loaded:
+            raise RuntimeError(f"the source model has not uploaded {name}")
+        src_spans, dst_spans = image_spans(src_image), image_spans(dst_image)
+        if [n for _, n in src_spans] != [n for _, n in dst_spans]:
+            raise RuntimeError(f"{name}: the two models disagree on the tensor's size")
+        for (sp, n), (dp_, _) in zip(src_spans, dst_spans):
+            last = view(dp_, n, dst_image.device_index)
+            last.copy_(view(sp, n, src_image.device_index))
+            total += n
+        destination.adopt_tensor(name)
+    _settle(last)
+    return total

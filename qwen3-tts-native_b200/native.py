@@ -60,6 +60,12 @@ class StateInfoC(C.Structure):        # 40 bytes
                 ("host_sync_count", C.c_uint64)]
 
 
+class TensorImageC(C.Structure):      # q3t_ops.h Q3tTensorImage
+    _fields_ = [("struct_size", C.c_uint32), ("device_index", C.c_int32), ("data", C.c_void_p),
+                ("data_bytes", C.c_uint64), ("scales", C.c_void_p), ("scales_bytes", C.c_uint64),
+                ("quantized", C.c_int32), ("loaded", C.c_int32)]
+
+
 class ModelMemoryC(C.Structure):      # 16 bytes
     _fields_ = [("shared_weight_bytes", C.c_uint64), ("tensor_count", C.c_uint32),
                 ("device_index", C.c_int32)]
@@ -116,7 +122,7 @@ EXPORTED_SYMBOLS = (
     "q3t_model_set_option", "q3t_model_run_frames", "q3t_session_read_state",
     "q3t_session_synthetic_prefill", "q3t_model_kernel_launches", "q3t_session_current_token",
     "q3t_launch_batch_causal_gqa_attention_fast_noalloc", "q3t_attention_static_scratch_capacity",
-    "q3t_kernel_error_count",
+    "q3t_kernel_error_count", "q3t_model_tensor_image", "q3t_model_adopt_tensor",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -311,6 +317,19 @@ class NativeTalkerModel:
         _check(library().qwen3_tts_model_upload_tensor(
             self._handle, name.encode(), a.ctypes.data_as(C.c_void_p), a.nbytes, a.ndim, shape,
             err, _ERR_CAP), err)
+
+    def tensor_image(self, name: str) -> TensorImageC:
+        """Device storage of a checkpoint tensor in decode form (int8 rows + fp32 row scales, or bf16)."""
+        image = TensorImageC()
+        image.struct_size = C.sizeof(TensorImageC)
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().q3t_model_tensor_image(self._handle, name.encode(), C.byref(image), err, _ERR_CAP), err)
+        return image
+
+    def adopt_tensor(self, name: str) -> None:
+        """Declares the tensor's device storage filled by the caller (broadcast, peer copy, file)."""
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().q3t_model_adopt_tensor(self._handle, name.encode(), err, _ERR_CAP), err)
 
     def finalize(self) -> ModelMemoryC:
         err = C.create_string_buffer(_ERR_CAP)

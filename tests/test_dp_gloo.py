@@ -90,3 +90,92 @@ def test_sharding_helpers():
         dp.RankInfo.from_env({"RANK": "2", "WORLD_SIZE": "2"})
     value, slowest, units = dp.whole_job_throughput(0.5, 100, 1)
     assert (value, slowest, units) == (200.0, 0.5, 100)
+
+
+class _HostImage:
+    """Stand-in for Q3tTensorImage whose 'pointers' are numpy arrays (no GPU in this test)."""
+
+    def __init__(self, data, scales, loaded):
+        self.data, self.data_bytes = data, data.nbytes
+        self.scales, self.scales_bytes = scales, 0 if scales is None else scales.nbytes
+        self.quantized, self.loaded, self.device_index = scales is not None, loaded, 0
+
+
+class _HostModel:
+    """The two calls broadcast_weight_image needs, over host memory."""
+
+    def __init__(self, shapes, fill):
+        self.tensors, self.adopted = {}, []
+        for i, (name, (rows, cols, quantized)) in enumerate(shapes.items()):
+            rng = np.random.default_rng(100 + i)
+            if quantized:
+                data = rng.integers(-127, 128, (rows, cols), dtype=np.int8) if fill else np.zeros((rows, cols), np.int8)
+                scales = rng.random(rows, dtype=np.float32) if fill else np.zeros(rows, np.float32)
+            else:
+                data = rng.integers(0, 65536, (rows, cols), dtype=np.uint16) if fill else np.zeros((rows, cols), np.uint16)
+                scales = None
+            self.tensors[name] = [data, scales, fill]
+
+    def tensor_image(self, name):
+        data, scales, loaded = self.tensors[name]
+        return _HostImage(data, scales, loaded)
+
+    def adopt_tensor(self, name):
+        if self.tensors[name][2]:
+            raise RuntimeError("duplicate tensor upload: " + name)
+        self.tensors[name][2] = True
+        self.adopted.append(name)
+
+
+IMAGE_SHAPES = {"layer.q_proj.weight": (48, 64, True), "layer.norm.weight": (1, 64, False),
+                "layer.down_proj.weight": (64, 96, True)}
+
+
+def image_worker(rank: int, world: int, port: int, results):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, REPO)
+    dp = importlib.import_module("qwen3-tts-native_b200.dp")
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        model = _HostModel(IMAGE_SHAPES, fill=(rank == 0))
+        host_view = lambda array, nbytes, device: torch.from_numpy(array.reshape(-1).view(np.uint8))
+        total = dp.broadcast_weight_image(model, list(IMAGE_SHAPES), rank, src=0, view=host_view)
+        digest = {n: (int(t[0].astype(np.int64).sum()), None if t[1] is None else float(t[1].sum()), t[2])
+                  for n, t in model.tensors.items()}
+        second = None
+        if rank == 1:
+            try:
+                model.adopt_tensor("layer.norm.weight")
+            except RuntimeError as e:
+                second = str(e)
+        results[rank] = dict(total=total, digest=digest, adopted=list(model.adopted), second=second)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_weight_image_reaches_the_other_rank():
+    import torch.multiprocessing as mp
+    world = 2
+    port = free_port()
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(image_worker, args=(world, port, results), nprocs=world, join=True)
+        r0, r1 = results[0], results[1]
+    expected = 48 * 64 + 48 * 4 + 64 * 2 + 64 * 96 + 64 * 4
+    assert r0["total"] == r1["total"] == expected
+    assert r0["digest"] == r1["digest"]                    # same bytes, everything marked loaded
+    assert all(v[2] for v in r1["digest"].values())
+    assert r0["adopted"] == [] and r1["adopted"] == list(IMAGE_SHAPES)
+    assert "duplicate" in r1["second"]
+
+
+def test_source_rank_must_have_uploaded():
+    sys.path.insert(0, REPO)
+    dp = importlib.import_module("qwen3-tts-native_b200.dp")
+    empty = _HostModel(IMAGE_SHAPES, fill=False)
+    with pytest.raises(RuntimeError, match="has not uploaded"):
+        dp.broadcast_weight_image(empty, list(IMAGE_SHAPES), rank=0, src=0, view=None)
+    with pytest.raises(RuntimeError, match="has not uploaded"):
+        dp.copy_weight_image(empty, _HostModel(IMAGE_SHAPES, fill=False), list(IMAGE_SHAPES), view=None)

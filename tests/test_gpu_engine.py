@@ -522,3 +522,45 @@ def test_seed_zero_and_reset(q3t, model):
     assert first >= 0
     a.close()
     b.close()
+
+
+def test_weight_image_hand_over(q3t, model, checkpoint):
+    """A second replica built from the first one's decode-form tensors (int8 rows, row scales, bf16
+    leftovers copied device to device and adopted) counts the same 404 tensors and decodes the same
+    frames; a tensor can be adopted only once, unknown names are refused, and a replica with a
+    tensor missing does not finalize."""
+    import importlib
+    dp = importlib.import_module("qwen3-tts-native_b200.dp")
+    names = list(checkpoint.keys())
+    image = model.tensor_image("talker.model.layers.3.self_attn.k_proj.weight")
+    assert image.quantized == 1 and image.loaded == 1
+    assert image.data_bytes == 1024 * 2048 and image.scales_bytes == 1024 * 4
+    norm = model.tensor_image("talker.model.norm.weight")
+    assert norm.quantized == 0 and norm.data_bytes == 2048 * 2 and not norm.scales
+
+    replica = q3t.NativeTalkerModel.create(0)
+    try:
+        copied = dp.copy_weight_image(model, replica, names[:-1])
+        with pytest.raises(q3t.NativeTalkerStatusError, match="duplicate"):
+            replica.adopt_tensor(names[0])
+        with pytest.raises(q3t.NativeTalkerStatusError, match="not part of"):
+            replica.tensor_image("talker.no_such.weight")
+        with pytest.raises(q3t.NativeTalkerStatusError):
+            replica.finalize()                                   # one tensor still missing
+        copied += dp.copy_weight_image(model, replica, names[-1:])
+        memory = replica.finalize()
+        assert memory.tensor_count == 404
+        assert memory.shared_weight_bytes == model.memory.shared_weight_bytes
+        assert 2_000_000_000 < copied < memory.shared_weight_bytes   # the image is smaller than the checkpoint
+        replica.set_option("mask_eos", 1)
+        a, b = start(q3t, model, 4242), start(q3t, replica, 4242)
+        for _ in range(3):
+            fa, fb = a.next_frame(9), b.next_frame(9)
+            assert np.array_equal(fa.codes, fb.codes)
+        ha, ta, ra = a.read_state()
+        hb, tb, rb = b.read_state()
+        assert np.array_equal(ha, hb) and np.array_equal(ta, tb) and ra == rb
+        a.close()
+        b.close()
+    finally:
+        replica.close()
