@@ -64,29 +64,47 @@ class ClockSampler:
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, device: int):
-        self.device = device
+    def __init__(self, devices, enabled: bool = True):
+        """One nvidia-smi process for all `devices` of the job (started by local rank 0 only: a
+        process per rank, each initialising NVML on every GPU at the start of the timed region,
+        perturbed an 8-rank run)."""
+        self.devices = list(devices)
+        self.enabled = enabled
         self.lines = []
+        self.first = 0
         self.proc = None
         self.thread = None
 
-    def start(self):
+    def start(self, ready_timeout_s: float = 5.0):
+        """Starts sampling and returns once the first sample has arrived, so that the tool's
+        start-up is over before the timed region begins."""
+        if not self.enabled:
+            return
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "--id=" + ",".join(str(d) for d in self.devices),
+                 f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
         self.thread = threading.Thread(target=self._read, daemon=True)
         self.thread.start()
+        deadline = time.time() + ready_timeout_s
+        while not self.lines and time.time() < deadline:
+            time.sleep(0.01)
+
+    def mark(self):
+        """Samples from here on belong to the timed region."""
+        self.first = len(self.lines)
 
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if not self.enabled:
+            return None
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -97,7 +115,7 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in self.lines[self.first:]:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
@@ -111,7 +129,7 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
-                "reasons": sorted(reasons)}
+                "gpus_sampled": len(self.devices), "reasons": sorted(reasons)}
 
 
 # ------------------------------------------------------------------ CPU restatement, timed
@@ -303,9 +321,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     # ---- device-resident frame loop -----------------------------------------------------
     model.run_frames(sessions, W, trailing_text_id=11)
     launches_before = model.kernel_launches()
-    barrier()
-    clocks = ClockSampler(local_rank)
+    clocks = ClockSampler(range(world), enabled=(rank == 0))
     clocks.start()
+    barrier()
+    clocks.mark()
     total_ms, per_frame = model.run_frames(sessions, K, trailing_text_id=11, want_frame_ms=True)
     barrier()
     clock_report = clocks.stop()
