@@ -3,19 +3,26 @@
 // Same arithmetic and fp32 summation order as gemv_rows_kernel<1,...> (and therefore as the
 // reference's int8_dequant_gemm_kernel<1>, int8_gemv.cu:58-128: lane l owns the 16-byte vectors
 // l, l+32, ... of a weight row, 16 sequential FMAs per vector, vector sums added to the lane
-// accumulator, shuffle-down tree) -- what changes is how the bytes move and how they are
-// converted:
-//   * one persistent CTA per SM owns a contiguous slice of the output channels; every warp owns
-//     a private ring of shared-memory stages and fills it with bulk asynchronous copies
-//     (cp.async.bulk global -> shared, completion counted on an mbarrier).  All copies of a
-//     slice are in flight as soon as the kernel starts (up to 96 KB per SM), before the
-//     activations are even staged; no register is tied up by a load in flight;
-//   * a warp works on two weight rows at once (rows c and c+1, or the gate and up rows of one
-//     channel), so the two FMA chains run as one packed fp32x2 chain (fma.rn.f32x2);
+// accumulator in vector order, shuffle-down tree) -- what changes is when the bytes move and how
+// they are converted:
+//   * one CTA per SM owns a contiguous slice of the output channels, and two CTAs fit on an SM:
+//     under programmatic stream serialisation the CTA of the next GEMV in the stream sits beside
+//     the one that computes.  Every warp owns a private ring of shared-memory stages and fills it
+//     with bulk asynchronous copies (cp.async.bulk global -> shared, completion counted on an
+//     mbarrier) before the dependency wait: up to 96 KB per CTA, the whole slice of a 12.6 MB
+//     matrix, is on its way while the predecessor still runs.  The row scales are fetched there
+//     too.  No register is tied up by a load in flight;
+//   * after the wait the activations go straight from global memory into registers, widened to
+//     fp32 once and kept as pairs (x of vector 2j, x of vector 2j+1) for all rows of the slice
+//     (rows of up to 2048 weights; longer rows keep packed bf16 and pair two rows instead);
+//   * the FMA chains of two vectors run as one packed chain (fma.rn.f32x2: two ordinary IEEE
+//     operations per instruction);
 //   * int8 -> fp32 without the conversion pipe: bytes are biased to unsigned with one XOR per
 //     word, dropped into the mantissa of 2^23 with PRMT and the bias 2^23+128 is subtracted
-//     (exact), again two rows per packed instruction;
-//   * the activations of a lane (K/32 values) live in registers as packed bf16 pairs.
+//     (exact), again two values per packed instruction;
+//   * the pair loop is not unrolled (one copy of the arithmetic in the instruction cache), the
+//     warp reductions of four consecutive row pairs run together, and their epilogues run side
+//     by side on eight lanes.
 // Every wait on an mbarrier is bounded; a wait that runs out records an error word that
 // gemv_b1_error_count() returns, drains its own copies and lets the kernel finish.
 
