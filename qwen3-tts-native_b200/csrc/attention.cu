@@ -171,6 +171,10 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
     __shared__ float wl[kAttnWarps][G];
     __shared__ __align__(16) float wacc[kAttnWarps][G][HD];
     __shared__ int is_last;
+    // this step's own K/V row, kept for the warp that attends to it (EARLY: saves re-reading
+    // from global memory what this CTA has just written there)
+    __shared__ __align__(16) bf16 knew[EARLY ? HD : 8];
+    __shared__ __align__(16) bf16 vnew[EARLY ? HD : 8];
 
     // ---- query heads (and, in fused mode, the new K/V row) ----------------------------
     if (a.fused) {
@@ -224,8 +228,14 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
                     const bf16* vsrc = a.v_new + (size_t)row * kn_stride + (size_t)kvh * HD;
 #pragma unroll
                     for (int j = 0; j < DPL; ++j) {
-                        kdst[lane + 32 * j] = f2bf(y[j]);
-                        vdst[lane + 32 * j] = vsrc[lane + 32 * j];
+                        const bf16 kb = f2bf(y[j]);
+                        const bf16 vb = vsrc[lane + 32 * j];
+                        kdst[lane + 32 * j] = kb;
+                        vdst[lane + 32 * j] = vb;
+                        if constexpr (EARLY) {
+                            knew[lane + 32 * j] = kb;
+                            vnew[lane + 32 * j] = vb;
+                        }
                     }
                 } else {
 #pragma unroll
@@ -291,8 +301,8 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
                 // CTA of the last split, visible since the barrier)
                 const int t_new = pos - w0;
                 if (t_new >= 0 && t_new < kWarpTokens) {
-                    const bf16* krow = kv_row(pos, false);
-                    const bf16* vrow = kv_row(pos, true);
+                    const bf16* krow = knew;     // written by the key warp before the barrier
+                    const bf16* vrow = vnew;
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt)
                         if (8 * nt + gid == t_new) {
