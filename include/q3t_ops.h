@@ -129,6 +129,35 @@ QWEN3_TTS_API int32_t q3t_pump_statistics(Q3tFramePump* pump, uint64_t* batches,
  * first (sessions are pinned for life, docs/ARCHITECTURE.md:285 of the reference). */
 QWEN3_TTS_API int32_t q3t_pick_device(const int32_t* active_sessions_per_device, int32_t devices);
 
+/* ---- hand-over of finished frames to the codec ------------------------------------------------
+ * The reference host's CudaPacketStager (native/qwen3-tts-runtime/src/cuda_packet_stager.rs:167-340)
+ * as a C object: one per session, on the session's GPU.  stage_frame copies the 16 codes of a frame
+ * begun with *_next_frame_begin_v2 from the talker's device buffer into the next slot of a 128-byte
+ * packet (up to 4 frames), ordered behind the frame's ready event, and returns the event to pass to
+ * qwen3_tts_session_next_frame_finish_v2 as consumer_done_event.  packet_view is what the codec
+ * reads (after ready_event); release_after_consumer orders the next packet behind the codec's own
+ * event and empties the packet.  Return codes: 0 ok, 1 refused (message says why; same refusals as
+ * the reference), 2 a CUDA call failed (the stager is poisoned and refuses everything after). */
+typedef struct Q3tPacketStager Q3tPacketStager;
+typedef struct Q3tStagedPacketView {
+    const uint16_t* device_codes;   /* [frame_count][16] */
+    uint64_t frame_count;
+    void* ready_event;              /* cudaEvent_t */
+} Q3tStagedPacketView;
+QWEN3_TTS_API Q3tPacketStager* q3t_packet_stager_create(int32_t device_index, char* error, size_t error_capacity);
+QWEN3_TTS_API void q3t_packet_stager_destroy(Q3tPacketStager* stager);
+QWEN3_TTS_API uint64_t q3t_packet_stager_device_bytes(const Q3tPacketStager* stager);
+QWEN3_TTS_API int32_t q3t_packet_stager_staged_frames(const Q3tPacketStager* stager);
+QWEN3_TTS_API int32_t q3t_packet_stager_stage_frame(Q3tPacketStager* stager, const uint16_t* device_codes,
+                                                    size_t code_count, void* producer_ready_event,
+                                                    int32_t source_device, void** copied_event, char* error,
+                                                    size_t error_capacity);
+QWEN3_TTS_API int32_t q3t_packet_stager_packet_view(const Q3tPacketStager* stager, Q3tStagedPacketView* view,
+                                                    char* error, size_t error_capacity);
+QWEN3_TTS_API int32_t q3t_packet_stager_release_after_consumer(Q3tPacketStager* stager,
+                                                               void* consumer_done_event, char* error,
+                                                               size_t error_capacity);
+
 /* ---- weight image -------------------------------------------------------------------------
  * The reference quantizes every decode matrix on every GPU while the checkpoint is uploaded
  * (talker.cu:564-668, int8_gemv.cu:20-52).  With one replica per GPU the work can be done once:

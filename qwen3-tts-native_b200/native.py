@@ -123,6 +123,9 @@ EXPORTED_SYMBOLS = (
     "q3t_session_synthetic_prefill", "q3t_model_kernel_launches", "q3t_session_current_token",
     "q3t_launch_batch_causal_gqa_attention_fast_noalloc", "q3t_attention_static_scratch_capacity",
     "q3t_kernel_error_count", "q3t_model_tensor_image", "q3t_model_adopt_tensor",
+    "q3t_packet_stager_create", "q3t_packet_stager_destroy", "q3t_packet_stager_device_bytes",
+    "q3t_packet_stager_staged_frames", "q3t_packet_stager_stage_frame", "q3t_packet_stager_packet_view",
+    "q3t_packet_stager_release_after_consumer",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -733,3 +736,79 @@ def pick_device(active_sessions_per_device: Sequence[int]) -> int:
     n = len(active_sessions_per_device)
     arr = (C.c_int32 * max(n, 1))(*[int(v) for v in active_sessions_per_device])
     return int(library().q3t_pick_device(arr, C.c_int32(n)))
+
+
+class StagedPacketViewC(C.Structure):      # q3t_ops.h Q3tStagedPacketView
+    _fields_ = [("device_codes", C.c_void_p), ("frame_count", C.c_uint64), ("ready_event", C.c_void_p)]
+
+
+class PacketStagerError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+class PacketStager:
+    """Device-to-device hand-over of begun frames to the codec (cuda_packet_stager.rs:167-340 of
+    the reference host): stage up to four frames, let the codec read the packet, release."""
+    CODEBOOKS = 16
+    MAX_PACKET_FRAMES = 4
+
+    def __init__(self, device_index: int = 0):
+        lib = library()
+        lib.q3t_packet_stager_create.restype = C.c_void_p
+        lib.q3t_packet_stager_device_bytes.restype = C.c_uint64
+        err = C.create_string_buffer(_ERR_CAP)
+        self._handle = lib.q3t_packet_stager_create(C.c_int32(device_index), err, _ERR_CAP)
+        if not self._handle:
+            raise PacketStagerError(2, err.value.decode(errors="replace"))
+        self.device_index = device_index
+
+    def _raise(self, status: int, err) -> None:
+        if status != 0:
+            raise PacketStagerError(status, err.value.decode(errors="replace"))
+
+    @property
+    def device_bytes(self) -> int:
+        return int(library().q3t_packet_stager_device_bytes(C.c_void_p(self._handle)))
+
+    @property
+    def staged_frames(self) -> int:
+        return int(library().q3t_packet_stager_staged_frames(C.c_void_p(self._handle)))
+
+    def stage_frame(self, device_codes: int, ready_event: int, source_device: Optional[int] = None,
+                    code_count: int = 16) -> int:
+        """Returns the event that fires once the frame's codes are in the packet."""
+        copied = C.c_void_p()
+        err = C.create_string_buffer(_ERR_CAP)
+        self._raise(library().q3t_packet_stager_stage_frame(
+            C.c_void_p(self._handle), C.c_void_p(device_codes), C.c_size_t(code_count),
+            C.c_void_p(ready_event), C.c_int32(self.device_index if source_device is None else source_device),
+            C.byref(copied), err, _ERR_CAP), err)
+        return int(copied.value or 0)
+
+    def stage(self, pending: "PendingTalkerFrame") -> int:
+        return self.stage_frame(pending.device_codes, pending.ready_event)
+
+    def packet_view(self) -> StagedPacketViewC:
+        view = StagedPacketViewC()
+        err = C.create_string_buffer(_ERR_CAP)
+        self._raise(library().q3t_packet_stager_packet_view(C.c_void_p(self._handle), C.byref(view), err,
+                                                            _ERR_CAP), err)
+        return view
+
+    def release_after_consumer(self, consumer_done_event: int) -> None:
+        err = C.create_string_buffer(_ERR_CAP)
+        self._raise(library().q3t_packet_stager_release_after_consumer(
+            C.c_void_p(self._handle), C.c_void_p(consumer_done_event), err, _ERR_CAP), err)
+
+    def close(self) -> None:
+        if self._handle:
+            library().q3t_packet_stager_destroy(C.c_void_p(self._handle))
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
