@@ -142,6 +142,12 @@ def cpu_frame_seconds(repeats: int = 1):
     description)."""
     from oracle import oracle as o
     o.build()
+    # all the host threads this process may use, whatever OMP_NUM_THREADS says (torchrun sets it
+    # to 1 for its workers; only rank 0 runs the CPU arm)
+    try:
+        o.set_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        o.set_threads(os.cpu_count() or 1)
     rng = np.random.default_rng(0)
 
     def layer(hidden, inter, qw, kvw):
