@@ -227,7 +227,7 @@ def workload_config(n_gpus: int):
                         "(5 layers, 16 positions) per frame, ragged KV U[64,2048], 16-token paged "
                         "bf16 KV, int8 per-channel weights, T=0.9 top-k 50 top-p 0.9",
             "sessions_per_gpu": SESSIONS, "global_sessions": SESSIONS * n_gpus,
-            "kv_lengths": "randint(64, 2048, seed 3 + rank)", "parallelism": f"dp{n_gpus}",
+            "kv_lengths": "randint(64, 2048, seed 3), the same draw on every GPU; session seeds differ per rank", "parallelism": f"dp{n_gpus}",
             "l2": "inputs larger than L2: 2.7 GB of weights and ~7.7 GB of KV per frame stream "
                   "from HBM; the predictor's 112 MB weight set may stay L2-resident across its 16 "
                   "positions, which is inherent to the workload"}
@@ -315,7 +315,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         model.close()
         return
 
-    lengths = dp.shard_kv_lengths(rank, SESSIONS)
+    lengths = dp.shard_kv_lengths(rank, SESSIONS, per_rank=False)   # configs[3]: replicated per GPU
     sessions = make_sessions(q3t, model, SESSIONS, lengths, total_frames, talker_cfg, predictor_cfg,
                              dp.shard_session_seeds(rank, SESSIONS)[0])
 

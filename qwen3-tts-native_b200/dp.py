@@ -44,10 +44,13 @@ def shard_session_seeds(rank: int, sessions_per_gpu: int, base: int = 1) -> List
     return [base + 1000 * rank + j for j in range(sessions_per_gpu)]
 
 
-def shard_kv_lengths(rank: int, sessions_per_gpu: int, low: int = 64, high: int = 2048, seed: int = 3) -> np.ndarray:
-    """Ragged KV lengths of a rank's sessions, U[low, high], seeded per rank (weak scaling: every
-    rank holds the same amount of work in expectation, none of it shared)."""
-    return np.random.default_rng(seed + rank).integers(low, high + 1, size=sessions_per_gpu)
+def shard_kv_lengths(rank: int, sessions_per_gpu: int, low: int = 64, high: int = 2048, seed: int = 3,
+                     per_rank: bool = True) -> np.ndarray:
+    """Ragged KV lengths of a rank's sessions, U[low, high].  Seeded per rank by default (every rank
+    holds the same amount of work in expectation, none of it shared); `per_rank=False` replicates
+    one draw on every GPU, which is how the 64-session configuration is specified (the slowest
+    rank then does not depend on the luck of its draw)."""
+    return np.random.default_rng(seed + (rank if per_rank else 0)).integers(low, high + 1, size=sessions_per_gpu)
 
 
 def assign_sessions(total_sessions: int, world: int) -> List[range]:

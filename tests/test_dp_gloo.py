@@ -82,6 +82,7 @@ def test_sharding_helpers():
     assert len(set(flat)) == len(flat) == 512
     assert np.array_equal(dp.shard_kv_lengths(3, 64), dp.shard_kv_lengths(3, 64))
     assert not np.array_equal(dp.shard_kv_lengths(3, 64), dp.shard_kv_lengths(4, 64))
+    assert np.array_equal(dp.shard_kv_lengths(3, 64, per_rank=False), dp.shard_kv_lengths(0, 64))   # replicated draw
     lens = dp.shard_kv_lengths(0, 64)
     assert lens.min() >= 64 and lens.max() <= 2048
     assert dp.RankInfo.from_env({}) == dp.RankInfo(0, 0, 1)
