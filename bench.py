@@ -277,14 +277,12 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
     if args.leg == "gemv":
         # operator microbenchmark: no model needed (keeps ncu captures small)
-        if args.chain >= 1:
-            g = native.benchmark_int8_gemv_chain(local_rank, args.gemv_in, args.gemv_out, chain=args.chain,
-                                                 buffers=16, iterations=max(args.steps, 1))
-        else:
-            g = native.benchmark_int8_gemv(local_rank, args.gemv_in, args.gemv_out, rows=args.rows,
-                                           buffers=16, iterations=max(args.steps, 1))
+        if args.gemv_mode is not None:
+            native.set_gemv_mode(args.gemv_mode)
+        g = native.benchmark_int8_gemv(local_rank, args.gemv_in, args.gemv_out, rows=args.rows,
+                                       buffers=16, iterations=max(args.steps, 1))
         print(json.dumps({"leg": "gemv", "in": args.gemv_in, "out": args.gemv_out, "rows": args.rows,
-                          "chain": args.chain,
+                          "gemv_mode": native.set_gemv_mode(-1),
                           "us_per_launch": g.mean_launch_microseconds,
                           "cold_us": g.cold_launch_microseconds,
                           "GBps": (args.gemv_in * args.gemv_out) / g.mean_launch_microseconds / 1e3}),
@@ -457,8 +455,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--chain", type=int, default=0,
-                    help="gemv leg: GEMVs per persistent chained launch (0 = the dispatcher's single launches)")
+    ap.add_argument("--gemv-mode", type=int, default=None,
+                    help="kernel for 1..8 rows: 0 SIMT, 1 mma.sync (default), 2 bulk-copy SIMT")
     ap.add_argument("--leg", choices=["all", "b64", "b1", "gemv"], default="all",
                     help="profiling aid: run one leg only and print a short JSON line")
     ap.add_argument("--gemv-in", type=int, default=2048)

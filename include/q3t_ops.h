@@ -185,20 +185,16 @@ QWEN3_TTS_API int32_t q3t_model_tensor_image(Qwen3TtsModelHandle model, const ch
 QWEN3_TTS_API int32_t q3t_model_adopt_tensor(Qwen3TtsModelHandle model, const char* name, char* error,
                                              size_t error_capacity);
 
-/* A chain of 1..8 dependent batch-1 GEMVs (rows == 1, in_features a multiple of 1024 up to 6144)
- * in one persistent cooperative launch: op i+1 may read what op i wrote.  Bit-identical to issuing
- * the same descriptors one by one through q3t_launch_int8_gemm_ex.  Launches through this entry
- * point share one set of barrier counters per device and must be ordered (one stream).  No
- * reference counterpart (it issues one launch per projection, talker.cu:2054-2333). */
-QWEN3_TTS_API int32_t q3t_launch_int8_gemv_chain(const Q3tGemmDesc* descs, int32_t count, void* stream);
-
-/* q3t_benchmark_int8_gemv for chained launches: `chain` GEMVs per launch, each on its own weight
- * image; the reported mean is per GEMV (launch time / chain). */
-QWEN3_TTS_API int32_t q3t_benchmark_int8_gemv_chain(int32_t device_index, int32_t input_features,
-                                                    int32_t output_features, int32_t chain,
-                                                    int32_t buffers, int32_t iterations,
-                                                    Qwen3TtsGemvBenchmark* output, char* error,
-                                                    size_t error_capacity);
+/* Which kernel takes projections of 1..8 rows (process-wide; returns the previous mode):
+ *   0  the SIMT kernel only: the summation order of the reference's int8_dequant_gemm_kernel
+ *      (int8_gemv.cu:58-128), outputs bit-identical to it;
+ *   1  (default) the mma.sync kernel where the shape allows (K = 512 * {2,3,4,6,8,9,12,...}):
+ *      same products, fp32 accumulation in another order (agreement ~1e-6 relative), 1..8 rows for
+ *      the price of one, weights bulk-copied ahead of the launch dependency;
+ *   2  the bulk-copy SIMT kernel where the shape allows (rows == 1), else SIMT.
+ * Also reachable as model option "gemv_mode" and as QWEN3_TTS_B1_GEMV=simt|bulk at load time.
+ * No reference counterpart (one kernel there). */
+QWEN3_TTS_API int32_t q3t_set_gemv_mode(int32_t mode);
 
 /* ---- norms, RoPE, KV append, glue (talker_kernels.cu) --------------------------------- */
 
@@ -325,6 +321,7 @@ QWEN3_TTS_API int32_t q3t_launch_sample_logits_at(
 /* Options: "mask_eos" (1: the talker sampler also masks EOS, for synthetic weights whose
  * logits would otherwise end a run at random), "use_graphs" (0: launch kernels one by one),
  * "batch_host_codes" (1: lockstep batches also mirror each frame's 16 codes to host memory),
+ * "gemv_mode" (process-wide, see q3t_set_gemv_mode),
  * "tc_min_rows" (process-wide: projections with at least this many rows run on the tensor
  * cores, default 9; 65 keeps every row count on the SIMT kernels, whose results do not depend on
  * the batch size), "prefill_chunk" (prompt positions per decoder pass, 1..64, default 64: a
@@ -359,10 +356,22 @@ QWEN3_TTS_API int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle sessio
 QWEN3_TTS_API int32_t q3t_session_current_token(Qwen3TtsSessionHandle session, uint16_t* token,
                                                 char* error, size_t error_capacity);
 
-/* Health counter: how many bounded device-side waits (mbarrier waits of the bulk-copy GEMV and
+/* Health counter: how many bounded device-side waits (mbarrier waits of the bulk-copy GEMVs and
  * of the tensor-core GEMM)
  * have run out since the library was loaded.  0 on a healthy run; kernels never spin forever. */
 QWEN3_TTS_API uint32_t q3t_kernel_error_count(void);
+
+/* Host-side fault injection for tests of the failure paths (a failed enqueue poisons the session,
+ * talker.cu:1245-1252; in a lockstep batch every session of it, talker.cu:1946-1956; a failed
+ * allocation is STATUS_ALLOCATION).  Nothing here makes a GPU fault: the engine is told that a call
+ * failed.  fail_launch_after(n): the n-th kernel launch the engine enqueues from now on reports a
+ * launch failure (n = 1: the next one; 0 disarms).  fail_allocation_after(n): likewise for device
+ * allocations.  report_device_wait_failure(device): bumps, from the host, the word that a bounded
+ * device-side wait bumps when it runs out; the calls in flight on that device then end with
+ * STATUS_CUDA and poisoned sessions.  Process-wide, for single-threaded tests. */
+QWEN3_TTS_API void q3t_test_fail_launch_after(int32_t launches);
+QWEN3_TTS_API void q3t_test_fail_allocation_after(int32_t allocations);
+QWEN3_TTS_API int32_t q3t_test_report_device_wait_failure(int32_t device_index);
 
 /* Number of this library's kernels launched so far through frame graphs of the model. */
 QWEN3_TTS_API int32_t q3t_model_kernel_launches(Qwen3TtsModelHandle model, uint64_t* launches,

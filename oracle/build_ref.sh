@@ -1,15 +1,25 @@
 #!/usr/bin/env bash
 # TEST INFRASTRUCTURE ONLY.
-# Compiles the reference project's own CUDA kernels, from the sources where they
-# lie in a checkout of luka-loehr/qwen3-tts-native, for sm_100a and links them
-# with ref_shim.cu into oracle/_ref/libq3t_ref.so.  No reference source is copied
-# into this repository and its CMake build is bypassed (that build pins sm_121
-# and CUDA 13).  The output directory is git-ignored.
+# Compiles the reference project's own CUDA code, from the sources where they lie
+# in a checkout of luka-loehr/qwen3-tts-native, for sm_100a.  Two outputs in
+# oracle/_ref/ (git-ignored):
+#   libq3t_ref.so               its three kernel files linked with ref_shim.cu: the
+#                               kernel launchers one by one, for operator parity;
+#   libqwen3_tts_cuda_ref.so    its whole talker library (eight .cu files + cuBLAS)
+#                               under its own C ABI: model, sessions and frames, for
+#                               parity of the frame composition and the prompt path.
+# No reference source is copied into this repository and its CMake build is
+# bypassed (that build pins sm_121 and CUDA 13).
 #
-#   usage: oracle/build_ref.sh [path/to/reference/checkout]
+#   usage: oracle/build_ref.sh path/to/reference/checkout
+#          (or QWEN3_TTS_REFERENCE_CHECKOUT=... oracle/build_ref.sh)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${1:-/root/reference}"
+REF="${1:-${QWEN3_TTS_REFERENCE_CHECKOUT:-}}"
+if [ -z "$REF" ]; then
+    echo "usage: $0 path/to/reference/checkout" >&2
+    exit 2
+fi
 SRC="$REF/native/qwen3-tts-native/native"
 if [ ! -f "$SRC/src/int8_gemv.cu" ]; then
     echo "reference checkout not found at $REF; nothing built" >&2
@@ -25,3 +35,10 @@ NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
     -Xlinker -rpath -Xlinker /usr/local/cuda/lib64 \
     -o "$OUT/libq3t_ref.so"
 echo "built $OUT/libq3t_ref.so"
+"$NVCC" -std=c++17 -O2 -gencode arch=compute_100a,code=sm_100a -shared -Xcompiler -fPIC \
+    -I"$SRC/include" -I"$SRC/src" \
+    "$SRC/src/gemv.cu" "$SRC/src/int8_gemv.cu" "$SRC/src/primitive_parity.cu" "$SRC/src/runtime.cu" \
+    "$SRC/src/sampling_kernels.cu" "$SRC/src/talker.cu" "$SRC/src/talker_kernels.cu" "$SRC/src/weights.cu" \
+    -lcublas -Xlinker -rpath -Xlinker /usr/local/cuda/lib64 \
+    -o "$OUT/libqwen3_tts_cuda_ref.so"
+echo "built $OUT/libqwen3_tts_cuda_ref.so"

@@ -5,6 +5,7 @@
 #include "q3t_ops.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -26,6 +27,18 @@ static_assert(QWEN3_TTS_MAX_BATCH_SESSIONS == kMaxRows && Q3T_MAX_ROWS == kMaxRo
 static_assert(Q3T_KV_PAGE_TOKENS == kPageTokens && Q3T_ATTENTION_CHUNK == kAttnChunk, "constants");
 
 namespace q3t {
+cudaError_t set_gemv_mma_error_sink(unsigned int* device_visible_word);
+cudaError_t set_gemv_b1_error_sink(unsigned int* device_visible_word);
+cudaError_t set_tc_error_sink(unsigned int* device_visible_word);
+
+namespace {
+std::atomic<unsigned int*> g_error_words[64];
+}
+
+volatile unsigned int* device_error_word(int device) {
+    return device >= 0 && device < 64 ? g_error_words[device].load(std::memory_order_acquire) : nullptr;
+}
+
 cudaError_t configure_device() {
     static std::mutex guard;
     static bool done[64] = {};
@@ -37,8 +50,21 @@ cudaError_t configure_device() {
     e = configure_gemv_kernels();
     if (e == cudaSuccess) e = configure_gemv_b1_kernels();
     if (e == cudaSuccess) e = configure_tc_kernels();
-    if (e == cudaSuccess) e = configure_gemv_chain_kernels();
+    if (e == cudaSuccess) e = configure_gemv_mma_kernels();
     if (e == cudaSuccess) e = configure_sampler_kernels();
+    if (e == cudaSuccess && device >= 0 && device < 64 && g_error_words[device].load() == nullptr) {
+        // the word the kernels' bounded waits bump when they give up; pinned and device-mapped, so
+        // the host reads it at its synchronisation points without a copy
+        unsigned int* word = nullptr;
+        e = cudaHostAlloc(reinterpret_cast<void**>(&word), sizeof(unsigned int), cudaHostAllocMapped);
+        if (e == cudaSuccess) {
+            *word = 0;
+            e = set_gemv_mma_error_sink(word);
+            if (e == cudaSuccess) e = set_gemv_b1_error_sink(word);
+            if (e == cudaSuccess) e = set_tc_error_sink(word);
+            if (e == cudaSuccess) g_error_words[device].store(word, std::memory_order_release);
+        }
+    }
     if (e == cudaSuccess && device >= 0 && device < 64) done[device] = true;
     return e;
 }
@@ -609,28 +635,6 @@ int32_t q3t_launch_int8_gemm_ex(const Q3tGemmDesc* d, void* stream) {
     return static_cast<int32_t>(launch_int8_gemm(a, S(stream)));
 }
 
-int32_t q3t_launch_int8_gemv_chain(const Q3tGemmDesc* descs, int32_t count, void* stream) {
-    if (descs == nullptr || count < 1 || count > kMaxChainOps) return cudaErrorInvalidValue;
-    if (const int32_t e = ready()) return e;
-    GemvArgs ops[kMaxChainOps];
-    for (int i = 0; i < count; ++i) {
-        const Q3tGemmDesc* d = descs + i;
-        if (d->struct_size != sizeof(Q3tGemmDesc) || d->epilogue < Q3T_EPI_PLAIN
-            || d->epilogue > Q3T_EPI_GATE_UP_SILU) {
-            return cudaErrorInvalidValue;
-        }
-        GemvArgs& a = ops[i];
-        a.w = d->weight; a.scales = d->scales; a.x = B(d->input); a.y = B(d->output);
-        a.y32 = d->output_f32; a.norm_w = B(d->norm_weight); a.norm_out = B(d->norm_output);
-        a.bias = B(d->bias); a.resid = B(d->residual);
-        a.in_features = d->in_features; a.out_features = d->out_features; a.rows = d->rows;
-        a.epilogue = d->epilogue;
-        a.eps = d->epsilon > 0.0f ? d->epsilon : kRmsEps;
-        if (!gemv_chain_supports(a)) return cudaErrorInvalidValue;
-    }
-    return static_cast<int32_t>(launch_gemv_chain(ops, count, nullptr, S(stream)));
-}
-
 int32_t q3t_launch_quantize_weight_rows(const uint16_t* weight, int8_t* quantized, float* scales,
                                         int32_t in_features, int32_t out_features, void* stream) {
     return static_cast<int32_t>(launch_quantize_weight_rows(B(weight), quantized, scales, in_features,
@@ -639,44 +643,12 @@ int32_t q3t_launch_quantize_weight_rows(const uint16_t* weight, int8_t* quantize
 
 }  // extern "C"
 
-namespace {
-int32_t benchmark_gemv(int32_t device_index, int32_t input_features, int32_t output_features, int32_t rows,
-                       int32_t buffers, int32_t iterations, int32_t chain, Qwen3TtsGemvBenchmark* output,
-                       char* error, size_t error_capacity);
-}
-
 extern "C" {
 
 int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t input_features,
                                 int32_t output_features, int32_t rows, int32_t buffers,
                                 int32_t iterations, Qwen3TtsGemvBenchmark* output, char* error,
                                 size_t error_capacity) {
-    return benchmark_gemv(device_index, input_features, output_features, rows, buffers, iterations, 1, output,
-                          error, error_capacity);
-}
-
-int32_t q3t_benchmark_int8_gemv_chain(int32_t device_index, int32_t input_features,
-                                      int32_t output_features, int32_t chain, int32_t buffers,
-                                      int32_t iterations, Qwen3TtsGemvBenchmark* output, char* error,
-                                      size_t error_capacity) {
-    if (chain < 1 || chain > kMaxChainOps || buffers < chain) {
-        write_error(error, error_capacity, "chain length must be 1..8 and not exceed the buffer count");
-        return QWEN3_TTS_TALKER_STATUS_INVALID_ARGUMENT;
-    }
-    return benchmark_gemv(device_index, input_features, output_features, 1, buffers, iterations, -chain, output,
-                          error, error_capacity);
-}
-
-}  // extern "C"
-
-namespace {
-
-// chain > 0: `chain` is ignored (single launches through the dispatcher); chain < 0: launches of
-// -chain chained GEMVs, each on its own weight image, iterations counted in GEMVs
-int32_t benchmark_gemv(int32_t device_index, int32_t input_features, int32_t output_features, int32_t rows,
-                       int32_t buffers, int32_t iterations, int32_t chain, Qwen3TtsGemvBenchmark* output,
-                       char* error, size_t error_capacity) {
-    const int links = chain < 0 ? -chain : 0;
     if (output == nullptr || input_features <= 0 || input_features % 16 != 0 || output_features <= 0
         || rows < 1 || rows > kMaxRows || buffers < 1 || iterations < 1) {
         write_error(error, error_capacity, "int8 GEMV benchmark arguments are out of range");
@@ -689,33 +661,30 @@ int32_t benchmark_gemv(int32_t device_index, int32_t input_features, int32_t out
         DeviceBuffer w(wbytes * buffers), s((size_t)output_features * sizeof(float));
         DeviceBuffer x((size_t)rows * input_features * sizeof(bf16));
         DeviceBuffer y((size_t)rows * output_features * sizeof(bf16));
-        check_cuda(cudaMemset(w.as<void>(), 1, w.bytes()), "cudaMemset");
-        check_cuda(cudaMemset(s.as<void>(), 0, s.bytes()), "cudaMemset");
-        check_cuda(cudaMemset(x.as<void>(), 0, x.bytes()), "cudaMemset");
         cudaStream_t stream = nullptr;
         cudaEvent_t t0 = nullptr, t1 = nullptr;
         check_cuda(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        // seeded pseudo-random weights, scales and activations (a constant fill would understate the
+        // switching activity of the memory system and of the arithmetic)
+        check_cuda(launch_fill_bytes(w.as<unsigned char>(), w.bytes(), 0x51ed27u, stream), "fill weights");
+        check_cuda(launch_fill_normal(x.as<bf16>(), (size_t)rows * input_features, 17, stream), "fill activations");
+        {
+            std::vector<float> scales(output_features);
+            for (int i = 0; i < output_features; ++i) scales[i] = (0.5f + (i % 97) / 97.0f) / 127.0f;
+            check_cuda(cudaMemcpyAsync(s.as<void>(), scales.data(), s.bytes(), cudaMemcpyHostToDevice, stream),
+                       "upload scales");
+            check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+        }
         check_cuda(cudaEventCreate(&t0), "cudaEventCreate");
         check_cuda(cudaEventCreate(&t1), "cudaEventCreate");
         auto run = [&](int i) {
             GemvArgs a;
             a.scales = s.as<float>(); a.x = x.as<bf16>(); a.y = y.as<bf16>();
             a.in_features = input_features; a.out_features = output_features; a.rows = rows;
-            if (links == 0) {
-                a.w = w.as<int8_t>() + (size_t)(i % buffers) * wbytes;
-                check_cuda(launch_int8_gemm(a, stream), "int8 GEMV");
-                return;
-            }
-            GemvArgs ops[kMaxChainOps];
-            for (int c = 0; c < links; ++c) {
-                ops[c] = a;
-                ops[c].w = w.as<int8_t>() + (size_t)((i * links + c) % buffers) * wbytes;
-                if (!gemv_chain_supports(ops[c])) throw std::runtime_error("shape not supported by the GEMV chain");
-            }
-            check_cuda(launch_gemv_chain(ops, links, nullptr, stream), "int8 GEMV chain");
+            a.w = w.as<int8_t>() + (size_t)(i % buffers) * wbytes;
+            check_cuda(launch_int8_gemm(a, stream), "int8 GEMV");
         };
         float cold_ms = 0.0f, total_ms = 0.0f;
-        int iterations_per_launch = 1;
         try {
             check_cuda(cudaEventRecord(t0, stream), "cudaEventRecord");
             run(0);
@@ -724,7 +693,7 @@ int32_t benchmark_gemv(int32_t device_index, int32_t input_features, int32_t out
             check_cuda(cudaEventElapsedTime(&cold_ms, t0, t1), "cudaEventElapsedTime");
             // The timed launches replay a captured graph (4 passes over the weight images), so
             // that the figure is the kernel's and not the host's launch rate.
-            const int per_graph = links == 0 ? buffers * 4 : (buffers * 4 + links - 1) / links;
+            const int per_graph = buffers * 4;
             cudaGraph_t graph = nullptr;
             check_cuda(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal),
                        "cudaStreamBeginCapture");
@@ -740,8 +709,7 @@ int32_t benchmark_gemv(int32_t device_index, int32_t input_features, int32_t out
             const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
             cudaGraphDestroy(graph);
             check_cuda(ie, "cudaGraphInstantiate");
-            const int per_replay = per_graph * (links == 0 ? 1 : links);
-            const int replays = (iterations + per_replay - 1) / per_replay;
+            const int replays = (iterations + per_graph - 1) / per_graph;
             cudaError_t le = cudaGraphLaunch(exec, stream);
             if (le == cudaSuccess) le = cudaStreamSynchronize(stream);
             if (le == cudaSuccess) le = cudaEventRecord(t0, stream);
@@ -751,8 +719,7 @@ int32_t benchmark_gemv(int32_t device_index, int32_t input_features, int32_t out
             if (le == cudaSuccess) le = cudaEventElapsedTime(&total_ms, t0, t1);
             cudaGraphExecDestroy(exec);
             check_cuda(le, "timed GEMV graph replays");
-            iterations = replays * per_graph * (links == 0 ? 1 : links);
-            if (links != 0) iterations_per_launch = links;
+            iterations = replays * per_graph;
         } catch (...) {
             cudaEventDestroy(t0); cudaEventDestroy(t1); cudaStreamDestroy(stream);
             throw;
@@ -763,15 +730,15 @@ int32_t benchmark_gemv(int32_t device_index, int32_t input_features, int32_t out
         b.output_features = output_features;
         b.iterations = iterations;
         b.weight_bytes = wbytes;
-        b.cold_launch_microseconds = cold_ms * 1000.0f / iterations_per_launch;
-        b.mean_launch_microseconds = total_ms * 1000.0f / iterations;     // per GEMV
+        b.cold_launch_microseconds = cold_ms * 1000.0f;
+        b.mean_launch_microseconds = total_ms * 1000.0f / iterations;
         b.tera_operations_per_second = static_cast<float>(
             2.0 * input_features * output_features * rows / (b.mean_launch_microseconds * 1.0e-6) / 1.0e12);
         *output = b;
     }, QWEN3_TTS_TALKER_STATUS_CUDA, error, error_capacity);
 }
 
-}  // namespace
+}  // extern "C"
 
 extern "C" {
 
@@ -967,10 +934,14 @@ int32_t q3t_model_set_option(Qwen3TtsModelHandle model, const char* key, int32_t
             m->prefill_chunk = value < 1 ? 1 : (value > kMaxRows ? kMaxRows : value);
         } else if (std::strcmp(key, "tc_min_rows") == 0) {
             set_tc_min_rows(value);     // process-wide: rows at or above this use the tensor cores
+        } else if (std::strcmp(key, "gemv_mode") == 0) {
+            if (value < 0 || value > 2) throw std::runtime_error("gemv_mode must be 0, 1 or 2");
+            set_gemv_mode(value);       // process-wide: kernel for projections of 1..8 rows
         } else {
             throw std::runtime_error(std::string("unknown model option: ") + key);
         }
         // captured graphs bake the option in
+        std::lock_guard<std::mutex> one_batch(m->batch_mutex);
         if (Workspace* w = m->batch_workspace_if_any()) {
             check_cuda(cudaStreamSynchronize(w->stream), "cudaStreamSynchronize");
             w->destroy_graphs();
@@ -1004,8 +975,19 @@ int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle session, int32_t pos
                    QWEN3_TTS_TALKER_STATUS_STATE, error, error_capacity);
 }
 
+int32_t q3t_set_gemv_mode(int32_t mode) { return set_gemv_mode(mode); }
+
+void q3t_test_fail_launch_after(int32_t launches) { fail_launch_after(launches); }
+void q3t_test_fail_allocation_after(int32_t allocations) { fail_allocation_after(allocations); }
+int32_t q3t_test_report_device_wait_failure(int32_t device_index) {
+    volatile unsigned int* word = device_error_word(device_index);
+    if (word == nullptr) return QWEN3_TTS_TALKER_STATUS_STATE;
+    *word = *word + 1;
+    return QWEN3_TTS_TALKER_STATUS_OK;
+}
+
 uint32_t q3t_kernel_error_count(void) {
-    return gemv_b1_error_count() + gemm_tc_error_count() + gemv_chain_error_count();
+    return gemv_b1_error_count() + gemm_tc_error_count() + gemv_mma_error_count();
 }
 
 int32_t q3t_session_current_token(Qwen3TtsSessionHandle session, uint16_t* token, char* error,

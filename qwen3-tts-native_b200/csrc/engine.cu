@@ -3,10 +3,15 @@
 #include "engine.hpp"
 
 #include <algorithm>
+#include <atomic>
+#include <cmath>
 #include <cstddef>
 #include <cstdlib>
+#include <cstdio>
 #include <cstring>
+#include <functional>
 #include <limits>
+#include <numeric>
 
 namespace q3t {
 
@@ -34,10 +39,39 @@ void check_cuda(cudaError_t status, const char* what) {
     }
 }
 
+namespace {
+std::atomic<int> g_fail_launch{0}, g_fail_allocation{0};
+std::atomic<uint64_t> g_next_session_id{1};
+
+// true exactly once, when an armed countdown reaches zero
+bool countdown_fires(std::atomic<int>& countdown) {
+    int left = countdown.load(std::memory_order_relaxed);
+    while (left > 0) {
+        if (countdown.compare_exchange_weak(left, left - 1, std::memory_order_relaxed)) return left == 1;
+    }
+    return false;
+}
+}  // namespace
+
+void fail_launch_after(int n) { g_fail_launch.store(n > 0 ? n : 0); }
+void fail_allocation_after(int n) { g_fail_allocation.store(n > 0 ? n : 0); }
+
+void check_launch(cudaError_t status, const char* what) {
+    if (status == cudaSuccess && countdown_fires(g_fail_launch)) status = cudaErrorLaunchOutOfResources;
+    check_cuda(status, what);
+}
+
 // ------------------------------------------------------------------ DeviceBuffer
 
 DeviceBuffer::DeviceBuffer(size_t bytes) : bytes_(bytes) {
-    if (bytes != 0) check_cuda(cudaMalloc(&ptr_, bytes), "cudaMalloc");
+    if (bytes == 0) return;
+    if (countdown_fires(g_fail_allocation)) throw std::bad_alloc();
+    const cudaError_t e = cudaMalloc(&ptr_, bytes);
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        throw std::bad_alloc();
+    }
+    check_cuda(e, "cudaMalloc");
 }
 DeviceBuffer::DeviceBuffer(DeviceBuffer&& o) noexcept : ptr_(o.ptr_), bytes_(o.bytes_) {
     o.ptr_ = nullptr;
@@ -441,6 +475,17 @@ void Model::finalize(uint64_t* weight_bytes, uint32_t* tensor_count) {
     *tensor_count = tensor_count_;
 }
 
+unsigned int Model::device_errors() const {
+    volatile unsigned int* word = device_error_word(device_);
+    return word != nullptr ? *word : 0u;
+}
+
+void Model::check_device_errors(unsigned int count_at_enqueue) const {
+    if (device_errors() != count_at_enqueue) {
+        throw CudaFailure("a bounded device-side wait ran out: the results of this call cannot be trusted");
+    }
+}
+
 Workspace& Model::batch_workspace() {
     std::lock_guard<std::mutex> lock(mutex);
     if (!batch_) batch_.reset(new Workspace(kMaxRows, device_));
@@ -457,18 +502,36 @@ Workspace& Model::prefill_workspace() {
 
 namespace {
 
+// Observation points of a prompt pass for the parity hooks (QWEN3_TTS_PARITY_TRACE,
+// QWEN3_TTS_STAGE_DUMP): called with the stage name, the layer and one activation row in device
+// memory.  Each call synchronises the stream, so a probed pass is never captured in a graph.
+struct Probe {
+    int row = 0;       // which row of the pass is observed (the last prompt position)
+    std::function<void(const char* stage, int layer, const bf16* values, int width)> emit;
+};
+
 void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWeights>& layers,
                     const uint32_t* rope_table, const KvPool& pool, const int* page_table, int table_stride,
-                    const int* positions, int n, int splits, cudaStream_t s, bool shared_cache = false) {
+                    const int* positions, int n, int splits, cudaStream_t s, bool shared_cache = false,
+                    const Probe* probe = nullptr) {
     const int qkv_width = d.q_width + 2 * d.kv_width;
     for (size_t l = 0; l < layers.size(); ++l) {
         const LayerWeights& lw = layers[l];
+        const int layer = static_cast<int>(l);
+        auto observe = [&](const char* stage, const bf16* base, int stride, int width) {
+            if (probe != nullptr) probe->emit(stage, layer, base + (size_t)probe->row * stride, width);
+        };
         GemvArgs g;
         g.w = lw.qkv.data; g.scales = lw.qkv.scales;
         g.x = w.hidden.as<bf16>(); g.y = w.qkv.as<bf16>();
         g.norm_w = lw.input_norm;
+        if (probe != nullptr) g.norm_out = w.normalized.as<bf16>();
         g.in_features = d.hidden; g.out_features = qkv_width; g.rows = n; g.epilogue = EPI_PLAIN;
-        check_cuda(launch_int8_gemm(g, s), "qkv projection");
+        check_launch(launch_int8_gemm(g, s), "qkv projection");
+        observe("input_norm", w.normalized.as<bf16>(), d.hidden, d.hidden);
+        observe("q_projection", w.qkv.as<bf16>(), qkv_width, d.q_width);
+        observe("k_projection", w.qkv.as<bf16>() + d.q_width, qkv_width, d.kv_width);
+        observe("v_projection", w.qkv.as<bf16>() + d.q_width + d.kv_width, qkv_width, d.kv_width);
 
         AttentionArgs a;
         a.q = w.qkv.as<bf16>();
@@ -492,25 +555,30 @@ void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWei
             // the rows are consecutive positions of one session: every row's K/V goes into the
             // cache first, then every row attends up to its own position
             a.append_mode = 1;
-            check_cuda(launch_decode_attention(a, s), "prompt KV append");
+            check_launch(launch_decode_attention(a, s), "prompt KV append");
             a.append_mode = 2;
         }
-        check_cuda(launch_decode_attention(a, s), "decode attention");
+        check_launch(launch_decode_attention(a, s), "decode attention");
+        observe("attention", w.attention.as<bf16>(), d.q_width, d.q_width);
 
         GemvArgs o;
         o.w = lw.o.data; o.scales = lw.o.scales;
         o.x = w.attention.as<bf16>(); o.y = w.hidden.as<bf16>();
         o.in_features = d.q_width; o.out_features = d.hidden; o.rows = n; o.epilogue = EPI_ADD;
         o.residual_settled = true;     // hidden was last written before the qkv projection
-        check_cuda(launch_int8_gemm(o, s), "attention output projection");
+        check_launch(launch_int8_gemm(o, s), "attention output projection");
+        observe("attention_residual", w.hidden.as<bf16>(), d.hidden, d.hidden);
 
         GemvArgs u;
         u.w = lw.gate_up.data; u.scales = lw.gate_up.scales;
         u.x = w.hidden.as<bf16>(); u.y = w.gate.as<bf16>();
         u.norm_w = lw.post_norm;
+        if (probe != nullptr) u.norm_out = w.normalized.as<bf16>();
         u.in_features = d.hidden; u.out_features = d.intermediate; u.rows = n;
         u.epilogue = EPI_GATE_UP_SILU;
-        check_cuda(launch_int8_gemm(u, s), "gate/up projection");
+        check_launch(launch_int8_gemm(u, s), "gate/up projection");
+        observe("post_attention_norm", w.normalized.as<bf16>(), d.hidden, d.hidden);
+        observe("gated_activation", w.gate.as<bf16>(), d.intermediate, d.intermediate);
 
         GemvArgs dn;
         dn.w = lw.down.data; dn.scales = lw.down.scales;
@@ -518,7 +586,8 @@ void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWei
         dn.in_features = d.intermediate; dn.out_features = d.hidden; dn.rows = n;
         dn.epilogue = EPI_ADD;
         dn.residual_settled = true;    // hidden was last written by the output projection, two launches up
-        check_cuda(launch_int8_gemm(dn, s), "down projection");
+        check_launch(launch_int8_gemm(dn, s), "down projection");
+        observe("layer_output", w.hidden.as<bf16>(), d.hidden, d.hidden);
     }
 }
 
@@ -526,15 +595,15 @@ void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWei
 void enqueue_predictor(Workspace& w, Model& m, int n, cudaStream_t s) {
     const FrameTable* table = w.table.as<FrameTable>();
     const int H = m.talker.hidden, PH = m.predictor.hidden;
-    check_cuda(launch_frame_begin(table, n, s), "frame begin");
+    check_launch(launch_frame_begin(table, n, s), "frame begin");
     for (int p = 0; p < kPredictorSequence; ++p) {
-        check_cuda(launch_predictor_input(table, p, m.codec_embedding, m.predictor_embedding_table,
+        check_launch(launch_predictor_input(table, p, m.codec_embedding, m.predictor_embedding_table,
                                           w.x_in.as<bf16>(), H, n, s), "predictor input");
         GemvArgs g;
         g.w = m.small_to_mtp.data; g.scales = m.small_to_mtp.scales;
         g.x = w.x_in.as<bf16>(); g.y = w.hidden.as<bf16>(); g.bias = m.small_to_mtp_bias;
         g.in_features = H; g.out_features = PH; g.rows = n; g.epilogue = EPI_BIAS;
-        check_cuda(launch_int8_gemm(g, s), "predictor input projection");
+        check_launch(launch_int8_gemm(g, s), "predictor input projection");
         enqueue_layers(w, m.predictor, m.predictor_layers, m.predictor_rope, *m.predictor_pool,
                        w.predictor_pages.as<int>(), 1,
                        w.predictor_positions.as<int>() + (size_t)p * kMaxRows, n, 1, s);
@@ -543,13 +612,13 @@ void enqueue_predictor(Workspace& w, Model& m, int n, cudaStream_t s) {
             h.w = m.predictor_heads[p - 1].data; h.scales = m.predictor_heads[p - 1].scales;
             h.x = w.hidden.as<bf16>(); h.y = w.logits.as<bf16>(); h.norm_w = m.predictor_norm;
             h.in_features = PH; h.out_features = kPredictorVocab; h.rows = n; h.epilogue = EPI_PLAIN;
-            check_cuda(launch_int8_gemm(h, s), "predictor head");
-            check_cuda(launch_sample_table(table, w.logits.as<bf16>(), kPredictorVocab,
+            check_launch(launch_int8_gemm(h, s), "predictor head");
+            check_launch(launch_sample_table(table, w.logits.as<bf16>(), kPredictorVocab,
                                            kPredictorVocab, 0, p, 0, kEos, n, s),
                        "sample predictor logits");
         }
     }
-    check_cuda(launch_pack_codes(table, n, s), "pack codec frame");
+    check_launch(launch_pack_codes(table, n, s), "pack codec frame");
 }
 
 void enqueue_text_projection(Workspace& w, Model& m, int n, bool residual, cudaStream_t s) {
@@ -558,7 +627,7 @@ void enqueue_text_projection(Workspace& w, Model& m, int n, bool residual, cudaS
     f1.w = m.text_fc1.data; f1.scales = m.text_fc1.scales;
     f1.x = w.x_in.as<bf16>(); f1.y = w.projection.as<bf16>(); f1.bias = m.text_fc1_bias;
     f1.in_features = H; f1.out_features = H; f1.rows = n; f1.epilogue = EPI_BIAS_SILU;
-    check_cuda(launch_int8_gemm(f1, s), "text projection fc1");
+    check_launch(launch_int8_gemm(f1, s), "text projection fc1");
     GemvArgs f2;
     f2.w = m.text_fc2.data; f2.scales = m.text_fc2.scales;
     f2.x = w.projection.as<bf16>(); f2.bias = m.text_fc2_bias;
@@ -568,7 +637,7 @@ void enqueue_text_projection(Workspace& w, Model& m, int n, bool residual, cudaS
     } else {
         f2.y = w.hidden.as<bf16>(); f2.epilogue = EPI_BIAS;
     }
-    check_cuda(launch_int8_gemm(f2, s), "text projection fc2");
+    check_launch(launch_int8_gemm(f2, s), "text projection fc2");
 }
 
 void enqueue_talker_head(Workspace& w, Model& m, int n, int advance, cudaStream_t s) {
@@ -579,17 +648,17 @@ void enqueue_talker_head(Workspace& w, Model& m, int n, int advance, cudaStream_
     h.x = w.hidden.as<bf16>(); h.y = w.logits.as<bf16>();
     h.norm_w = m.talker_norm; h.norm_out = w.normalized.as<bf16>();
     h.in_features = H; h.out_features = kTalkerVocab; h.rows = n; h.epilogue = EPI_PLAIN;
-    check_cuda(launch_int8_gemm(h, s), "codec head");
-    check_cuda(launch_sample_table(table, w.logits.as<bf16>(), kTalkerVocab, kTalkerVocab, 1, 0,
+    check_launch(launch_int8_gemm(h, s), "codec head");
+    check_launch(launch_sample_table(table, w.logits.as<bf16>(), kTalkerVocab, kTalkerVocab, 1, 0,
                                    m.mask_eos, kEos, n, s), "sample talker logits");
-    check_cuda(launch_frame_end(table, w.normalized.as<bf16>(), H, n, advance, s), "frame end");
+    check_launch(launch_frame_end(table, w.normalized.as<bf16>(), H, n, advance, s), "frame end");
 }
 
 // next talker input, 28 layers, head, sample (talker.cu:1703-1880)
 void enqueue_talker(Workspace& w, Model& m, int n, int splits, cudaStream_t s) {
     FrameTable* table = w.table.as<FrameTable>();
     const int H = m.talker.hidden;
-    check_cuda(launch_talker_input(table, m.codec_embedding, m.predictor_embedding_table,
+    check_launch(launch_talker_input(table, m.codec_embedding, m.predictor_embedding_table,
                                    m.text_embedding, kTextVocab, w.hidden.as<bf16>(),
                                    w.x_in.as<bf16>(), H, n, s), "talker input");
     enqueue_text_projection(w, m, n, true, s);
@@ -603,29 +672,127 @@ void enqueue_prompt_step(Workspace& w, Model& m, const int* text_ids, const int*
                          int splits, cudaStream_t s) {
     FrameTable* table = w.table.as<FrameTable>();
     const int H = m.talker.hidden;
-    check_cuda(launch_prompt_gather(table, text_ids, m.text_embedding, kTextVocab,
+    check_launch(launch_prompt_gather(table, text_ids, m.text_embedding, kTextVocab,
                                     w.x_in.as<bf16>(), H, s), "prompt gather");
     enqueue_text_projection(w, m, 1, false, s);
-    check_cuda(launch_prompt_combine(table, text_ids, codec_ids, m.codec_embedding, kTalkerVocab,
+    check_launch(launch_prompt_combine(table, text_ids, codec_ids, m.codec_embedding, kTalkerVocab,
                                      w.hidden.as<bf16>(), H, s), "prompt combine");
     enqueue_layers(w, m.talker, m.talker_layers, m.talker_rope, *m.talker_pool, w.talker_pages.as<int>(),
                    Workspace::kMaxPagesPerRow, table->position, 1, splits, s);
-    check_cuda(launch_advance_position(table, s), "advance position");
+    check_launch(launch_advance_position(table, s), "advance position");
 }
 
 // prompt positions base .. base + rows - 1 of row 0's session as the rows of one decoder pass
 void enqueue_prompt_chunk(Workspace& w, Model& m, const int* text_ids, const int* codec_ids, int base,
-                          int rows, int splits, cudaStream_t s) {
+                          int rows, int splits, cudaStream_t s, const Probe* probe = nullptr) {
     const int H = m.talker.hidden;
-    check_cuda(launch_prompt_rows(text_ids, codec_ids, base, rows, m.text_embedding, kTextVocab,
+    check_launch(launch_prompt_rows(text_ids, codec_ids, base, rows, m.text_embedding, kTextVocab,
                                   w.x_in.as<bf16>(), w.prompt_positions.as<int>(), H, s), "prompt rows");
     enqueue_text_projection(w, m, rows, false, s);
-    check_cuda(launch_prompt_combine_rows(text_ids, codec_ids, base, rows, m.codec_embedding, kTalkerVocab,
+    check_launch(launch_prompt_combine_rows(text_ids, codec_ids, base, rows, m.codec_embedding, kTalkerVocab,
                                           w.hidden.as<bf16>(), H, s), "prompt combine");
+    if (probe != nullptr) probe->emit("input", -1, w.hidden.as<bf16>() + (size_t)probe->row * H, H);
     // page-table stride 0: every row reads and writes the cache of the session bound to row 0
     enqueue_layers(w, m.talker, m.talker_layers, m.talker_rope, *m.talker_pool, w.talker_pages.as<int>(), 0,
-                   w.prompt_positions.as<int>(), rows, splits, s, true);
+                   w.prompt_positions.as<int>(), rows, splits, s, true, probe);
 }
+
+// ---- parity hooks of the prompt path --------------------------------------------------------
+// QWEN3_TTS_PARITY_TRACE: one line per observed vector on stderr, in the reference's format
+// (talker.cu:2342-2432: "QWEN3_TTS_TRACE {json}" with stage, layer, mean, rms, maximum and the first
+// 16 values; the 20 largest logits at the end), for the input row, every layer's output, the final
+// norm and the logits of the last prompt position.  QWEN3_TTS_STAGE_DUMP: the layer-0 stages and the
+// final logits as raw bf16 files named <stage>.bf16, in the directory the variable names (a value
+// without a slash selects the reference's /tmp/native_stages, talker.cu:2503-2538).
+struct ParityHooks {
+    bool trace = false;
+    std::string dump_dir;
+    cudaStream_t stream = nullptr;
+
+    static ParityHooks from_environment(cudaStream_t s) {
+        ParityHooks h;
+        h.stream = s;
+        h.trace = std::getenv("QWEN3_TTS_PARITY_TRACE") != nullptr;
+        if (const char* d = std::getenv("QWEN3_TTS_STAGE_DUMP")) {
+            h.dump_dir = std::strchr(d, '/') != nullptr ? d : "/tmp/native_stages";
+        }
+        return h;
+    }
+    bool active() const { return trace || !dump_dir.empty(); }
+
+    std::vector<float> fetch(const bf16* values, int width) const {
+        std::vector<bf16> raw(width);
+        check_cuda(cudaMemcpyAsync(raw.data(), values, (size_t)width * sizeof(bf16), cudaMemcpyDeviceToHost,
+                                   stream), "copy parity vector to host");
+        check_cuda(cudaStreamSynchronize(stream), "synchronize parity vector");
+        std::vector<float> out(width);
+        for (int i = 0; i < width; ++i) out[i] = __bfloat162float(raw[i]);
+        return out;
+    }
+    void dump(const char* stage, const bf16* values, int width) const {
+        if (dump_dir.empty()) return;
+        std::vector<bf16> raw(width);
+        check_cuda(cudaMemcpyAsync(raw.data(), values, (size_t)width * sizeof(bf16), cudaMemcpyDeviceToHost,
+                                   stream), "copy stage dump to host");
+        check_cuda(cudaStreamSynchronize(stream), "synchronize stage dump");
+        const std::string path = dump_dir + "/" + stage + ".bf16";
+        std::FILE* f = std::fopen(path.c_str(), "wb");
+        if (f == nullptr) throw std::runtime_error("failed to create stage dump " + path);
+        const size_t written = std::fwrite(raw.data(), sizeof(bf16), raw.size(), f);
+        if (std::fclose(f) != 0 || written != raw.size()) throw std::runtime_error("failed to write stage dump " + path);
+    }
+    void vector_line(const char* stage, int layer, const bf16* values, int width) const {
+        if (!trace) return;
+        const std::vector<float> v = fetch(values, width);
+        double sum = 0.0, squares = 0.0;
+        float largest = 0.0f;
+        for (float x : v) {
+            sum += x;
+            squares += (double)x * x;
+            largest = std::max(largest, std::fabs(x));
+        }
+        std::string line = "QWEN3_TTS_TRACE {\"stage\":\"" + std::string(stage) + "\",\"layer\":" + std::to_string(layer);
+        char number[64];
+        std::snprintf(number, sizeof(number), ",\"mean\":%.9g", sum / width); line += number;
+        std::snprintf(number, sizeof(number), ",\"rms\":%.9g", std::sqrt(squares / width)); line += number;
+        std::snprintf(number, sizeof(number), ",\"maximum\":%.9g,\"first\":[", largest); line += number;
+        for (int i = 0; i < std::min(width, 16); ++i) {
+            std::snprintf(number, sizeof(number), "%s%.9g", i == 0 ? "" : ",", v[i]);
+            line += number;
+        }
+        std::fprintf(stderr, "%s]}\n", line.c_str());
+    }
+    void logits_line(const bf16* logits, int vocabulary) const {
+        if (!trace) return;
+        const std::vector<float> v = fetch(logits, vocabulary);
+        std::vector<int> order(vocabulary);
+        std::iota(order.begin(), order.end(), 0);
+        const int top = std::min(20, vocabulary);
+        std::partial_sort(order.begin(), order.begin() + top, order.end(),
+                          [&v](int a, int b) { return v[a] == v[b] ? a < b : v[a] > v[b]; });
+        std::string line = "QWEN3_TTS_TRACE {\"stage\":\"logits\",\"top\":[";
+        char item[96];
+        for (int r = 0; r < top; ++r) {
+            std::snprintf(item, sizeof(item), "%s{\"token\":%d,\"logit\":%.9g}", r == 0 ? "" : ",", order[r], v[order[r]]);
+            line += item;
+        }
+        std::fprintf(stderr, "%s]}\n", line.c_str());
+    }
+    // the probe a prompt pass is run with
+    Probe probe(int row) const {
+        Probe p;
+        p.row = row;
+        const ParityHooks* self = this;
+        p.emit = [self](const char* stage, int layer, const bf16* values, int width) {
+            const bool input = std::strcmp(stage, "input") == 0;
+            const bool output = std::strcmp(stage, "layer_output") == 0;
+            if (input) self->vector_line("input", -1, values, width);
+            if (output) self->vector_line("layer", layer, values, width);
+            if (input || layer == 0) self->dump(stage, values, width);
+        };
+        return p;
+    }
+};
 
 int count_kernel_nodes(cudaGraph_t graph) {
     size_t total = 0;
@@ -679,7 +846,8 @@ void validate_sampling_params(const SamplingParams& p) {
 // ------------------------------------------------------------------ Session
 
 Session::Session(std::shared_ptr<Model> model, int max_sequence_length, uint64_t seed)
-    : model_(std::move(model)), device_(model_->device()), max_seq_(max_sequence_length) {
+    : model_(std::move(model)), id_(g_next_session_id.fetch_add(1)), device_(model_->device()),
+      max_seq_(max_sequence_length) {
     if (max_sequence_length < 16 || max_sequence_length > 8192) {
         throw std::runtime_error("max sequence length must be in [16, 8192]");
     }
@@ -750,15 +918,12 @@ void Session::release() noexcept {
 
 Session::~Session() {
     cudaSetDevice(device_);
+    // A lockstep frame of this session that was begun and never finished may still be running on
+    // the shared workspace: its last event is this session's own, so no other thread's stream (which
+    // may be capturing a graph at this moment) has to be touched.  Workspaces remember bound sessions
+    // by id, and ids are never reused, so nothing has to be erased from them either.
+    if (frame_in_flight_ && semantic_ready_ != nullptr) cudaEventSynchronize(semantic_ready_);
     if (stream_ != nullptr) cudaStreamSynchronize(stream_);
-    // a batch workspace may still hold this session's page ids
-    if (model_) {
-        Workspace* batch = model_->batch_workspace_if_any();
-        if (batch != nullptr) {
-            cudaStreamSynchronize(batch->stream);
-            batch->bound.clear();
-        }
-    }
     release();
     solo_.reset();
 }
@@ -826,7 +991,7 @@ void Session::validate_begin(int semantic_token, int trailing_text, const Sampli
 // Makes the page lists of s[0..n) resident in the workspace's page tables.
 void Session::bind_rows(Workspace& w, Session** s, int n) {
     bool same = static_cast<int>(w.bound.size()) == n;
-    for (int i = 0; same && i < n; ++i) same = w.bound[i] == s[i];
+    for (int i = 0; same && i < n; ++i) same = w.bound[i] == s[i]->id_;
     if (same) return;
     check_cuda(cudaStreamSynchronize(w.stream), "cudaStreamSynchronize(rebind)");
     const int stride = Workspace::kMaxPagesPerRow;
@@ -842,7 +1007,8 @@ void Session::bind_rows(Workspace& w, Session** s, int n) {
                "upload talker page table");
     check_cuda(cudaMemcpyAsync(w.predictor_pages.as<void>(), predictor_rows, (size_t)n * sizeof(int),
                                cudaMemcpyHostToDevice, w.stream), "upload predictor page table");
-    w.bound.assign(s, s + n);
+    w.bound.resize(n);
+    for (int i = 0; i < n; ++i) w.bound[i] = s[i]->id_;
 }
 
 Workspace::Graphs& Session::frame_graphs(Workspace& w, Model& m, int n, int splits) {
@@ -924,6 +1090,7 @@ uint64_t Session::take_lease(Workspace* w, bool host_codes) {
     pending_position_ = static_cast<uint32_t>(position_);
     pending_workspace_ = w;
     pending_frame_serial_ = w != nullptr ? w->frame_serial + 1 : 0;    // the frame about to be launched
+    pending_errors_ = model_->device_errors();
     return lease;
 }
 
@@ -979,6 +1146,7 @@ void Session::batch_begin(Model* model, Session** s, int n, const int* trailing_
         }
         s[i]->validate_begin(s[i]->current_token_, trailing_text[i], talker[i], predictor[i]);
     }
+    std::lock_guard<std::mutex> one_batch(model->batch_mutex);
     Workspace& w = model->batch_workspace();
     const bool host_codes = model->batch_host_codes != 0;
     for (int i = 0; i < n; ++i) s[i]->take_lease(&w, host_codes);
@@ -1030,8 +1198,14 @@ FrameResult Session::finish_frame(uint64_t lease_id, cudaEvent_t consumer_done) 
     check_cuda(cudaEventSynchronize(semantic_ready_), "cudaEventSynchronize(semantic ready)");
     ++host_sync_count;
     const int next = *h_token_;
-    if (next < 0 || next >= kTalkerVocab) {
-        throw std::runtime_error("device sampler returned an invalid token");
+    try {
+        model_->check_device_errors(pending_errors_);
+        if (next < 0 || next >= kTalkerVocab) {
+            throw std::runtime_error("device sampler returned an invalid token");
+        }
+    } catch (...) {
+        drop_lease_poisoned();
+        throw;
     }
     FrameResult r{};
     r.talker_position = pending_position_;
@@ -1088,12 +1262,15 @@ void Session::prefill(const int32_t* text_ids, const int32_t* codec_ids, int cou
     // skinny GEMM) on the model's prompt workspace, one prompt at a time; with prefill_chunk = 1,
     // or a prompt of one position, it runs position by position on the session's own workspace.
     const int chunk = std::min(std::max(m.prefill_chunk, 1), kMaxRows);
-    const bool chunked = chunk > 1 && count > 1;
+    const ParityHooks hooks = ParityHooks::from_environment(nullptr);
+    // the parity hooks observe the chunked pass (they synchronise, so nothing of it may be captured)
+    const bool chunked = (chunk > 1 && count > 1) || hooks.active();
     std::unique_lock<std::mutex> one_prompt(m.prefill_mutex, std::defer_lock);
     if (chunked) one_prompt.lock();
     Workspace& w = chunked ? m.prefill_workspace() : *solo_;
     position_ = 0;
     generated_ = 0;
+    const unsigned int errors_before = m.device_errors();
     try {
         DeviceBuffer ids(2 * (size_t)count * sizeof(int));
         int* d_text = ids.as<int>();
@@ -1114,9 +1291,16 @@ void Session::prefill(const int32_t* text_ids, const int32_t* codec_ids, int cou
         check_cuda(cudaEventRecord(w.talker_start, w.stream), "cudaEventRecord");
         if (chunked) {
             int last_rows = 0;
+            ParityHooks observed = hooks;
+            observed.stream = w.stream;
             for (int base = 0; base < count; base += chunk) {
                 last_rows = std::min(chunk, count - base);
-                enqueue_prompt_chunk(w, m, d_text, d_codec, base, last_rows, splits, w.stream);
+                if (hooks.active() && base + last_rows == count) {
+                    const Probe probe = observed.probe(last_rows - 1);     // the last prompt position
+                    enqueue_prompt_chunk(w, m, d_text, d_codec, base, last_rows, splits, w.stream, &probe);
+                } else {
+                    enqueue_prompt_chunk(w, m, d_text, d_codec, base, last_rows, splits, w.stream);
+                }
             }
             if (last_rows > 1) {
                 // the head and the sampler read row 0: bring the last position's hidden state there
@@ -1146,11 +1330,19 @@ void Session::prefill(const int32_t* text_ids, const int32_t* codec_ids, int cou
             for (int i = 0; i < count; ++i) enqueue_prompt_step(w, m, d_text, d_codec, splits, w.stream);
         }
         enqueue_talker_head(w, m, 1, 0, w.stream);
+        if (hooks.active()) {
+            ParityHooks observed = hooks;
+            observed.stream = w.stream;
+            observed.vector_line("final_norm", m.talker.layers, w.normalized.as<bf16>(), m.talker.hidden);
+            observed.dump("final_logits", w.logits.as<bf16>(), kTalkerVocab);
+            observed.logits_line(w.logits.as<bf16>(), kTalkerVocab);
+        }
         check_cuda(cudaEventRecord(w.talker_stop, w.stream), "cudaEventRecord");
         check_cuda(cudaStreamSynchronize(w.stream), "synchronize sampled token");
         ++host_sync_count;
         ++device_sample_count;
         check_cuda(cudaEventElapsedTime(gpu_ms, w.talker_start, w.talker_stop), "cudaEventElapsedTime");
+        m.check_device_errors(errors_before);
     } catch (...) {
         cudaStreamSynchronize(w.stream);
         poisoned_ = true;
@@ -1182,7 +1374,10 @@ void Session::run_frames(Model* model, Session** s, int n, int frames, int trail
             throw std::runtime_error("frame loop would overflow the talker KV cache");
         }
     }
+    std::unique_lock<std::mutex> one_batch(model->batch_mutex, std::defer_lock);
+    if (n > 1) one_batch.lock();
     Workspace& w = n == 1 ? *s[0]->solo_ : model->batch_workspace();
+    const unsigned int errors_before = model->device_errors();
     std::vector<cudaEvent_t> marks;
     try {
         check_cuda(cudaEventSynchronize(w.table_uploaded), "cudaEventSynchronize(table)");
@@ -1204,6 +1399,7 @@ void Session::run_frames(Model* model, Session** s, int n, int frames, int trail
             check_cuda(cudaEventRecord(marks[f + 1], w.stream), "cudaEventRecord(frame mark)");
         }
         check_cuda(cudaStreamSynchronize(w.stream), "cudaStreamSynchronize(frame loop)");
+        model->check_device_errors(errors_before);
         if (frame_ms != nullptr) {
             for (int f = 0; f < frames; ++f) {
                 check_cuda(cudaEventElapsedTime(&frame_ms[f], marks[f], marks[f + 1]), "cudaEventElapsedTime");

@@ -34,6 +34,20 @@ public:
 };
 
 void check_cuda(cudaError_t status, const char* what);
+// check_cuda for the kernel launches of a frame or prompt: the host-side fault injector below can
+// make the n-th of them report a failure without any CUDA call failing
+void check_launch(cudaError_t status, const char* what);
+
+// Host-side fault injection for tests (nothing here makes a GPU fault).  fail_launch_after(n): the
+// n-th kernel launch the engine enqueues from now on reports cudaErrorLaunchOutOfResources (n = 1: the
+// next one; 0 disarms).  fail_allocation_after(n): the n-th device allocation of the engine from now
+// on throws std::bad_alloc.  Both disarm themselves after firing.
+void fail_launch_after(int n);
+void fail_allocation_after(int n);
+
+// One host-mapped word per device that the kernels' bounded waits bump when they run out, so that
+// the host sees it at its next synchronisation point without a copy.  Null before configure_device().
+volatile unsigned int* device_error_word(int device);
 
 class DeviceBuffer {
 public:
@@ -123,7 +137,7 @@ struct Workspace {
     DeviceBuffer counters;
     int scratch_splits = 0;
     int option_epoch = 0;            // Model::option_epoch the captured graphs were built under
-    std::vector<const Session*> bound;  // sessions whose page lists are resident
+    std::vector<uint64_t> bound;     // ids of the sessions whose page lists are resident (ids are never reused)
     struct Graphs {
         cudaGraphExec_t predictor = nullptr;
         cudaGraphExec_t talker = nullptr;
@@ -170,6 +184,14 @@ public:
     Workspace& batch_workspace();
     Workspace& prefill_workspace();     // rows of a prompt chunk; one prompt at a time (prefill_mutex)
     std::mutex prefill_mutex;
+    // serialises every use of the lockstep workspace (its page tables, captured graphs and stream):
+    // batch_begin, run_frames with more than one session, option changes
+    std::mutex batch_mutex;
+    // How many bounded device-side waits have run out on this device so far.  A session notes the
+    // count when it enqueues work and compares at the host synchronisation point that follows: a
+    // frame or prompt during which it advanced cannot be trusted (check_device_errors throws).
+    unsigned int device_errors() const;
+    void check_device_errors(unsigned int count_at_enqueue) const;
     int prefill_chunk = kMaxRows;       // prompt positions per pass (1: one position at a time)
     Workspace* batch_workspace_if_any() {
         std::lock_guard<std::mutex> lock(mutex);
@@ -294,6 +316,7 @@ private:
                              bool record_session_events);
 
     std::shared_ptr<Model> model_;
+    const uint64_t id_;             // unique for the life of the process
     int device_;
     int max_seq_;
     int position_ = 0;
@@ -308,6 +331,7 @@ private:
     uint32_t pending_position_ = 0;
     Workspace* pending_workspace_ = nullptr;   // whose timing events belong to the pending frame
     uint64_t pending_frame_serial_ = 0;
+    unsigned int pending_errors_ = 0;           // Model::device_errors() when the pending frame was enqueued
     // true while this session's own stream may hold work a lockstep frame has to be ordered after
     // (prompt, solo frame, reset, a consumer's event); lockstep frames themselves leave it false
     bool own_stream_busy_ = true;

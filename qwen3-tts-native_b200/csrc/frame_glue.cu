@@ -209,6 +209,26 @@ fill_normal_kernel(bf16* __restrict__ dst, size_t count, unsigned long long seed
     }
 }
 
+// seeded pseudo-random int8 weights, uniform in [-127, 127], eight per thread and step
+__global__ void __launch_bounds__(kThreads)
+fill_bytes_kernel(unsigned char* __restrict__ dst, size_t count, unsigned long long seed) {
+    const size_t words = count / 8;
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < words; i += (size_t)gridDim.x * kThreads) {
+        unsigned long long z = i * 0x9e3779b97f4a7c15ULL + seed;
+        z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL;
+        z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL;
+        z ^= z >> 31;
+        unsigned long long out = 0;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            const int v = static_cast<int>(((z >> (8 * b)) & 0xffull) * 255ull >> 8) - 127;   // -127..127
+            out |= static_cast<unsigned long long>(static_cast<unsigned char>(v)) << (8 * b);
+        }
+        reinterpret_cast<unsigned long long*>(dst)[i] = out;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < count % 8) dst[words * 8 + threadIdx.x] = 1;
+}
+
 // grid (pages, layers*2): block (p, plane) fills the 16 x kv_width page `page_ids[p]` of that
 // K or V plane
 __global__ void __launch_bounds__(kThreads)
@@ -299,6 +319,15 @@ cudaError_t launch_fill_normal(bf16* dst, size_t count, unsigned long long seed,
     size_t blocks = (count + kThreads - 1) / kThreads;
     if (blocks > 2048) blocks = 2048;
     fill_normal_kernel<<<static_cast<unsigned int>(blocks), kThreads, 0, stream>>>(dst, count, seed);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_fill_bytes(unsigned char* dst, size_t count, unsigned long long seed, cudaStream_t stream) {
+    if (dst == nullptr || count == 0 || (reinterpret_cast<uintptr_t>(dst) & 7u) != 0) return cudaErrorInvalidValue;
+    size_t blocks = (count / 8 + kThreads - 1) / kThreads;
+    if (blocks > 4096) blocks = 4096;
+    if (blocks < 1) blocks = 1;
+    fill_bytes_kernel<<<static_cast<unsigned int>(blocks), kThreads, 0, stream>>>(dst, count, seed);
     return cudaGetLastError();
 }
 

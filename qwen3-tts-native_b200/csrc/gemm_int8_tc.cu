@@ -57,18 +57,7 @@ constexpr unsigned long long kBudgetNs = 2000000000ull;   // 2 s for the whole k
 
 __device__ unsigned int g_tc_errors = 0;
 
-// Optional phase timestamps of CTA 0 (SM clock), compiled in only for pipeline studies.
-#ifdef Q3T_TC_TRACE
-__device__ long long g_tc_trace[160];
-__device__ unsigned long long g_tc_span[2 + 2 * 160];   // min start, max end, per-CTA start/end (global timer)
-#define TC_TRACE(slot) do { if (blockIdx.x == 0 && (slot) < 160) g_tc_trace[(slot)] = clock64(); } while (0)
-#define TC_SPAN(which) do { unsigned long long now_ = 0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now_)); \
-        if (blockIdx.x < 160) g_tc_span[2 + 2 * blockIdx.x + (which)] = now_; \
-        if (which) atomicMax(&g_tc_span[1], now_); else atomicMin(&g_tc_span[0], now_); } while (0)
-#else
-#define TC_TRACE(slot) do { } while (0)
-#define TC_SPAN(which) do { } while (0)
-#endif
+__device__ unsigned int* g_tc_error_sink = nullptr;   // host-mapped word of the engine, if any
 
 struct TcParams {
     const float* scales;
@@ -308,9 +297,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
         scale = p.scales[channel];
         if (GATEUP) scale_up = p.scales[N + channel];
     }
-
-    if (tid == 0) TC_TRACE(0);
-    if (tid == 0) TC_SPAN(0);
     Guard guard;
     guard.deadline = now_ns() + kBudgetNs;
     guard.abort_flag = abort_flag;
@@ -342,7 +328,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    if (tid == 0) TC_TRACE(1);
     // The weight copies (warp 0) start at once: weights never depend on the kernel before this
     // one.  Everyone else first waits for that kernel to complete (activations, residual), and
     // only then is the kernel after this one let in: every kernel of the library signals its
@@ -353,7 +338,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     if (warp >= 1 && warp <= 3) {
         pdl_wait();
         if (warp == 1) pdl_trigger();
-        if (tid == 32) TC_TRACE(2);
     }
 
     if (warp == 0) {
@@ -393,9 +377,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 const int sa = i % kAStages;
                 const int sx = i % kXStages;
                 bool ok = true;
-                if (i < 16) TC_TRACE(64 + i);
                 ok = ok && guard.wait(&full_a[sa], (i / kAStages) & 1);
-                if (i < 16) TC_TRACE(80 + i);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_col = tmem_base + kAccCols + sa * kAStageCols;
@@ -408,7 +390,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                                 (i | j) != 0 ? 1u : 0u);
                 }
                 umma_commit(&empty_a[sa]);       // frees the TMEM stage and the activation stage
-                if (i < 16) TC_TRACE(8 + i);
             }
             umma_commit(acc_done);   // fires when every MMA issued above has completed
         }
@@ -424,7 +405,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             // a wait that gives up does so for the whole warp: the warp-level syncs below must be
             // reached by all 32 lanes or by none
             if (!__all_sync(0xffffffffu, guard.wait(&full_w[s], (i / kWStages) & 1))) { ok = false; break; }
-            if (t == 0 && i < 16) TC_TRACE(24 + i);
             // this thread's row: 128 bytes, whose 16-byte pieces sit at piece ^ (row & 7)
             const unsigned char* rowp = w8 + s * kWStageBytes + t * 128;
             int4 raw[8];
@@ -458,10 +438,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 mbar_arrive(&full_a[sa]);
                 mbar_arrive(&empty_w[s]);
             }
-            if (t == 0 && i < 16) TC_TRACE(40 + i);
         }
         if (ok) ok = guard.wait(acc_done, 0);
-        if (t == 0 && group == 0) TC_TRACE(56);
         if (!ok) *abort_flag = 1;
         // all accumulator readers meet here, so that they agree on whether the tile is complete
         dequant_barrier();
@@ -472,7 +450,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             constexpr int kCols = MT / kGroups;
             float v[kCols];
             tmem_load_row<kCols>(lane_base + group * kCols, v);
-            if (t == 0 && group == 0) TC_TRACE(61);
             if (p.splits == 1) {
                 // nothing to exchange: park the rows in this CTA's own shared memory
 #pragma unroll
@@ -492,7 +469,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                     }
                 }
             }
-            if (t == 0 && group == 0) TC_TRACE(62);
         }
     }
 
@@ -515,13 +491,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     };
     if (base_wanted && p.residual_settled != 0) fetch_bases();
     if (warp == 0 || warp >= 4) pdl_wait();
-    if (tid == 128) TC_TRACE(63);
     if (base_wanted && p.residual_settled == 0) fetch_bases();
     __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    if (tid == 0) TC_TRACE(57);
     cluster_sync();       // the only cluster barrier: nothing remote is touched after it
-    if (tid == 0) TC_TRACE(58);
     if (*abort_flag == 0 && channel < N) {
         const int row0 = split * rows_share;
         const int my_rows = min(rows_share, p.rows - row0);
@@ -548,7 +521,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 }
             }
             const size_t out = (size_t)(row0 + j) * N + channel;
-            if (tid == 0 && u < 3) TC_TRACE(100 + 3 * u);
             float val;
             if (GATEUP) {
                 const float gate = acc * scale;
@@ -560,22 +532,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 val = finish(p, acc, scale, channel, out, base_wanted && u < kBasePre, base);
             }
             if (p.y32 != nullptr) p.y32[out] = val;
-            if (tid == 0 && u < 3) TC_TRACE(101 + 3 * u);
             if (!GATEUP && p.epilogue == EPI_BIAS_ADD) p.resid[out] = f2bf(val);
             else p.y[out] = f2bf(val);
-            if (tid == 0 && u < 3) TC_TRACE(102 + 3 * u);
         }
     }
-    if (tid == 0) TC_TRACE(59);
     __syncthreads();
     if (*abort_flag) {
         // give copies that are still in flight time to land before the CTA's memory is released
-        if (tid == 0) atomicAdd(&g_tc_errors, 1u);
+        if (tid == 0) {
+            atomicAdd(&g_tc_errors, 1u);
+            if (g_tc_error_sink != nullptr) atomicAdd_system(g_tc_error_sink, 1u);
+        }
         const unsigned long long until = now_ns() + 200000ull;
         while (now_ns() < until) __nanosleep(1000);
         __syncthreads();
     }
-    if (tid == 0) TC_SPAN(1);
     if (warp == 3) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
                      : "memory");
@@ -790,6 +761,10 @@ unsigned int gemm_tc_error_count() {
     unsigned int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_errors, sizeof(v)) != cudaSuccess) return ~0u;
     return v;
+}
+
+cudaError_t set_tc_error_sink(unsigned int* device_visible_word) {
+    return cudaMemcpyToSymbol(g_tc_error_sink, &device_visible_word, sizeof(device_visible_word));
 }
 
 }  // namespace q3t

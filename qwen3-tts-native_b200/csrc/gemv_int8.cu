@@ -355,36 +355,33 @@ bool pdl_enabled() {
     return on;
 }
 
+namespace {
+// 0: SIMT only, 1: tensor-core GEMV where it applies (default), 2: the bulk-copy SIMT kernel where it applies
+int g_gemv_mode = [] {
+    const char* v = std::getenv("QWEN3_TTS_B1_GEMV");
+    if (v != nullptr && std::strcmp(v, "simt") == 0) return 0;
+    if (v != nullptr && std::strcmp(v, "bulk") == 0) return 2;
+    return 1;
+}();
+}  // namespace
+
+int set_gemv_mode(int mode) {
+    const int before = g_gemv_mode;
+    if (mode >= 0 && mode <= 2) g_gemv_mode = mode;
+    return before;
+}
+int gemv_mode() { return g_gemv_mode; }
+
+// Which kernel takes a projection:
+//   9..64 rows, K a multiple of 128     tcgen05 kernel (gemm_int8_tc.cu)
+//   1..8 rows, K = 512 * {2,3,4,6,...}   mma.sync kernel (gemv_int8_mma.cu): weights bulk-copied ahead of the
+//                                       dependency wait, 1e-6-level agreement with the SIMT kernel
+//   everything else, or gemv mode 0     SIMT kernel below, which keeps the reference's summation order
+//                                       bit for bit (mode 0 is for callers that need exactly that)
 cudaError_t launch_int8_gemm(const GemvArgs& a, cudaStream_t stream) {
-    // Batch-1 dispatch between the SIMT kernel and the bulk-copy kernel.  The bulk kernel keeps a
-    // CTA's whole weight slice on its way into shared memory while the kernel before it still
-    // runs; it wins when the matrix comes from HBM and the slice of an SM fits its 96 KB of rings
-    // (6144 x 2048: 3.9 us against 4.9 us).  Larger matrices refill the rings behind eight warps and
-    // lose to the SIMT kernel's many warps, and matrices that sit in L2 during a frame gain nothing,
-    // so by default only plain and residual epilogues without the RMSNorm prologue, rows of at
-    // most 2048 weights and 8..14 MB take it.  QWEN3_TTS_B1_GEMV = "bulk": every supported shape;
-    // "simt": never; QWEN3_TTS_B1_BULK_MIN_MB moves the lower bound.
-    static const int b1_mode = [] {
-        const char* v = std::getenv("QWEN3_TTS_B1_GEMV");
-        if (v != nullptr && std::strcmp(v, "bulk") == 0) return 2;
-        if (v != nullptr && std::strcmp(v, "simt") == 0) return 0;
-        if (v != nullptr && std::strcmp(v, "fit") == 0) return 3;   // every epilogue, slice must fit the rings
-        return 1;
-    }();
-    static const size_t b1_min_bytes = [] {
-        const char* v = std::getenv("QWEN3_TTS_B1_BULK_MIN_MB");
-        const long mb = v != nullptr ? std::strtol(v, nullptr, 10) : 8;
-        return static_cast<size_t>(mb < 0 ? 0 : mb) << 20;
-    }();
-    constexpr size_t b1_max_bytes = (size_t)14 << 20;      // 148 SMs x 96 KB of rings
     if (gemm_tc_supports(a)) return launch_int8_gemm_tc(a, stream);
-    if (b1_mode != 0 && gemv_b1_supports(a)) {
-        const size_t bytes = (size_t)a.in_features * a.out_features * (a.epilogue == EPI_GATE_UP_SILU ? 2 : 1);
-        const bool plain = a.norm_w == nullptr && (a.epilogue == EPI_PLAIN || a.epilogue == EPI_ADD);
-        if (b1_mode == 2 || ((plain || b1_mode == 3) && a.in_features <= 2048 && bytes >= b1_min_bytes && bytes <= b1_max_bytes)) {
-            return launch_int8_gemv_b1(a, stream);
-        }
-    }
+    if (g_gemv_mode == 1 && gemv_mma_supports(a)) return launch_int8_gemv_mma(a, stream);
+    if (g_gemv_mode == 2 && gemv_b1_supports(a)) return launch_int8_gemv_b1(a, stream);
     return launch_int8_gemm_simt(a, stream);
 }
 

@@ -38,44 +38,7 @@ constexpr int kWaitLimit = 1 << 22;          // mbarrier try_wait attempts befor
 
 __device__ unsigned int g_gemv_b1_errors = 0;
 
-// Optional phase timestamps for study builds (-DQ3T_B1_TRACE): lane 0 of every warp of every
-// 37th CTA writes %globaltimer at the marked points.  Compiled out otherwise.
-#ifdef Q3T_B1_TRACE
-__device__ unsigned long long g_b1_trace[8 * 8 * 16];
-#define B1_TRACE(slot)                                                                          \
-    do {                                                                                        \
-        if ((threadIdx.x & 31) == 0 && blockIdx.x % 37 == 0 && (slot) < 16) {                     \
-            unsigned long long t_;                                                              \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
-            g_b1_trace[(blockIdx.x / 37 * 8 + threadIdx.x / 32) * 16 + (slot)] = t_;              \
-        }                                                                                       \
-    } while (0)
-__device__ unsigned long long g_b1_cta_times[8 * 256 * 2];   // [launch % 8][CTA]: dependency wait returned, last warp done
-__device__ unsigned int g_b1_smid[8 * 256];
-__device__ unsigned long long g_b1_start[8 * 256];
-__device__ unsigned int g_b1_launches;                        // launches completed (CTA 0 counts at exit)
-#define B1_TRACE_CTA(which)                                                                     \
-    do {                                                                                        \
-        if ((threadIdx.x & 31) == 0 && blockIdx.x < 256) {                                        \
-            unsigned long long t_;                                                              \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
-            if (!(which)) trace_launch_ = *reinterpret_cast<volatile unsigned int*>(&g_b1_launches); \
-            unsigned long long* e_ = &g_b1_cta_times[((trace_launch_ & 7) * 256 + blockIdx.x) * 2]; \
-            if (which) atomicMax(e_ + 1, t_);                                                    \
-            else if (threadIdx.x == 0) {                                                         \
-                e_[0] = t_;                                                                      \
-                unsigned int sm_;                                                                \
-                asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_));                                 \
-                g_b1_smid[(trace_launch_ & 7) * 256 + blockIdx.x] = sm_;                           \
-                g_b1_start[(trace_launch_ & 7) * 256 + blockIdx.x] = trace_start_;                 \
-            }                                                                                    \
-            if ((which) && blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_b1_launches, 1u);     \
-        }                                                                                       \
-    } while (0)
-#else
-#define B1_TRACE(slot) do { } while (0)
-#define B1_TRACE_CTA(which) do { } while (0)
-#endif
+__device__ unsigned int* g_gemv_b1_error_sink = nullptr;   // host-mapped word of the engine, if any
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -116,10 +79,6 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
         ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
 }
-
-
-
-
 
 // byte `I` of a word of unsigned-biased weights as the float 2^23 + byte
 template <int I>
@@ -180,12 +139,6 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
     using R = Ring<VPL>;
     constexpr int K = R::kK;
     constexpr int STAGES = R::kStages;
-#ifdef Q3T_B1_TRACE
-    unsigned int trace_launch_ = 0;
-    unsigned long long trace_start_;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(trace_start_));
-#endif
-    B1_TRACE(0);
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* ring = smem;
     bf16* xs = reinterpret_cast<bf16*>(smem + R::kRingBytes);
@@ -250,12 +203,9 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
     // the stream is resident while this one computes: its weight slice is already in its rings
     // when this grid completes.  Only the weights and scales were touched so far; the activations
     // below are the predecessor's output.
-    B1_TRACE(1);
     pdl_wait();
     pdl_trigger();   // after the wait, as everywhere in the library; the successor's CTAs move in as this
                      // grid's predecessors' CTAs leave and fetch their weights while this one computes
-    B1_TRACE(2);
-    B1_TRACE_CTA(0);
 
     // ---- the activations of this lane, as fp32 in registers ------------------------------
     // Lane l owns the 16-byte weight vectors l, l+32, ... of every row, so it needs the same
@@ -305,7 +255,6 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
     }
 
     const unsigned long long neg_bias = pack2(-8388736.0f, -8388736.0f);   // -(2^23 + 128)
-    B1_TRACE(3);
     // The warp reductions of up to kGroup consecutive pairs run together (their shuffle chains
     // are independent, so a group pays the five-step latency once), and the group's results are
     // then spread over lanes 0..2*kGroup-1, which run the epilogue side by side.  The pair loop
@@ -334,7 +283,6 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
             break;
         }
         const unsigned char* a = my_ring + (size_t)stage * R::kPairBytes;
-        B1_TRACE(4 + 3 * it);
         float ra, rb;
         if (kVectorPairs) {
             float row_acc[2] = {0.0f, 0.0f};
@@ -404,7 +352,6 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue(stage, next);
         }
-        B1_TRACE(5 + 3 * it);
 #pragma unroll
         for (int k = 0; k < kGroup; ++k) {      // static indices keep the partials in registers
             if (gi == k) {
@@ -416,7 +363,6 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
         ++it;
         done = gi + 1;
       }
-      B1_TRACE(12);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
@@ -425,7 +371,6 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
             pb[gi] += __shfl_down_sync(0xffffffffu, pb[gi], o);
         }
       }
-      B1_TRACE(13);
       // lane 2g takes the first row of the group's pair g, lane 2g+1 its second row
       float mine = 0.0f;
 #pragma unroll
@@ -458,12 +403,13 @@ __global__ void __launch_bounds__(kThreads, VPL <= 6 ? 2 : 1) gemv_b1_kernel(con
             store_result(p, c, mine, scale);
         }
       }
-      B1_TRACE(14);
     }
-    B1_TRACE_CTA(1);
     if (failed) {
         // record, then give the copies already issued a bounded chance to land before leaving
-        if (lane == 0) atomicAdd(&g_gemv_b1_errors, 1u);
+        if (lane == 0) {
+            atomicAdd(&g_gemv_b1_errors, 1u);
+            if (g_gemv_b1_error_sink != nullptr) atomicAdd_system(g_gemv_b1_error_sink, 1u);
+        }
         // (the stages after the failed one were filled or refilled earlier; none is issued now)
         for (int d = 1; d < STAGES; ++d) {
             pair += kWarps;
@@ -564,6 +510,10 @@ unsigned int gemv_b1_error_count() {
     unsigned int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_gemv_b1_errors, sizeof(v)) != cudaSuccess) return ~0u;
     return v;
+}
+
+cudaError_t set_gemv_b1_error_sink(unsigned int* device_visible_word) {
+    return cudaMemcpyToSymbol(g_gemv_b1_error_sink, &device_visible_word, sizeof(device_visible_word));
 }
 
 }  // namespace q3t

@@ -64,21 +64,24 @@ cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
 }
 
-// Dispatcher: 1..8 rows run the SIMT kernel; more rows run it in passes of 8 rows.
+// Dispatcher over the kernels below (see its definition for the rule)
 cudaError_t launch_int8_gemm(const GemvArgs& args, cudaStream_t stream);
 cudaError_t launch_int8_gemm_simt(const GemvArgs& args, cudaStream_t stream);
 // batch-1 kernel (bulk-copy rings, packed fp32x2 math): rows == 1 and K in {1024,2048,3072,6144}
 bool gemv_b1_supports(const GemvArgs& args);
 cudaError_t launch_int8_gemv_b1(const GemvArgs& args, cudaStream_t stream);
 cudaError_t configure_gemv_b1_kernels();
-// chain of dependent batch-1 GEMVs in one persistent cooperative launch (gemv_chain.cu):
-// rows == 1, K a multiple of 1024 up to 6144; bit-identical to the SIMT kernel
-constexpr int kMaxChainOps = 8;
-constexpr int kChainSyncWords = 4;       // barrier arrivals, exit tickets, errors, spare (zeroed once)
-bool gemv_chain_supports(const GemvArgs& args);
-cudaError_t launch_gemv_chain(const GemvArgs* ops, int count, unsigned int* sync, cudaStream_t stream);
-cudaError_t configure_gemv_chain_kernels();   // also allocates the default counters of the device
-unsigned int gemv_chain_error_count();
+// 1..8 rows on mma.sync with the weights bulk-copied ahead of the dependency wait (gemv_int8_mma.cu):
+// K = 512 * {2, 3, 4, 6, 8, 9, 12, ...}; same value as the SIMT kernel up to the order of summation
+bool gemv_mma_supports(const GemvArgs& args);
+cudaError_t launch_int8_gemv_mma(const GemvArgs& args, cudaStream_t stream);
+cudaError_t configure_gemv_mma_kernels();
+unsigned int gemv_mma_error_count();
+// which kernel launch_int8_gemm picks for 1..8 rows: 0 SIMT (the reference's summation order, bit for
+// bit), 1 mma.sync where it applies (default), 2 the bulk-copy SIMT kernel where it applies.
+// Process-wide; returns the previous mode.
+int set_gemv_mode(int mode);
+int gemv_mode();
 // tensor-core path (tcgen05, TMEM accumulators): rows >= tc_min_rows() and K % 64 == 0
 bool gemm_tc_supports(const GemvArgs& args);
 cudaError_t launch_int8_gemm_tc(const GemvArgs& args, cudaStream_t stream);
@@ -262,6 +265,8 @@ cudaError_t launch_prompt_combine(const FrameTable* table, const int* text_ids, 
 // benchmark harness: seeded pseudo-random N(0,1) fills of a flat buffer / of whole KV pages
 // (grid over `pages` page ids and `planes` = layers*2 K/V planes of every slab)
 cudaError_t launch_fill_normal(bf16* dst, size_t count, unsigned long long seed, cudaStream_t stream);
+// seeded pseudo-random int8 values uniform in [-127, 127]; dst 8-byte aligned
+cudaError_t launch_fill_bytes(unsigned char* dst, size_t count, unsigned long long seed, cudaStream_t stream);
 cudaError_t launch_fill_kv_pages(bf16* const* slabs, int slab_shift, long long page_elems,
                                  long long plane_elems, const int* page_ids, int pages, int planes,
                                  unsigned long long seed, cudaStream_t stream);

@@ -111,7 +111,8 @@ EXPORTED_SYMBOLS = (
     "q3t_launch_int8_gemm_rows", "q3t_launch_int8_gemm_rows_add",
     "q3t_launch_int8_gate_up_silu_rows", "q3t_launch_int8_gemm_ex",
     "q3t_launch_quantize_weight_rows", "q3t_benchmark_int8_gemv", "q3t_launch_rms_norm_rows",
-    "q3t_launch_int8_gemv_chain", "q3t_benchmark_int8_gemv_chain", "q3t_host_pump_frames",
+    "q3t_set_gemv_mode", "q3t_test_fail_launch_after", "q3t_test_fail_allocation_after",
+    "q3t_test_report_device_wait_failure", "q3t_host_pump_frames",
     "q3t_pump_create", "q3t_pump_destroy", "q3t_pump_register", "q3t_pump_unregister",
     "q3t_pump_begin_frame", "q3t_pump_statistics", "q3t_pick_device",
     "q3t_launch_head_rms_norm_rows", "q3t_launch_rope_rows_at", "q3t_launch_kv_scatter_rows",
@@ -142,9 +143,15 @@ def library() -> C.CDLL:
                 "(there is no CPU fallback for the decode path)")
         lib = C.CDLL(path)
         lib.qwen3_tts_talker_abi_version.restype = C.c_uint32
-        lib.q3t_attention_scratch_bytes.restype = C.c_size_t
-        lib.q3t_attention_static_scratch_capacity.restype = C.c_size_t
-        lib.q3t_kernel_error_count.restype = C.c_uint32
+        # (a library that exports only the reference's own ABI may be loaded through
+        # QWEN3_TTS_TALKER_LIBRARY for side-by-side runs: the q3t_* additions are then absent)
+        for name, restype in (("q3t_attention_scratch_bytes", C.c_size_t),
+                              ("q3t_attention_static_scratch_capacity", C.c_size_t),
+                              ("q3t_kernel_error_count", C.c_uint32),
+                              ("q3t_test_fail_launch_after", None),
+                              ("q3t_test_fail_allocation_after", None)):
+            if hasattr(lib, name):
+                getattr(lib, name).restype = restype
         lib.qwen3_tts_model_destroy.restype = None
         lib.qwen3_tts_session_destroy.restype = None
         lib.qwen3_tts_model_destroy.argtypes = [C.c_void_p]
@@ -178,16 +185,17 @@ def library() -> C.CDLL:
         lib.qwen3_tts_model_create.argtypes = [C.c_int32, C.POINTER(C.c_void_p), C.c_char_p, C.c_size_t]
         lib.qwen3_tts_model_finalize.argtypes = [C.c_void_p, C.POINTER(ModelMemoryC), C.c_char_p,
                                                  C.c_size_t]
-        lib.q3t_model_run_frames.argtypes = [
-            C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, SamplingConfigC,
-            SamplingConfigC, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_char_p, C.c_size_t]
-        lib.q3t_model_set_option.argtypes = [C.c_void_p, C.c_char_p, C.c_int32, C.c_char_p, C.c_size_t]
-        lib.q3t_session_read_state.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                               C.c_char_p, C.c_size_t]
-        lib.q3t_session_synthetic_prefill.argtypes = [C.c_void_p, C.c_int32, C.c_uint64, C.c_char_p,
-                                                      C.c_size_t]
-        lib.q3t_model_kernel_launches.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.c_char_p,
-                                                  C.c_size_t]
+        for name, argtypes in (
+                ("q3t_model_run_frames", [
+                    C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, SamplingConfigC,
+                    SamplingConfigC, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_char_p, C.c_size_t]),
+                ("q3t_model_set_option", [C.c_void_p, C.c_char_p, C.c_int32, C.c_char_p, C.c_size_t]),
+                ("q3t_session_read_state", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p,
+                                            C.c_size_t]),
+                ("q3t_session_synthetic_prefill", [C.c_void_p, C.c_int32, C.c_uint64, C.c_char_p, C.c_size_t]),
+                ("q3t_model_kernel_launches", [C.c_void_p, C.POINTER(C.c_uint64), C.c_char_p, C.c_size_t])):
+            if hasattr(lib, name):
+                getattr(lib, name).argtypes = argtypes
         _lib = lib
     return _lib
 
@@ -592,14 +600,10 @@ def probe_device(device_index: int = 0) -> DeviceInfoC:
     return out
 
 
-def benchmark_int8_gemv_chain(device_index: int, in_features: int, out_features: int, chain: int = 8,
-                              buffers: int = 16, iterations: int = 2000) -> GemvBenchmarkC:
-    """GEMVs chained `chain` to a persistent launch; the mean is per GEMV."""
-    out = GemvBenchmarkC()
-    err = C.create_string_buffer(_ERR_CAP)
-    _check(library().q3t_benchmark_int8_gemv_chain(device_index, in_features, out_features, chain, buffers,
-                                                   iterations, C.byref(out), err, _ERR_CAP), err)
-    return out
+def set_gemv_mode(mode: int) -> int:
+    """Kernel for projections of 1..8 rows: 0 SIMT (bit-identical to the reference's summation order),
+    1 mma.sync where the shape allows (default), 2 bulk-copy SIMT.  Returns the previous mode."""
+    return int(library().q3t_set_gemv_mode(int(mode)))
 
 
 def benchmark_int8_gemv(device_index: int, in_features: int, out_features: int, rows: int = 1,

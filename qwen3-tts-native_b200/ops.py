@@ -98,54 +98,6 @@ def int8_gemm(w, scales, x, *, epilogue=EPI_PLAIN, y_in=None, norm_w=None, bias=
                 resid=_u16(dr) if dr is not None else None)
 
 
-def int8_gemv_chain(links):
-    """One persistent launch over a chain of batch-1 GEMVs.  `links` is a list of dicts with keys
-    w, scales, x (name of a buffer or a host array), y (name), epilogue and optionally norm_w, bias,
-    resid (name); buffers named by strings are device vectors shared between links, so a link can
-    read what an earlier link wrote.  Returns {name: host array} of every named buffer."""
-    lib = native.library()
-    named = {}
-    keep = []
-    descs = (GemmDescC * len(links))()
-
-    def buf(spec, width):
-        if isinstance(spec, str):
-            if spec not in named:
-                named[spec] = torch.zeros((1, width), dtype=torch.int16, device="cuda")
-            return named[spec]
-        t = _dev(np.ascontiguousarray(spec, dtype=np.uint16).reshape(1, -1))
-        keep.append(t)
-        return t
-
-    for d, link in zip(descs, links):
-        w = np.asarray(link["w"], dtype=np.int8)
-        epi = link.get("epilogue", EPI_PLAIN)
-        wr, k = w.shape
-        n = wr // 2 if epi == EPI_GATE_UP_SILU else wr
-        dw, ds = _dev(w), _dev(np.asarray(link["scales"], dtype=np.float32))
-        keep += [dw, ds]
-        d.struct_size = C.sizeof(GemmDescC)
-        d.epilogue = epi
-        d.weight, d.scales = dw.data_ptr(), ds.data_ptr()
-        d.input = buf(link["x"], k).data_ptr()
-        if "init" in link:           # initial contents of a named buffer (e.g. a residual stream)
-            for name, values in link["init"].items():
-                t = buf(name, np.asarray(values).size)
-                t.copy_(_dev(np.ascontiguousarray(values, dtype=np.uint16).reshape(1, -1)))
-        if epi == EPI_BIAS_ADD:
-            d.residual = buf(link["resid"], n).data_ptr()
-        else:
-            d.output = buf(link["y"], n).data_ptr()
-        for key, field in (("norm_w", "norm_weight"), ("bias", "bias")):
-            if link.get(key) is not None:
-                t = _dev(np.asarray(link[key], dtype=np.uint16))
-                keep.append(t)
-                setattr(d, field, t.data_ptr())
-        d.in_features, d.out_features, d.rows, d.epsilon = k, n, 1, 1.0e-6
-    _ok(lib.q3t_launch_int8_gemv_chain(descs, len(links), None), "q3t_launch_int8_gemv_chain")
-    return {name: _u16(t) for name, t in named.items()}
-
-
 _weight_cache = {}
 
 

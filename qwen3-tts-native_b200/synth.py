@@ -75,8 +75,13 @@ def _kind(name: str) -> str:
     return "matrix"
 
 
-def make_tensor(name: str, shape: Tuple[int, ...], seed: int = 0) -> np.ndarray:
-    """bf16 bit patterns (uint16) of one tensor; depends only on (name, shape, seed)."""
+def make_tensor(name: str, shape: Tuple[int, ...], seed: int = 0, exact_int8: bool = False) -> np.ndarray:
+    """bf16 bit patterns (uint16) of one tensor; depends only on (name, shape, seed, exact_int8).
+
+    exact_int8: every decode matrix is int8-representable as a bf16 tensor: row = q * 2^e with
+    integer q in [-127, 127], one |q| = 127 per row and a power-of-two scale.  The per-row int8
+    quantizer (scale = absmax / 127, q = round(w / scale)) then returns exactly q and 2^e, so a bf16
+    GEMM over the tensor and an int8 GEMM over its quantized form multiply the same numbers."""
     g = torch.Generator()
     g.manual_seed((zlib.crc32(name.encode()) ^ (seed * 0x9E3779B1)) & 0x7FFFFFFF)
     kind = _kind(name)
@@ -87,7 +92,13 @@ def make_tensor(name: str, shape: Tuple[int, ...], seed: int = 0) -> np.ndarray:
     else:
         rows, cols = shape
         q = torch.randint(-127, 128, shape, generator=g, dtype=torch.int8)
-        scale = (0.5 + torch.rand((rows, 1), generator=g)) / (73.6 * float(cols) ** 0.5)
+        if exact_int8:
+            q[:, 0] = 127
+            exponent = torch.round(torch.log2((0.5 + torch.rand((rows, 1), generator=g))
+                                              / (73.6 * float(cols) ** 0.5)))
+            scale = torch.pow(2.0, exponent)
+        else:
+            scale = (0.5 + torch.rand((rows, 1), generator=g)) / (73.6 * float(cols) ** 0.5)
         t = q.to(torch.float32) * scale
     return t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
 
@@ -114,7 +125,8 @@ def checkpoint_cuda(device: int, seed: int = 0,
         yield name, t.to(torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
 
 
-def checkpoint(seed: int = 0, predictor_head_dim: int = 128) -> Iterator[Tuple[str, np.ndarray]]:
+def checkpoint(seed: int = 0, predictor_head_dim: int = 128,
+               exact_int8: bool = False) -> Iterator[Tuple[str, np.ndarray]]:
     """Yields (name, bf16 bits) for all 404 tensors, one at a time (about 3.8 GB in total)."""
     for name, shape in tensor_shapes(predictor_head_dim).items():
-        yield name, make_tensor(name, shape, seed)
+        yield name, make_tensor(name, shape, seed, exact_int8)

@@ -12,6 +12,16 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
+
+@pytest.fixture(autouse=True)
+def simt_kernels(q3t):
+    """These tests pin the kernel that keeps the reference's summation order (gemv mode 0); the
+    default kernel for 1..8 rows has its own file, test_gpu_gemv_mma.py."""
+    before = q3t.native.set_gemv_mode(0)
+    yield
+    q3t.native.set_gemv_mode(before)
+
+
 SHAPES = [  # (out_features, in_features)
     (8, 16), (5, 32), (33, 64), (130, 272),
     (6144, 2048),   # config 0 / gate, up
@@ -20,7 +30,7 @@ SHAPES = [  # (out_features, in_features)
     (3072, 2048),   # codec head
     (2048, 1024),   # predictor lm_head / q
     (1024, 3072),   # predictor down
-    (131, 1024), (77, 3072), (5, 6144),   # odd channel counts on the batch-1 kernel
+    (131, 1024), (77, 3072), (5, 6144),   # odd channel counts
 ]
 
 
@@ -163,6 +173,17 @@ def test_quantizer_vs_reference_kernel(orc, ops, ref):
     assert np.array_equal(q, rq) and np.array_equal(s, rs)
 
 
+@pytest.mark.parametrize("n,k", [(6144, 2048), (2048, 6144), (131, 1024)])
+def test_bulk_copy_simt_kernel_bit_exact(orc, ops, q3t, n, k):
+    """gemv mode 2: the bulk-copy SIMT kernel for one row keeps the same summation order."""
+    q3t.native.set_gemv_mode(2)
+    w, s, x = case(orc, 13, n, k, 1)
+    base = orc.to_bf16(np.random.default_rng(14).standard_normal((1, n)).astype(np.float32))
+    assert np.array_equal(ops.int8_gemm_rows(w, s, x), orc.int8_gemm_rows(w, s, x))
+    assert np.array_equal(ops.int8_gemm_rows(w, s, x, y_in=base, mode=1),
+                          orc.int8_gemm_rows(w, s, x, y_in=base, mode=1))
+
+
 def test_no_device_wait_ran_out(q3t, ops):
-    """The bulk-copy GEMV bounds every mbarrier wait; a healthy run never exhausts one."""
+    """The bulk-copy GEMVs bound every mbarrier wait; a healthy run never exhausts one."""
     assert q3t.library().q3t_kernel_error_count() == 0
