@@ -1,44 +1,51 @@
 // Int8 weight-only GEMV / skinny GEMM for 1..8 activation rows: bulk copies ahead of the dependency
-// wait, the arithmetic on the tensor cores.
+// wait, integer tensor-core arithmetic on the raw weight bytes.
 //
-// y[r][n] = epilogue( scale[n] * sum_k W[n][k] * x[r][k] ), W int8 [N][K] row-major, x bf16, fp32
-// accumulate: the arithmetic of the reference's int8_dequant_gemm_kernel, its residual form and its
-// gate/up/SiLU form (native/qwen3-tts-native/native/src/int8_gemv.cu:58-293) with the RMSNorm that
-// precedes them (talker_kernels.cu:27-48) as an optional prologue.  What bounds a batch-1 GEMV on
-// B200 is not the 12.6 MB it streams but what its CTAs still have to do once the launch before it
-// has finished, so this kernel moves everything it can ahead of that point and keeps the rest short:
+// y[r][n] = epilogue( scale[n] * sum_k W[n][k] * x[r][k] ), W int8 [N][K] row-major, x bf16: the
+// operation of the reference's int8_dequant_gemm_kernel, its residual form and its gate/up/SiLU form
+// (native/qwen3-tts-native/native/src/int8_gemv.cu:58-293) with the RMSNorm that precedes them
+// (talker_kernels.cu:27-48) as an optional prologue.
 //
-//   before the dependency wait    One CTA per SM owns a contiguous slice of the output channels.  Its
-//                                 weights go to shared memory as tiles of 16 rows, one bulk
-//                                 asynchronous copy per row (cp.async.bulk, completion counted on an
-//                                 mbarrier per tile), rows 64 bytes further apart than their length so
-//                                 that the fragment loads below hit every bank once.  Two CTAs fit on
-//                                 an SM: under programmatic stream serialisation the slice of the next
-//                                 GEMV in the stream is on its way while this one computes.  Scales,
-//                                 biases, RMSNorm weights and (when the caller says they are settled)
-//                                 the residual are requested here too.
-//   after it                      Warp w owns an eighth of K.  Its lanes read their part of the
-//                                 activation rows straight into registers, as the B fragments of
-//                                 mma.sync.m16n8k16: row r of the batch is column r of B, so 1..8 rows
-//                                 cost what one row costs and a row's result does not depend on the
-//                                 rows beside it.  The weight tile is the A operand: a lane loads 16
-//                                 bytes of rows g and g+8 and turns them into fp16 exactly (XOR to
-//                                 unsigned, PRMT of two bytes beside the exponent byte of 1024, one
-//                                 packed subtract of 1152): an eighth of the instructions that one FMA
-//                                 per weight and lane needs.  Contraction index k is permuted the
-//                                 same way on both operands, so 16 consecutive bytes feed four MMAs.
-//   activations as fp16           bf16 has the range of fp32 and fp16 has not, so every warp scales
-//                                 its part of a row by the power of two that puts the part's largest
-//                                 magnitude in [2^14, 2^15) and removes the factor from its partial
-//                                 sums again: exact for every element within 2^28 of the largest
-//                                 (bf16 has 8 significant bits, fp16 11), below fp32 rounding noise
-//                                 for the rest.  Products are exact, accumulation is fp32.
-//   the end                       The eight warps' partial sums meet in shared memory and are added in
-//                                 warp order (deterministic); the epilogues are the SIMT kernel's.
+// What bounds a batch-1 GEMV on B200 is not the 12.6 MB it streams but (a) when the copies are
+// requested and (b) how many instructions each weight costs once the launch before it has finished:
+// one FMA per weight and lane, or one byte permute per two weights to feed an fp16 MMA, both leave
+// the kernel issue-bound at about half of the memory roofline.  So:
 //
-// The fp32 value differs from the SIMT kernel's only by the order of summation (the north-star
-// tolerance is 1e-3 relative; this is ~1e-6).  Callers that need the reference's exact summation
-// order select the SIMT kernel (set_gemv_mode).
+//   before the dependency wait    One CTA per SM owns a contiguous slice of the output channels, in
+//                                 tiles of 16 rows.  The rows of a tile are consecutive in global
+//                                 memory, so a tile is TWO bulk asynchronous copies of eight rows
+//                                 into shared memory (cp.async.bulk, completion counted on an
+//                                 mbarrier): the copy engine spends about as long on a 1 KB copy as on
+//                                 a 16 KB one, and the 64 bytes between the two halves keep the
+//                                 fragment loads below free of bank conflicts.  Two CTAs fit on an SM:
+//                                 the slice of the next GEMV in the stream is on its way while this
+//                                 one computes.  Scales, biases and RMSNorm weights are requested
+//                                 here too.
+//   after it, activations         Warp w owns an eighth of K.  Its 32 lanes fetch that part of every
+//                                 activation row with coalesced loads and turn it into fixed point:
+//                                 x * 2^e rounded to an integer of 22 bits, e chosen per row and warp
+//                                 from the largest magnitude of the part.  Every element within 2^13
+//                                 of that magnitude is represented exactly (bf16 has 8 significant
+//                                 bits), the rest to 2^-21 of it: more than an fp32 accumulator keeps.
+//                                 The integer plus 2^22 is written to shared memory as three unsigned
+//                                 bytes ("limbs"), one row of bytes per limb.
+//   after it, weights             mma.sync.m16n8k32 (s8 x u8 -> s32): the weight bytes are the A
+//                                 operand exactly as they lie in memory, no conversion and no
+//                                 instruction but the 16-byte shared-memory loads; the three limbs of
+//                                 an activation row are three COLUMNS of B, a fourth column of ones
+//                                 yields the row sums of W that the offset of 2^22 has to be corrected
+//                                 by.  Products and sums are integers: exact, in any order.  A 16-byte
+//                                 load of two weight rows feeds two MMAs; contraction index k is
+//                                 permuted the same way on both operands.
+//   the end                       Per warp: (limb2 - 64 * ones) * 65536 + limb1 * 256 + limb0, times
+//                                 2^-e, in fp32.  The eight warps' values meet in shared memory and are
+//                                 added in warp order; the epilogues are the SIMT kernel's.
+//
+// Against the SIMT kernel (the reference's summation order) the fp32 value differs at the 1e-6 level;
+// the north-star tolerance is 1e-3 relative.  Because the arithmetic on the weights is exact, a row's
+// result does not depend on the rows computed beside it, bit for bit.  Callers that need the
+// reference's exact summation order select the SIMT kernel (set_gemv_mode).
+//
 // Every mbarrier wait is bounded; a wait that runs out bumps an error counter, lets the copies
 // already issued land and ends the kernel.
 
@@ -53,10 +60,13 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / kWarp;
 constexpr int kTileRows = 16;              // weight rows per tile = M of the MMA
-constexpr int kMaxGroup = 3;               // tiles whose accumulators a warp keeps at once
+constexpr int kMaxGroup = 3;               // tiles whose partial sums wait in shared memory at once
 constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 110 * 1024;    // per CTA: two CTAs per SM
-constexpr int kWaitLimit = 1 << 22;        // mbarrier try_wait attempts before giving up
+constexpr int kSmemBudget = 113 * 1024;    // per CTA: two CTAs per SM (228 KB, 1 KB of it reserved per CTA)
+constexpr int kWaitLimit = 1 << 17;        // mbarrier try_wait attempts before giving up (a fraction of a second)
+constexpr int kXsPad = 16;                 // bytes between limb rows in shared memory (bank spread)
+constexpr int kLimbs = 3;
+constexpr int kHalfPad = 64;               // bytes between the two halves of a weight tile (bank spread)
 
 __device__ unsigned int g_gemv_mma_errors = 0;
 __device__ unsigned int* g_gemv_mma_error_sink = nullptr;   // host-mapped word of the engine, if any
@@ -97,22 +107,21 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
         : "memory");
 }
 
-// two bytes of a word of unsigned-biased weights (w + 128) as two fp16 weights, exactly:
-// {byte, 0x64} is the fp16 1024 + byte = 1152 + w
-template <int kSelector>
-__device__ __forceinline__ uint32_t weights_f16x2(uint32_t biased_word) {
-    const uint32_t carried = __byte_perm(biased_word, 0x64646464u, kSelector);
-    uint32_t d;
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(carried), "r"(0x64806480u));   // - (1152, 1152)
-    return d;
+// D(16x8, s32) += A(16x32, s8, row) * B(32x8, u8, col)
+__device__ __forceinline__ void imma_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                          uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// byte `kByte` of four words, gathered into one word
+template <int kByte>
+__device__ __forceinline__ uint32_t gather_byte(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+    const uint32_t lo = __byte_perm(w0, w1, ((4 + kByte) << 4) | kByte);
+    const uint32_t hi = __byte_perm(w2, w3, ((4 + kByte) << 4) | kByte);
+    return __byte_perm(lo, hi, 0x5410);
 }
 
 struct MmaParams {
@@ -130,21 +139,22 @@ struct MmaParams {
     int rows;               // 1..8
     int epilogue;
     float eps;
-    int chunks;             // K = chunks * 512 * J
     int stages;             // tiles resident in shared memory
-    int group;              // tiles per accumulator group, 1..kMaxGroup
-    int red_cols;           // columns kept per row in the exchange buffer: rows rounded up to even
-    int residual_settled;
+    int group;              // tiles per exchange of partial sums, 1..kMaxGroup
+    int ring_bytes;         // shared memory of the weight stages (the last stage may be a short one)
 };
 
-// Lane (g, t) = (lane / 4, lane % 4) of warp w owns, of chunk c of every activation and weight row,
-// the 16 elements at c * KC + w * KW + 64 * j + 16 * t for j = 0..J-1.
-template <int J, bool GATEUP, bool NORM>
-__global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const MmaParams p) {
-    constexpr int KC = 512 * J;                    // K elements per chunk
-    constexpr int KW = 64 * J;                     // ... of which one warp owns these
+// Q = K / 512: warp w owns the K elements [w * 64 Q, (w + 1) * 64 Q) of every row.  As MMA operand,
+// lane (g, t) = (lane / 4, lane % 4) owns of that range the 16 elements at 64 j + 16 t, j = 0..Q-1; in
+// the conversion of the activations lane l owns the 2 Q elements at 2 Q l.  Column c of the B operand
+// of 8-column group q: limb c % 4 of activation row 2 q + c / 4, where "limb 3" is all ones.
+// NTMAX: 8-column groups of B a launch may need: 1 serves one or two activation rows, 4 up to eight.
+template <int Q, bool GATEUP, bool NORM, int NTMAX>
+__global__ void __launch_bounds__(kThreads, NTMAX == 1 ? 2 : 1) gemv_mma_kernel(const MmaParams p) {
+    constexpr int KW = 64 * Q;                     // K elements of one warp
     constexpr int kOut = GATEUP ? 8 : 16;          // output channels per tile
     constexpr uint32_t kFull = 0xffffffffu;
+    constexpr int RB = (32 / Q) > 8 ? 8 : (32 / Q);   // activation rows fetched together (registers)
 
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x;
@@ -152,12 +162,19 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const MmaParams p
     const int warp = tid / kWarp;
     const int g = lane >> 2;
     const int t = lane & 3;
-    const int N = p.N, K = p.K, R = p.rows, S = p.stages, C = p.chunks, RP = p.red_cols, Gf = p.group;
+    const int N = p.N, K = p.K, R = p.rows, S = p.stages, Gf = p.group;
+    const int xs_stride = K + kXsPad;              // bytes between limb rows
+    const int NT = (R + 1) / 2;                    // MMAs per 32 k: two activation rows per 8 columns
 
-    const int stage_bytes = kTileRows * K;         // a tile: 16 weight rows, as they lie in global memory
+    // A tile in shared memory: two halves of eight weight rows as they lie in global memory, the second
+    // half 64 bytes further than the first ends.  MMA row m is row m / 2 of half m % 2, so the two
+    // lanes of a quarter-warp that read the same 16-byte column of their rows hit different banks.
+    const int half_bytes = 8 * K + kHalfPad;
+    const int stage_bytes = 2 * half_bytes;
     unsigned char* ring = smem;
-    float* red = reinterpret_cast<float*>(smem + (size_t)S * stage_bytes);     // [warp][tile][16][RP]
-    float* partial = red + kWarps * Gf * kTileRows * RP;                       // NORM: [rows][256]
+    unsigned char* xs = smem + p.ring_bytes;                                    // [R][limb][K + pad] bytes
+    float* red = reinterpret_cast<float*>(xs + (size_t)R * kLimbs * xs_stride); // [warp][row of x][4][16]
+    float* partial = red + kWarps * R * 64;                                      // NORM: [rows][256]
     uint64_t* bars = reinterpret_cast<uint64_t*>(partial + (NORM ? R * kThreads : 0));
     unsigned int* done = reinterpret_cast<unsigned int*>(bars + S);
 
@@ -166,48 +183,53 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const MmaParams p
     const int c1 = static_cast<int>(static_cast<unsigned int>(N) * (blockIdx.x + 1) / gridDim.x);
     const int T = (c1 - c0 + kOut - 1) / kOut;
 
-    // One lane requests tile `tile` into its stage: the rows of a tile are consecutive in global
-    // memory, so a tile is one bulk copy (two for gate and up rows); a copy costs the copy engine
-    // about the same whatever its size, so fewer and larger ones arrive sooner.
+    // One lane requests tile `tile` into its stage: one bulk copy per half (gate rows and up rows, or
+    // the first and the second eight channels).
     auto issue_tile = [&](int tile) {
         const int stage = tile % S;
         const int first = c0 + tile * kOut;
         const int valid = min(kOut, c1 - first);
         uint64_t* bar = &bars[stage];
         unsigned char* dst = ring + (size_t)stage * stage_bytes;
-        const uint32_t bytes = static_cast<uint32_t>(valid) * K;
-        mbar_expect_tx(bar, GATEUP ? 2 * bytes : bytes);
-        bulk_load(dst, p.w + (size_t)first * K, bytes, bar);
-        if (GATEUP) bulk_load(dst + 8 * (size_t)K, p.w + ((size_t)N + first) * K, bytes, bar);
+        if (GATEUP) {
+            const uint32_t bytes = static_cast<uint32_t>(valid) * K;
+            mbar_expect_tx(bar, 2 * bytes);
+            bulk_load(dst, p.w + (size_t)first * K, bytes, bar);
+            bulk_load(dst + half_bytes, p.w + ((size_t)N + first) * K, bytes, bar);
+        } else {
+            const int lower = min(valid, 8), upper = valid - lower;
+            mbar_expect_tx(bar, static_cast<uint32_t>(valid) * K);
+            bulk_load(dst, p.w + (size_t)first * K, static_cast<uint32_t>(lower) * K, bar);
+            if (upper > 0) {
+                bulk_load(dst + half_bytes, p.w + (size_t)(first + 8) * K, static_cast<uint32_t>(upper) * K, bar);
+            }
+        }
     };
 
-    // Warp w sets up the barrier of stage w and requests the unit that starts in it at once: nothing
+    // Warp w sets up the barrier of stage w and requests the tile that starts in it at once: nothing
     // here waits for another warp.  (The other warps meet these barriers only after the CTA-wide
     // barrier further down.)
-    if (warp < S) {
-        if (lane == 0) {
-            mbar_init(&bars[warp], 1);
-            done[warp] = 0;
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            if (warp < T) issue_tile(warp);
-        }
+    if (warp < S && lane == 0) {
+        mbar_init(&bars[warp], 1);
+        done[warp] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (warp < T) issue_tile(warp);
     }
 
     // ---- constants of the epilogue, requested now ------------------------------------------------
-    // Thread tid finishes outputs idx = tid and tid + 256 of a group: idx = (tile * 16 + row) * RP + col.
+    // Thread tid finishes outputs idx = tid and tid + 256 of a group: idx = col * 64 + tile * 16 + row.
     const int first_group = min(Gf, T);
     float pre_scale[2] = {0.0f, 0.0f}, pre_scale_up[2] = {0.0f, 0.0f}, pre_bias[2] = {0.0f, 0.0f};
-    float pre_base[2] = {0.0f, 0.0f};
     auto decode = [&](int idx, int group_base, int group_tiles, int& channel, int& col) -> bool {
-        col = idx % RP;
-        const int rest = idx / RP;
-        const int row = rest & (kTileRows - 1);
-        const int gt = rest >> 4;
+        col = idx >> 6;
+        const int gt = (idx >> 4) & 3;
+        const int row = idx & (kTileRows - 1);
         channel = c0 + (group_base + gt) * kOut + row;
         return gt < group_tiles && col < R && row < kOut && channel < c1;
     };
     const bool adds = p.epilogue == EPI_ADD || p.epilogue == EPI_BIAS_ADD;
+    const bool biased_epilogue = p.epilogue == EPI_BIAS || p.epilogue == EPI_BIAS_SILU || p.epilogue == EPI_BIAS_ADD;
     const bf16* base_src = p.epilogue == EPI_ADD ? p.y : p.resid;
     bool pre_ok[2];
     int pre_channel[2], pre_col[2];
@@ -217,58 +239,36 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const MmaParams p
         if (pre_ok[q]) {
             pre_scale[q] = p.scales[pre_channel[q]];
             if (GATEUP) pre_scale_up[q] = p.scales[N + pre_channel[q]];
-            if (p.epilogue == EPI_BIAS || p.epilogue == EPI_BIAS_SILU || p.epilogue == EPI_BIAS_ADD) {
-                pre_bias[q] = bf2f(p.bias[pre_channel[q]]);
-            }
-            if (adds && p.residual_settled) pre_base[q] = bf2f(base_src[(size_t)pre_col[q] * N + pre_channel[q]]);
+            if (biased_epilogue) pre_bias[q] = bf2f(p.bias[pre_channel[q]]);
         }
     }
-    // RMSNorm weights of this lane's K elements
-    uint32_t nw[NORM ? 8 * J : 1];
+    // RMSNorm weights of the elements this lane converts
+    uint32_t nw[NORM ? Q : 1];
     if (NORM) {
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.norm_w + warp * KW + 2 * Q * lane);
 #pragma unroll
-        for (int j = 0; j < J; ++j) {
-            const int4* src = reinterpret_cast<const int4*>(p.norm_w + warp * KW + 64 * j + 16 * t);
-            const int4 a = src[0], b = src[1];
-            nw[NORM ? 8 * j + 0 : 0] = a.x; nw[NORM ? 8 * j + 1 : 0] = a.y;
-            nw[NORM ? 8 * j + 2 : 0] = a.z; nw[NORM ? 8 * j + 3 : 0] = a.w;
-            nw[NORM ? 8 * j + 4 : 0] = b.x; nw[NORM ? 8 * j + 5 : 0] = b.y;
-            nw[NORM ? 8 * j + 6 : 0] = b.z; nw[NORM ? 8 * j + 7 : 0] = b.w;
-        }
+        for (int m = 0; m < Q; ++m) nw[NORM ? m : 0] = src[m];
     }
 
     __syncthreads();     // the barriers set up above are visible to every warp
 
-    // Everything above touched only constants of the model (and values the caller declared settled).
+    // Everything above touched only constants of the model.
     pdl_wait();
-    pdl_trigger();
+    pdl_trigger();   // after the wait, as everywhere in the library.  (Triggering at kernel start was
+                     // measured: the successor's bulk copies then collide with this kernel's fetch of
+                     // its activations, which costs more than the earlier start of the copies gains.)
 
-    if (adds && !p.residual_settled) {
+    // the value a residual epilogue adds to: requested now, needed at the very end
+    float pre_base[2] = {0.0f, 0.0f};
+    if (adds) {
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             if (pre_ok[q]) pre_base[q] = bf2f(base_src[(size_t)pre_col[q] * N + pre_channel[q]]);
         }
     }
 
-    // ---- activations -----------------------------------------------------------------------------
-    const bool has_row = g < R;
-    const bf16* xrow = p.x + (size_t)(has_row ? g : 0) * K + warp * KW + 16 * t;
-    uint32_t raw[8 * J];                    // packed bf16 pairs of the current (or next) chunk
-    auto load_raw = [&](int chunk) {
-#pragma unroll
-        for (int j = 0; j < J; ++j) {
-            int4 a = make_int4(0, 0, 0, 0), b = make_int4(0, 0, 0, 0);
-            if (has_row) {
-                const int4* src = reinterpret_cast<const int4*>(xrow + (size_t)chunk * KC + 64 * j);
-                a = src[0];
-                b = src[1];
-            }
-            raw[8 * j + 0] = a.x; raw[8 * j + 1] = a.y; raw[8 * j + 2] = a.z; raw[8 * j + 3] = a.w;
-            raw[8 * j + 4] = b.x; raw[8 * j + 5] = b.y; raw[8 * j + 6] = b.z; raw[8 * j + 7] = b.w;
-        }
-    };
-    load_raw(0);
-
+    // ---- activations: fetched by all lanes, converted, parked in shared memory as fp16 ------------
+    float inv_mine = 0.0f;           // NORM: lane r keeps 1/rms of row r
     if (NORM) {
         // sum of squares in the order of the stand-alone RMSNorm (thread i takes elements i, i + 256,
         // ...; halving tree over the 256 partial sums), so that the normalised row is bit-identical
@@ -282,157 +282,245 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const MmaParams p
             partial[r * kThreads + tid] = ss;
         }
         __syncthreads();
-        float inv = 0.0f;
         for (int r = 0; r < R; ++r) {
             const float total = tree_sum_256(partial + r * kThreads, lane);
             const float v = rsqrtf(total / static_cast<float>(K) + p.eps);
-            if (r == g) inv = v;
+            if (r == lane) inv_mine = v;
         }
+    }
+    // Arrival of the tiles of a group (long there, in a chain of launches: the test costs its latency
+    // only, which the first group hides behind the fetch of the activations).
+    bool failed = false;
+    int stage = 0;                           // (tiles waited for) % S and its phase, kept without divisions
+    uint32_t parity = 0;
+    int stage_of[kMaxGroup] = {};
+    auto await_group = [&](int group_tiles) {
 #pragma unroll
-        for (int m = 0; m < 8 * J; ++m) {
-            const uint32_t wv = nw[NORM ? m : 0];
-            const float lo = rbf(bf_lo(raw[m]) * inv) * bf_lo(wv);
-            const float hi = rbf(bf_hi(raw[m]) * inv) * bf_hi(wv);
-            const __nv_bfloat162 o = __floats2bfloat162_rn(lo, hi);
-            raw[m] = *reinterpret_cast<const uint32_t*>(&o);
+        for (int gt = 0; gt < kMaxGroup; ++gt) {
+            if (gt < group_tiles && !failed) {
+                bool ready = mbar_try_wait(&bars[stage], parity);
+                if (!ready) ready = mbar_wait_bounded(&bars[stage], parity);
+                if (!__all_sync(kFull, ready)) failed = true;
+                stage_of[gt] = stage;
+                if (++stage == S) {
+                    stage = 0;
+                    parity ^= 1u;
+                }
+            }
         }
-        if (p.norm_out != nullptr && blockIdx.x == 0 && has_row) {
+    };
+
+    float unscale_mine = 1.0f;       // lane r keeps 2^-e of row r in this warp's part
+    {
+        const size_t my_offset = (size_t)warp * KW + 2 * Q * lane;      // elements
+#pragma unroll 1
+        for (int r0 = 0; r0 < R; r0 += RB) {
+            uint32_t raw[RB][Q];
 #pragma unroll
-            for (int j = 0; j < J; ++j) {
-                int4* dst = reinterpret_cast<int4*>(p.norm_out + (size_t)g * K + warp * KW + 64 * j + 16 * t);
-                dst[0] = make_int4(raw[8 * j + 0], raw[8 * j + 1], raw[8 * j + 2], raw[8 * j + 3]);
-                dst[1] = make_int4(raw[8 * j + 4], raw[8 * j + 5], raw[8 * j + 6], raw[8 * j + 7]);
+            for (int b = 0; b < RB; ++b) {
+                if (r0 + b < R) {
+                    const bf16* src = p.x + (size_t)(r0 + b) * K + my_offset;
+                    if constexpr (Q % 4 == 0) {
+#pragma unroll
+                        for (int m = 0; m < Q / 4; ++m) {
+                            const int4 v = reinterpret_cast<const int4*>(src)[m];
+                            raw[b][4 * m + 0] = v.x; raw[b][4 * m + 1] = v.y;
+                            raw[b][4 * m + 2] = v.z; raw[b][4 * m + 3] = v.w;
+                        }
+                    } else if constexpr (Q % 2 == 0) {
+#pragma unroll
+                        for (int m = 0; m < Q / 2; ++m) {
+                            const int2 v = reinterpret_cast<const int2*>(src)[m];
+                            raw[b][2 * m + 0] = v.x; raw[b][2 * m + 1] = v.y;
+                        }
+                    } else {
+#pragma unroll
+                        for (int m = 0; m < Q; ++m) raw[b][m] = reinterpret_cast<const uint32_t*>(src)[m];
+                    }
+                }
+            }
+            if (r0 == 0) await_group(min(Gf, T));      // the activations are in flight meanwhile
+#pragma unroll
+            for (int b = 0; b < RB; ++b) {
+                const int r = r0 + b;
+                if (r < R) {
+                    if (NORM) {
+                        const float inv = __shfl_sync(kFull, inv_mine, r);
+#pragma unroll
+                        for (int m = 0; m < Q; ++m) {
+                            const uint32_t wv = nw[NORM ? m : 0];
+                            const float lo = rbf(bf_lo(raw[b][m]) * inv) * bf_lo(wv);
+                            const float hi = rbf(bf_hi(raw[b][m]) * inv) * bf_hi(wv);
+                            const __nv_bfloat162 o = __floats2bfloat162_rn(lo, hi);
+                            raw[b][m] = *reinterpret_cast<const uint32_t*>(&o);
+                        }
+                        if (p.norm_out != nullptr && blockIdx.x == 0) {
+                            uint32_t* dst = reinterpret_cast<uint32_t*>(p.norm_out + (size_t)r * K + my_offset);
+#pragma unroll
+                            for (int m = 0; m < Q; ++m) dst[m] = raw[b][m];
+                        }
+                    }
+                    // largest magnitude of the row in this warp's part -> its power of two
+                    __nv_bfloat162 m2 = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&raw[b][0]));
+#pragma unroll
+                    for (int m = 1; m < Q; ++m) {
+                        m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&raw[b][m])));
+                    }
+                    const uint32_t mbits = *reinterpret_cast<const uint32_t*>(&m2);
+                    const uint32_t top = __reduce_max_sync(kFull, max(mbits & 0xffffu, mbits >> 16));
+                    const uint32_t eb_raw = (top >> 7) & 0xffu;              // biased exponent of the largest magnitude
+                    const uint32_t eb = min(max(eb_raw, 21u), 240u);
+                    const float scale = __uint_as_float((274u - eb) << 23);  // largest magnitude -> [2^20, 2^21)
+                    if (lane == r) {
+                        // 1 / scale; an infinity or NaN among the activations makes the row's results NaN
+                        unscale_mine = eb_raw == 255u ? __uint_as_float(0x7fc00000u) : __uint_as_float((eb - 20u) << 23);
+                    }
+                    // x * scale + 1.5 * 2^23 rounds to an integer in fp32 whose low 23 bits are the fixed-point
+                    // value plus 2^22: bytes 0, 1, 2 of the float's bit pattern are the three limbs
+                    uint32_t fixed[2 * Q];
+#pragma unroll
+                    for (int m = 0; m < Q; ++m) {
+                        fixed[2 * m] = __float_as_uint(fmaf(bf_lo(raw[b][m]), scale, 12582912.0f));
+                        fixed[2 * m + 1] = __float_as_uint(fmaf(bf_hi(raw[b][m]), scale, 12582912.0f));
+                    }
+                    unsigned char* dst = xs + (size_t)r * kLimbs * xs_stride + my_offset;
+#pragma unroll
+                    for (int m = 0; m < Q / 2; ++m) {
+                        const uint32_t f0 = fixed[4 * m], f1 = fixed[4 * m + 1], f2 = fixed[4 * m + 2], f3 = fixed[4 * m + 3];
+                        reinterpret_cast<uint32_t*>(dst)[m] = gather_byte<0>(f0, f1, f2, f3);
+                        reinterpret_cast<uint32_t*>(dst + xs_stride)[m] = gather_byte<1>(f0, f1, f2, f3);
+                        reinterpret_cast<uint32_t*>(dst + 2 * xs_stride)[m] = gather_byte<2>(f0, f1, f2, f3);
+                    }
+                }
             }
         }
     }
+    __syncwarp();        // this warp's part of every row is in shared memory; no other warp reads it
 
-    // B fragments: the lane's elements of row g times 2^e, as fp16 pairs; `unscale` is 2^-e
-    uint32_t xb[8 * J];
-    float scale_now = 1.0f, unscale = 1.0f;
-    auto convert = [&]() {
-        __nv_bfloat162 m2 = __floats2bfloat162_rn(0.0f, 0.0f);
-#pragma unroll
-        for (int m = 0; m < 8 * J; ++m) {
-            m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&raw[m])));
-        }
-        const uint32_t mbits = *reinterpret_cast<const uint32_t*>(&m2);
-        uint32_t top = max(mbits & 0xffffu, mbits >> 16);       // bits of the largest magnitude (bf16, sign clear)
-        top = max(top, __shfl_xor_sync(kFull, top, 1));
-        top = max(top, __shfl_xor_sync(kFull, top, 2));
-        uint32_t eb = (top >> 7) & 0xffu;                        // its biased exponent
-        eb = min(max(eb, 16u), 254u);
-        scale_now = __uint_as_float((268u - eb) << 23);          // largest magnitude -> [2^14, 2^15)
-        unscale = __uint_as_float((eb - 14u) << 23);
-#pragma unroll
-        for (int m = 0; m < 8 * J; ++m) {
-            const __half2 h = __floats2half2_rn(bf_lo(raw[m]) * scale_now, bf_hi(raw[m]) * scale_now);
-            xb[m] = *reinterpret_cast<const uint32_t*>(&h);
+    // ---- B fragments come from shared memory --------------------------------------------------------
+    // Column g of 8-column group q, for activation rows 2q (g < 4) and 2q + 1 (g >= 4): limbs 0, 1, 2 and
+    // a column of ones.  The accumulator lanes t = 0, 1 then hold {limb 0, limb 1} and {limb 2, ones} of
+    // the even row, lanes t = 2, 3 the same of the odd row: a row's value is put together by two
+    // neighbouring lanes.
+    const int col_limb = g & 3;
+    const unsigned char* my_x = xs + (size_t)col_limb * xs_stride + warp * KW + 16 * t;
+    auto load_b = [&](int j, int q, uint32_t (&b)[4]) {
+        const int row = 2 * q + (g >> 2);
+        if (col_limb < 3 && row < R) {
+            const int4 v = *reinterpret_cast<const int4*>(my_x + (size_t)row * kLimbs * xs_stride + 64 * j);
+            b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w;
+        } else {
+            const uint32_t fill = col_limb == 3 ? 0x01010101u : 0u;
+            b[0] = fill; b[1] = fill; b[2] = fill; b[3] = fill;
         }
     };
 
     // ---- tiles -----------------------------------------------------------------------------------
-    // One tile at a time and one copy of the arithmetic (the loops over tiles and chunks are not
-    // unrolled: the code stays in the instruction cache).  After up to Gf tiles the warps' partial
-    // sums meet in shared memory.
-    bool failed = false;
+    // Up to kMaxGroup tiles run side by side: K is the outer loop, so a B fragment is fetched once for
+    // all of them and a warp has several independent accumulator chains in flight.  After a group the
+    // warps' values meet in shared memory.
     int tile = 0;                            // tiles consumed so far (uniform over the CTA)
-    bool converted = false;
-    const unsigned char* my_rows = ring + (size_t)g * K + warp * KW + 16 * t;
-    float* mine = red + (size_t)warp * Gf * kTileRows * RP;
-    for (int group_base = 0; group_base < T && !failed; group_base += Gf) {
+    const unsigned char* my_rows = ring + (size_t)(g & 1) * half_bytes + (size_t)(g >> 1) * K + warp * KW + 16 * t;
+    const int row_lo = 8 * (g & 1) + (g >> 1);      // where MMA rows g and g + 8 sit in the tile
+    const int row_hi = row_lo + 4;
+    float* mine = red + (size_t)warp * R * 64;
+    constexpr int kChains = NTMAX == 1 ? 2 : 1;     // accumulator sets per tile and column group
+    float unscale[NTMAX][2];                        // 2^-e of the activation rows 2q and 2q + 1
+#pragma unroll
+    for (int q = 0; q < NTMAX; ++q) {
+        unscale[q][0] = __shfl_sync(kFull, unscale_mine, 2 * q);
+        unscale[q][1] = __shfl_sync(kFull, unscale_mine, 2 * q + 1);
+    }
+    for (int group_base = 0; group_base < T; group_base += Gf) {      // left only after the CTA-wide vote below
         const int G = min(Gf, T - group_base);
-#pragma unroll 1
-        for (int gt = 0; gt < G && !failed; ++gt) {
-            // four accumulator sets, one per MMA of a 16-byte group: four independent chains instead of
-            // one chain of dependent tensor-core instructions; they are added in a fixed order below
-            float acc[4][4];
+        if (group_base > 0) await_group(G);
+        const unsigned char* rows[kMaxGroup];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f;
-            }
-            const int stage = tile % S;
-            const uint32_t parity = static_cast<uint32_t>(tile / S) & 1u;
-            bool waited = false;
-#pragma unroll 1
-            for (int c = 0; c < C; ++c) {
-                // activations of this chunk; with one chunk the first conversion serves every tile
-                if (C > 1 || !converted) {
-                    const float before = scale_now;
-                    convert();
-                    converted = true;
-                    if (c > 0) {
-                        // the accumulators carry the previous chunk's power of two: bring them to this one's
-                        const float ratio = scale_now / before;
-                        const float r0 = __shfl_sync(kFull, ratio, 8 * t);
-                        const float r1 = __shfl_sync(kFull, ratio, 8 * t + 4);
+        for (int gt = 0; gt < kMaxGroup; ++gt) rows[gt] = my_rows + (size_t)stage_of[gt] * stage_bytes;
+        if (!failed) {
+            int acc[kMaxGroup][NTMAX][kChains][4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            acc[i][0] *= r0; acc[i][1] *= r1; acc[i][2] *= r0; acc[i][3] *= r1;
+            for (int gt = 0; gt < kMaxGroup; ++gt)
+#pragma unroll
+                for (int q = 0; q < NTMAX; ++q)
+#pragma unroll
+                    for (int h = 0; h < kChains; ++h)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[gt][q][h][c] = 0;
+#pragma unroll
+            for (int j = 0; j < Q; ++j) {
+                uint32_t b[NTMAX][4];
+#pragma unroll
+                for (int q = 0; q < NTMAX; ++q) {
+                    if (q < NT) load_b(j, q, b[q]);
+                }
+#pragma unroll
+                for (int gt = 0; gt < kMaxGroup; ++gt) {
+                    if (gt < G) {
+                        const int4 wa = *reinterpret_cast<const int4*>(rows[gt] + 64 * j);
+                        const int4 wb = *reinterpret_cast<const int4*>(rows[gt] + 4 * (size_t)K + 64 * j);
+#pragma unroll
+                        for (int q = 0; q < NTMAX; ++q) {
+                            if (q < NT) {
+                                imma_16832(acc[gt][q][0], wa.x, wb.x, wa.y, wb.y, b[q][0], b[q][1]);
+                                imma_16832(acc[gt][q][kChains - 1], wa.z, wb.z, wa.w, wb.w, b[q][2], b[q][3]);
+                            }
                         }
                     }
-                    // request the elements of the chunk after this one (of this tile or the next)
-                    if (C > 1 && (c + 1 < C || tile + 1 < T)) load_raw((c + 1) % C);
-                }
-                if (!waited) {
-                    waited = true;
-                    if (!__all_sync(kFull, mbar_wait_bounded(&bars[stage], parity))) {
-                        failed = true;
-                        break;
-                    }
-                }
-                const unsigned char* rows_lo = my_rows + (size_t)stage * stage_bytes + (size_t)c * KC;
-                const unsigned char* rows_hi = rows_lo + 8 * (size_t)K;
-                int4 wa = *reinterpret_cast<const int4*>(rows_lo);
-                int4 wb = *reinterpret_cast<const int4*>(rows_hi);
-#pragma unroll
-                for (int j = 0; j < J; ++j) {
-                    const uint32_t ua[4] = {(uint32_t)wa.x ^ 0x80808080u, (uint32_t)wa.y ^ 0x80808080u,
-                                            (uint32_t)wa.z ^ 0x80808080u, (uint32_t)wa.w ^ 0x80808080u};
-                    const uint32_t ub[4] = {(uint32_t)wb.x ^ 0x80808080u, (uint32_t)wb.y ^ 0x80808080u,
-                                            (uint32_t)wb.z ^ 0x80808080u, (uint32_t)wb.w ^ 0x80808080u};
-                    if (j + 1 < J) {      // the next group's bytes are on their way while this one is converted
-                        wa = *reinterpret_cast<const int4*>(rows_lo + 64 * (j + 1));
-                        wb = *reinterpret_cast<const int4*>(rows_hi + 64 * (j + 1));
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        mma_16816(acc[i], weights_f16x2<0x4140>(ua[i]), weights_f16x2<0x4140>(ub[i]),
-                                  weights_f16x2<0x4342>(ua[i]), weights_f16x2<0x4342>(ub[i]),
-                                  xb[8 * j + 2 * i], xb[8 * j + 2 * i + 1]);
-                    }
                 }
             }
-            if (failed) break;
-            __syncwarp();      // every lane has read the stage
-            if (T > S) {
+            __syncwarp();      // every lane has read the stages
+            if (T > S && lane == 0) {
                 // the last of the eight warps to leave a stage requests the tile that reuses it
-                unsigned int before = 0;
-                if (lane == 0) {
-                    __threadfence_block();
-                    before = atomicAdd(&done[stage], 1u);
-                    if ((before & (kWarps - 1)) == kWarps - 1 && tile + S < T) {
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        issue_tile(tile + S);
+                __threadfence_block();
+#pragma unroll
+                for (int gt = 0; gt < kMaxGroup; ++gt) {
+                    if (gt < G) {
+                        const unsigned int before = atomicAdd(&done[stage_of[gt]], 1u);
+                        if ((before & (kWarps - 1)) == kWarps - 1 && tile + gt + S < T) {
+                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            issue_tile(tile + gt + S);
+                        }
                     }
                 }
             }
-            ++tile;
-            // this warp's share of the tile, freed of its power of two
-            const float i0 = __shfl_sync(kFull, unscale, 8 * t);
-            const float i1 = __shfl_sync(kFull, unscale, 8 * t + 4);
-            if (2 * t < RP) {
-                float2* lo = reinterpret_cast<float2*>(mine + (gt * kTileRows + g) * RP + 2 * t);
-                float2* hi = reinterpret_cast<float2*>(mine + (gt * kTileRows + g + 8) * RP + 2 * t);
-                *lo = make_float2(((acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0])) * i0,
-                                  ((acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1])) * i1);
-                *hi = make_float2(((acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2])) * i0,
-                                  ((acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3])) * i1);
+            tile += G;
+            // This warp's share of the tiles.  Of a group of four lanes, t = 0 holds limbs 0 and 1 of the
+            // even activation row and t = 1 its limb 2 and the row sum of W (t = 2, 3: the odd row).  The
+            // three limb sums are exact integers below 2^25; their combination is done in fp32, high part
+            // in the odd lane, low part in the even lane, one exchange.
+#pragma unroll
+            for (int gt = 0; gt < kMaxGroup; ++gt) {
+                if (gt < G) {
+#pragma unroll
+                    for (int q = 0; q < NTMAX; ++q) {
+                        if (q < NT) {
+                            int d[4];
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) d[c] = acc[gt][q][0][c] + (kChains == 2 ? acc[gt][q][kChains - 1][c] : 0);
+                            float part[2];      // tile rows g, g + 8
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                const int first = d[2 * half], second = d[2 * half + 1];
+                                part[half] = (t & 1) ? static_cast<float>(first - 64 * second) * 65536.0f
+                                                     : fmaf(static_cast<float>(second), 256.0f, static_cast<float>(first));
+                                part[half] += __shfl_xor_sync(kFull, part[half], 1);
+                            }
+                            const int row = 2 * q + (t >> 1);
+                            if ((t & 1) == 0 && row < R) {
+                                const float u = unscale[q][t >> 1];
+                                mine[row * 64 + gt * kTileRows + row_lo] = part[0] * u;
+                                mine[row * 64 + gt * kTileRows + row_hi] = part[1] * u;
+                            }
+                        }
+                    }
+                }
             }
         }
         // ---- the warps' partial sums meet; epilogue ------------------------------------------------
         failed = __syncthreads_or(failed ? 1 : 0) != 0;      // every thread arrives here, whatever it saw
         if (failed) break;
-        const int warp_stride = Gf * kTileRows * RP;
+        const int warp_stride = R * 64;
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             const int idx = tid + q * kThreads;
@@ -442,7 +530,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const MmaParams p
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) {
                 sum += red[w * warp_stride + idx];
-                if (GATEUP) sum_up += red[w * warp_stride + idx + 8 * RP];
+                if (GATEUP) sum_up += red[w * warp_stride + idx + 8];
             }
             const bool first = group_base == 0;
             const float scale = first ? pre_scale[q] : p.scales[channel];
@@ -499,95 +587,141 @@ int sm_count() {
     return g_sm_count[device];
 }
 
-int lanes_of(int in_features) {       // J: 64-element groups per lane and chunk
-    const int q = in_features / 512;
-    if (in_features % 512 != 0 || q < 2) return 0;
-    if (q % 4 == 0) return 4;
-    if (q % 3 == 0) return 3;
-    if (q % 2 == 0) return 2;
-    return 0;
+bool supported_q(int q, bool norm) {
+    if (norm) return q == 2 || q == 4;                  // the fused RMSNorm is built for hidden sizes 1024 and 2048
+    return q == 2 || q == 4 || q == 6 || q == 12;
 }
 
 struct Plan {
-    int j = 0, chunks = 0, grid = 0, stages = 0, group = 0, red_cols = 0;
-    size_t smem = 0;
+    int q = 0, grid = 0, stages = 0, group = 0;
+    size_t ring = 0, smem = 0;
 };
 
+constexpr int kSmemBudgetAlone = 200 * 1024;   // one CTA per SM: launches of three or more activation rows
+
+// Shared memory of a launch.  When every tile of a CTA can be resident at once, the last stage is
+// only as long as the longest last tile needs (a CTA's channels rarely fill their last tile).
+bool plan_with_budget(const GemvArgs& a, int rows, size_t budget, Plan& plan);
+
 bool plan_for(const GemvArgs& a, int rows, Plan& plan) {
-    const int j = lanes_of(a.in_features);
-    if (j == 0 || rows < 1 || rows > 8 || a.out_features < 1) return false;
-    const int chunks = a.in_features / (512 * j);
-    if (chunks > 8 || (a.norm_w != nullptr && chunks != 1)) return false;
+    // one or two rows: room for two CTAs per SM if the shape allows, else the SM to itself
+    if (rows <= 2 && plan_with_budget(a, rows, kSmemBudget, plan)) return true;
+    return plan_with_budget(a, rows, kSmemBudgetAlone, plan);
+}
+
+bool plan_with_budget(const GemvArgs& a, int rows, size_t budget, Plan& plan) {
+    if (a.in_features % 512 != 0 || rows < 1 || rows > 8 || a.out_features < 1) return false;
+    const int q = a.in_features / 512;
+    if (!supported_q(q, a.norm_w != nullptr)) return false;
     const bool gateup = a.epilogue == EPI_GATE_UP_SILU;
     const int per_tile = gateup ? 8 : 16;
+    const size_t K = a.in_features;
     int grid = sm_count();
     if (grid > a.out_features) grid = a.out_features;
     const int channels = (a.out_features + grid - 1) / grid;
     const int tiles = (channels + per_tile - 1) / per_tile;
-    const int group = tiles < kMaxGroup ? tiles : kMaxGroup;
-    const int red_cols = rows <= 2 ? 2 : (rows + 1) / 2 * 2;
-    const size_t stage_bytes = (size_t)kTileRows * a.in_features;
-    const size_t fixed = (size_t)kWarps * group * kTileRows * red_cols * sizeof(float)
+    const size_t half_bytes = 8 * K + kHalfPad;
+    const size_t stage_bytes = 2 * half_bytes;
+    const int last_rows = channels - (tiles - 1) * per_tile;         // channels of the longest last tile
+    const size_t last_bytes = gateup ? half_bytes + (size_t)last_rows * K
+                                     : (last_rows > 8 ? half_bytes + (size_t)(last_rows - 8) * K : (size_t)last_rows * K);
+    const size_t fixed = (size_t)rows * kLimbs * (K + kXsPad)
+        + (size_t)kWarps * rows * 64 * sizeof(float)
         + (a.norm_w != nullptr ? (size_t)rows * kThreads * sizeof(float) : 0)
         + kMaxStages * (sizeof(uint64_t) + sizeof(unsigned int));
-    if (fixed + stage_bytes > (size_t)kSmemBudget) return false;
-    int stages = static_cast<int>(((size_t)kSmemBudget - fixed) / stage_bytes);
-    if (stages > tiles) stages = tiles;
-    if (stages > kMaxStages) stages = kMaxStages;
-    plan.j = j; plan.chunks = chunks; plan.grid = grid; plan.stages = stages; plan.group = group;
-    plan.red_cols = red_cols;
-    plan.smem = fixed + (size_t)stages * stage_bytes;
+    const size_t all_resident = (size_t)(tiles - 1) * stage_bytes + last_bytes;
+    int stages;
+    size_t ring;
+    // The tile loop reads all sixteen rows of a stage whatever was copied into it (rows past the
+    // last channel feed accumulators nobody reads), so a short last stage must still lie inside the
+    // allocation: what follows the ring has to cover the rows that were left out.
+    if (tiles <= kMaxStages && fixed + all_resident <= budget && (size_t)tiles * stage_bytes <= budget) {
+        stages = tiles;
+        ring = (all_resident + 127) / 128 * 128;
+        if (ring + fixed < (size_t)tiles * stage_bytes) ring = (size_t)tiles * stage_bytes - fixed / 128 * 128;
+    } else {
+        if (fixed + stage_bytes > budget) return false;
+        stages = static_cast<int>((budget - fixed) / stage_bytes);
+        if (stages > kMaxStages) stages = kMaxStages;
+        if (stages >= tiles) stages = tiles;
+        ring = (size_t)stages * stage_bytes;
+    }
+    int group = tiles < kMaxGroup ? tiles : kMaxGroup;
+    if (group > stages) group = stages;         // a group's tiles are all resident before it starts
+    plan.q = q; plan.grid = grid; plan.stages = stages; plan.group = group;
+    plan.ring = ring;
+    plan.smem = fixed + ring;
     return true;
 }
 
-template <int J, bool GATEUP, bool NORM>
-cudaError_t launch_kernel(const MmaParams& p, const Plan& plan, cudaStream_t stream) {
-    return launch_pdl(gemv_mma_kernel<J, GATEUP, NORM>, dim3(static_cast<unsigned int>(plan.grid)), dim3(kThreads),
-                      plan.smem, stream, p);
-}
-
-template <int J>
-cudaError_t launch_flags(const MmaParams& p, const Plan& plan, bool gateup, bool norm, cudaStream_t stream) {
-    if (gateup) {
-        return norm ? launch_kernel<J, true, true>(p, plan, stream) : launch_kernel<J, true, false>(p, plan, stream);
+// activation rows one launch can take for this shape (more rows run as several launches)
+int rows_per_launch(const GemvArgs& a) {
+    Plan plan;
+    for (int rows = 8; rows >= 1; --rows) {
+        if (plan_for(a, rows, plan)) return rows;
     }
-    return norm ? launch_kernel<J, false, true>(p, plan, stream) : launch_kernel<J, false, false>(p, plan, stream);
+    return 0;
 }
 
-template <int J>
-cudaError_t configure_j() {
-    cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<J, false, false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<J, false, true>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<J, true, false>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<J, true, true>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+template <int Q, bool GATEUP, bool NORM>
+cudaError_t launch_rows(const MmaParams& p, const Plan& plan, cudaStream_t stream) {
+    const dim3 grid(static_cast<unsigned int>(plan.grid));
+    if (p.rows <= 2) return launch_pdl(gemv_mma_kernel<Q, GATEUP, NORM, 1>, grid, dim3(kThreads), plan.smem, stream, p);
+    return launch_pdl(gemv_mma_kernel<Q, GATEUP, NORM, 4>, grid, dim3(kThreads), plan.smem, stream, p);
+}
+
+template <int Q>
+cudaError_t launch_flags(const MmaParams& p, const Plan& plan, bool gateup, bool norm, cudaStream_t stream) {
+    if constexpr (Q == 2 || Q == 4) {
+        if (norm) {
+            return gateup ? launch_rows<Q, true, true>(p, plan, stream) : launch_rows<Q, false, true>(p, plan, stream);
+        }
+    }
+    return gateup ? launch_rows<Q, true, false>(p, plan, stream) : launch_rows<Q, false, false>(p, plan, stream);
+}
+
+template <int Q, bool GATEUP, bool NORM>
+cudaError_t configure_one() {
+    cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<Q, GATEUP, NORM, 1>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudgetAlone);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<Q, GATEUP, NORM, 4>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudgetAlone);
+    return e;
+}
+
+template <int Q>
+cudaError_t configure_q() {
+    cudaError_t e = configure_one<Q, false, false>();
+    if (e == cudaSuccess) e = configure_one<Q, true, false>();
+    if constexpr (Q == 2 || Q == 4) {
+        if (e == cudaSuccess) e = configure_one<Q, false, true>();
+        if (e == cudaSuccess) e = configure_one<Q, true, true>();
+    }
     return e;
 }
 
 }  // namespace
 
 cudaError_t configure_gemv_mma_kernels() {
-    cudaError_t e = configure_j<2>();
-    if (e == cudaSuccess) e = configure_j<3>();
-    if (e == cudaSuccess) e = configure_j<4>();
+    cudaError_t e = configure_q<2>();
+    if (e == cudaSuccess) e = configure_q<4>();
+    if (e == cudaSuccess) e = configure_q<6>();
+    if (e == cudaSuccess) e = configure_q<12>();
     sm_count();
     return e;
 }
 
 bool gemv_mma_supports(const GemvArgs& a) {
-    Plan plan;
-    if (a.rows < 1 || a.rows > kMaxRows || !plan_for(a, a.rows < 8 ? a.rows : 8, plan)) return false;
-    // bulk copies and 16-byte fragment loads need aligned sources; every row offset is a multiple of K
+    if (a.rows < 1 || a.rows > kMaxRows || rows_per_launch(a) == 0) return false;
+    // bulk copies and vector loads need aligned sources; every row offset is a multiple of K
     if ((reinterpret_cast<uintptr_t>(a.w) & 15u) != 0 || (reinterpret_cast<uintptr_t>(a.x) & 15u) != 0) return false;
     if (a.norm_w != nullptr && (reinterpret_cast<uintptr_t>(a.norm_w) & 15u) != 0) return false;
     if (a.norm_out != nullptr && (reinterpret_cast<uintptr_t>(a.norm_out) & 15u) != 0) return false;
     return true;
 }
 
-// More than 8 rows: passes of 8 rows over the same weights, each row computed exactly as it would be alone.
+// More rows than one launch takes (8, fewer for long rows): several launches over the same weights.
+// The arithmetic on a row does not depend on the rows beside it, so the split is invisible.
 cudaError_t launch_int8_gemv_mma(const GemvArgs& a, cudaStream_t stream) {
     if (!gemv_mma_supports(a) || a.w == nullptr || a.scales == nullptr || a.x == nullptr) {
         return cudaErrorInvalidValue;
@@ -599,8 +733,9 @@ cudaError_t launch_int8_gemv_mma(const GemvArgs& a, cudaStream_t stream) {
         return cudaErrorInvalidValue;
     }
     const bool norm = a.norm_w != nullptr;
-    for (int r0 = 0; r0 < a.rows; r0 += 8) {
-        const int rows = a.rows - r0 < 8 ? a.rows - r0 : 8;
+    const int step = a.rows <= 2 ? a.rows : rows_per_launch(a);
+    for (int r0 = 0; r0 < a.rows; r0 += step) {
+        const int rows = a.rows - r0 < step ? a.rows - r0 : step;
         Plan plan;
         if (!plan_for(a, rows, plan)) return cudaErrorInvalidValue;
         MmaParams p;
@@ -611,13 +746,13 @@ cudaError_t launch_int8_gemv_mma(const GemvArgs& a, cudaStream_t stream) {
         p.norm_out = a.norm_out != nullptr ? a.norm_out + (size_t)r0 * a.in_features : nullptr;
         p.resid = a.resid != nullptr ? a.resid + (size_t)r0 * a.out_features : nullptr;
         p.K = a.in_features; p.N = a.out_features; p.rows = rows; p.epilogue = a.epilogue; p.eps = a.eps;
-        p.chunks = plan.chunks; p.stages = plan.stages; p.group = plan.group; p.red_cols = plan.red_cols;
-        p.residual_settled = a.residual_settled ? 1 : 0;
+        p.stages = plan.stages; p.group = plan.group; p.ring_bytes = static_cast<int>(plan.ring);
         cudaError_t e;
-        switch (plan.j) {
+        switch (plan.q) {
             case 2: e = launch_flags<2>(p, plan, gateup, norm, stream); break;
-            case 3: e = launch_flags<3>(p, plan, gateup, norm, stream); break;
-            default: e = launch_flags<4>(p, plan, gateup, norm, stream); break;
+            case 4: e = launch_flags<4>(p, plan, gateup, norm, stream); break;
+            case 6: e = launch_flags<6>(p, plan, gateup, norm, stream); break;
+            default: e = launch_flags<12>(p, plan, gateup, norm, stream); break;
         }
         if (e != cudaSuccess) return e;
     }

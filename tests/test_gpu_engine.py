@@ -185,14 +185,16 @@ def test_lockstep_batch_equals_solo(q3t, model, n):
     """session_bench.rs protocol: identical code sequences with and without batching."""
     frames = 3
     seeds = [1000 + i for i in range(n)]
-    solo = {seed: run_solo(q3t, model, seed, frames) for seed in seeds[:3]}
     # Bit-identity with the solo run needs the reference's summation order, which the SIMT
-    # kernels keep and the tensor-core kernel (9 rows and up by default) does not.
+    # kernels keep and the tensor-core kernels (the default for every row count) do not promise.
     model.set_option("tc_min_rows", 65)
+    model.set_option("gemv_mode", 0)
     try:
+        solo = {seed: run_solo(q3t, model, seed, frames) for seed in seeds[:3]}
         sessions, got = lockstep(q3t, model, seeds, frames)
     finally:
         model.set_option("tc_min_rows", 9)
+        model.set_option("gemv_mode", 1)
     for seed in seeds[:3]:
         assert got[seed] == solo[seed], seed
     # duplicate seed => identical, different seeds => different (session_bench.rs:228-232)
@@ -303,6 +305,7 @@ def test_chunked_prompt_equals_position_by_position(q3t, orc, model):
     def run(chunk, tc_min_rows):
         model.set_option("prefill_chunk", chunk)
         model.set_option("tc_min_rows", tc_min_rows)
+        model.set_option("gemv_mode", 0 if tc_min_rows > 64 else 1)     # 65: SIMT kernels everywhere
         try:
             s = start(q3t, model, 31, max_seq=128, prompt=(text, codec))
             first = s.current_semantic_token
@@ -313,6 +316,7 @@ def test_chunked_prompt_equals_position_by_position(q3t, orc, model):
         finally:
             model.set_option("prefill_chunk", 64)
             model.set_option("tc_min_rows", 9)
+            model.set_option("gemv_mode", 1)
 
     one = run(1, 65)
     rows = run(64, 65)
@@ -356,6 +360,7 @@ def test_frame_pump_batches_concurrent_owners(q3t, model):
     import threading
     n, frames = 12, 4
     model.set_option("tc_min_rows", 65)
+    model.set_option("gemv_mode", 0)
     pump = q3t.native.BatchFramePump(model, max_batch=64, window_us=20000)
     try:
         solo = [run_solo(q3t, model, 400 + i, frames) for i in range(n)]
@@ -392,6 +397,7 @@ def test_frame_pump_batches_concurrent_owners(q3t, model):
     finally:
         pump.close()
         model.set_option("tc_min_rows", 9)
+        model.set_option("gemv_mode", 1)
     assert q3t.native.pick_device([3, 1, 1, 2]) == 1 and q3t.native.pick_device([0]) == 0
     assert q3t.native.pick_device([]) == -1
 
