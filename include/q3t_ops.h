@@ -188,13 +188,23 @@ QWEN3_TTS_API int32_t q3t_model_adopt_tensor(Qwen3TtsModelHandle model, const ch
 /* Which kernel takes projections of 1..8 rows (process-wide; returns the previous mode):
  *   0  the SIMT kernel only: the summation order of the reference's int8_dequant_gemm_kernel
  *      (int8_gemv.cu:58-128), outputs bit-identical to it;
- *   1  (default) the mma.sync kernel where the shape allows (K = 512 * {2,3,4,6,8,9,12,...}):
- *      same products, fp32 accumulation in another order (agreement ~1e-6 relative), 1..8 rows for
- *      the price of one, weights bulk-copied ahead of the launch dependency;
+ *   1  (default) the int8 tensor-core kernel where the shape allows (K = 512 * {2, 4, 6, 12}; with a
+ *      fused RMSNorm K = 512 * {2, 4}): activations as three byte limbs of a per-row fixed-point
+ *      value, exact integer products and sums (agreement ~1e-7 relative, a row's result bitwise
+ *      independent of the rows beside it), weights bulk-copied ahead of the launch dependency;
  *   2  the bulk-copy SIMT kernel where the shape allows (rows == 1), else SIMT.
  * Also reachable as model option "gemv_mode" and as QWEN3_TTS_B1_GEMV=simt|bulk at load time.
  * No reference counterpart (one kernel there). */
 QWEN3_TTS_API int32_t q3t_set_gemv_mode(int32_t mode);
+
+/* Which kernel computes decode attention (process-wide; returns the previous mode):
+ *   1  (default) the split-KV kernel: tensor-core products, chunked fp32 sums; within 1e-3 of the
+ *      reference's batch_causal_gqa_attention_fast_kernel (talker_kernels.cu:506-595) on the fp32 value;
+ *   0  parity mode: every fp32 sum in that kernel's order, bf16 output bit-identical to it; one
+ *      thread walks a whole cache row, so it is slow.  Positions must be below 8192.
+ * With gemv mode 0 and "tc_min_rows" 65 every operator of a frame is then bit-identical to the
+ * reference's.  Also reachable as model option "attention_mode". */
+QWEN3_TTS_API int32_t q3t_set_attention_mode(int32_t mode);
 
 /* ---- norms, RoPE, KV append, glue (talker_kernels.cu) --------------------------------- */
 
@@ -322,6 +332,7 @@ QWEN3_TTS_API int32_t q3t_launch_sample_logits_at(
  * logits would otherwise end a run at random), "use_graphs" (0: launch kernels one by one),
  * "batch_host_codes" (1: lockstep batches also mirror each frame's 16 codes to host memory),
  * "gemv_mode" (process-wide, see q3t_set_gemv_mode),
+ * "attention_mode" (process-wide, see q3t_set_attention_mode),
  * "tc_min_rows" (process-wide: projections with at least this many rows run on the tensor
  * cores, default 9; 65 keeps every row count on the SIMT kernels, whose results do not depend on
  * the batch size), "prefill_chunk" (prompt positions per decoder pass, 1..64, default 64: a
@@ -382,6 +393,13 @@ QWEN3_TTS_API int32_t q3t_model_kernel_launches(Qwen3TtsModelHandle model, uint6
 QWEN3_TTS_API int32_t q3t_session_read_state(Qwen3TtsSessionHandle session, uint16_t* last_hidden,
                                              int32_t* frame_tokens, uint64_t* random_state,
                                              char* error, size_t error_capacity);
+
+/* Test hook: the talker K and V rows of positions [first_position, first_position + count) of one
+ * layer as the session's cache holds them (K after its head norm and rotation), copied to host
+ * memory as [count][1024] bf16 each; either pointer may be NULL. */
+QWEN3_TTS_API int32_t q3t_session_read_kv(Qwen3TtsSessionHandle session, int32_t layer,
+                                          int32_t first_position, int32_t count, uint16_t* keys,
+                                          uint16_t* values, char* error, size_t error_capacity);
 
 #ifdef __cplusplus
 }

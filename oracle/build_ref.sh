@@ -1,13 +1,15 @@
 #!/usr/bin/env bash
 # TEST INFRASTRUCTURE ONLY.
 # Compiles the reference project's own CUDA code, from the sources where they lie
-# in a checkout of luka-loehr/qwen3-tts-native, for sm_100a.  Two outputs in
+# in a checkout of luka-loehr/qwen3-tts-native, for sm_100a.  Three outputs in
 # oracle/_ref/ (git-ignored):
 #   libq3t_ref.so               its three kernel files linked with ref_shim.cu: the
 #                               kernel launchers one by one, for operator parity;
 #   libqwen3_tts_cuda_ref.so    its whole talker library (eight .cu files + cuBLAS)
 #                               under its own C ABI: model, sessions and frames, for
-#                               parity of the frame composition and the prompt path.
+#                               parity of the frame composition and the prompt path;
+#   libqwen3_tts_cuda_ref_state.so  the same library with two more exports (ref_state_shim.cu)
+#                               through which a test seeds a session's state after the prompt.
 # No reference source is copied into this repository and its CMake build is
 # bypassed (that build pins sm_121 and CUDA 13).
 #
@@ -42,3 +44,12 @@ echo "built $OUT/libq3t_ref.so"
     -lcublas -Xlinker -rpath -Xlinker /usr/local/cuda/lib64 \
     -o "$OUT/libqwen3_tts_cuda_ref.so"
 echo "built $OUT/libqwen3_tts_cuda_ref.so"
+# the same library with talker.cu compiled through ref_state_shim.cu (two more exports that let
+# a test read and seed a session's state after the prompt)
+"$NVCC" -std=c++17 -O2 -gencode arch=compute_100a,code=sm_100a -shared -Xcompiler -fPIC \
+    -I"$SRC/include" -I"$SRC/src" \
+    "$SRC/src/gemv.cu" "$SRC/src/int8_gemv.cu" "$SRC/src/primitive_parity.cu" "$SRC/src/runtime.cu" \
+    "$SRC/src/sampling_kernels.cu" "$HERE/ref_state_shim.cu" "$SRC/src/talker_kernels.cu" "$SRC/src/weights.cu" \
+    -lcublas -Xlinker -rpath -Xlinker /usr/local/cuda/lib64 \
+    -o "$OUT/libqwen3_tts_cuda_ref_state.so"
+echo "built $OUT/libqwen3_tts_cuda_ref_state.so"

@@ -824,7 +824,7 @@ static int32_t attention_common(AttentionArgs& a, int max_sequence_length, void*
         const cudaError_t e = cudaMemsetAsync(scratch, 0, cb, stream);
         if (e != cudaSuccess) return static_cast<int32_t>(e);
     }
-    return static_cast<int32_t>(launch_decode_attention(a, stream));
+    return static_cast<int32_t>(launch_attention(a, stream));
 }
 
 int32_t q3t_launch_batch_causal_gqa_attention_fast(
@@ -938,6 +938,9 @@ int32_t q3t_model_set_option(Qwen3TtsModelHandle model, const char* key, int32_t
         } else if (std::strcmp(key, "gemv_mode") == 0) {
             if (value < 0 || value > 2) throw std::runtime_error("gemv_mode must be 0, 1 or 2");
             set_gemv_mode(value);       // process-wide: kernel for projections of 1..8 rows
+        } else if (std::strcmp(key, "attention_mode") == 0) {
+            if (value < 0 || value > 1) throw std::runtime_error("attention_mode must be 0 or 1");
+            set_attention_mode(value);  // process-wide: 0 sums in the reference's order (parity, slow)
         } else {
             throw std::runtime_error(std::string("unknown model option: ") + key);
         }
@@ -977,6 +980,7 @@ int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle session, int32_t pos
 }
 
 int32_t q3t_set_gemv_mode(int32_t mode) { return set_gemv_mode(mode); }
+int32_t q3t_set_attention_mode(int32_t mode) { return set_attention_mode(mode); }
 
 void q3t_test_fail_launch_after(int32_t launches) { fail_launch_after(launches); }
 void q3t_test_fail_allocation_after(int32_t allocations) { fail_allocation_after(allocations); }
@@ -1018,6 +1022,13 @@ int32_t q3t_session_read_state(Qwen3TtsSessionHandle session, uint16_t* last_hid
         session_of(session)->read_state(last_hidden, frame_tokens,
                                         reinterpret_cast<unsigned long long*>(random_state));
     }, QWEN3_TTS_TALKER_STATUS_STATE, error, error_capacity);
+}
+
+int32_t q3t_session_read_kv(Qwen3TtsSessionHandle session, int32_t layer, int32_t first_position,
+                            int32_t count, uint16_t* keys, uint16_t* values, char* error,
+                            size_t error_capacity) {
+    return protect([&] { session_of(session)->read_kv(layer, first_position, count, keys, values); },
+                   QWEN3_TTS_TALKER_STATUS_STATE, error, error_capacity);
 }
 
 }  // extern "C"

@@ -610,6 +610,138 @@ cudaError_t launch_hd(const AttentionArgs& a, cudaStream_t stream) {
     }
 }
 
+
+// ---- the reference's order of summation ---------------------------------------------------
+//
+// Parity mode.  One CTA of 256 threads per (row, query head) that forms every fp32 sum in the
+// order of the reference's batch_causal_gqa_attention_fast_kernel (talker_kernels.cu:506-595):
+// a position's score is one thread's fmaf chain over the head's dimensions in ascending order;
+// thread t exponentiates and adds up positions t, t + 256, ... and the 256 partial sums meet in a
+// halving tree; a dimension's output is one thread's fmaf chain over the positions in ascending
+// order, times the reciprocal of the sum.  The bf16 result is bit-identical to that kernel's, which
+// the split-KV kernel above (tensor-core products, chunked sums) cannot promise.  In fused mode the
+// query head gets its RMSNorm and rotation here, in the arithmetic of the kernel above; K and V of
+// the new token are appended by that kernel beforehand (append_mode 1).  Slow by design: each
+// thread walks whole rows of the cache.
+constexpr int kOrderedThreads = 256;
+constexpr int kOrderedMaxLength = 8192;     // scores of one head in shared memory
+
+template <int HD>
+__global__ void __launch_bounds__(kOrderedThreads) attention_reference_order_kernel(const AttentionArgs a) {
+    __shared__ float scores[kOrderedMaxLength];
+    __shared__ float reduction[kOrderedThreads];
+    __shared__ float qs[HD];
+    const int tid = threadIdx.x;
+    const int lane = tid % kWarp;
+    const int warp = tid / kWarp;
+    const int row = blockIdx.x / a.q_heads;
+    const int head = blockIdx.x % a.q_heads;
+    const int kvh = head / (a.q_heads / a.kv_heads);
+    const int kvw = a.kv_heads * HD;
+    const int q_stride = a.q_stride > 0 ? a.q_stride : a.q_heads * HD;
+
+    pdl_wait();
+    pdl_trigger();
+    const int pos = a.positions[row];
+    const int len = min(pos + 1, kOrderedMaxLength);     // the launcher's callers keep positions below the limit
+
+    auto kv_row = [&](int token, bool value) -> const bf16* {
+        if (a.kv.page_table != nullptr) {
+            const int pid = a.kv.page_table[(size_t)row * a.kv.table_stride + token / kPageTokens];
+            const bf16* slab = a.kv.slabs[pid >> a.kv.slab_shift];
+            const long long in_slab = (long long)(pid & ((1 << a.kv.slab_shift) - 1)) * a.kv.page_elems;
+            return slab + in_slab + (value ? a.kv.v_offset : a.kv.k_offset)
+                   + (size_t)(token % kPageTokens) * kvw + (size_t)kvh * HD;
+        }
+        const bf16* base = value ? a.kv.v_bases[row] : a.kv.k_bases[row];
+        return base + (size_t)token * kvw + (size_t)kvh * HD;
+    };
+
+    // ---- the query head -------------------------------------------------------------------
+    const bf16* qsrc = a.q + (size_t)row * q_stride + (size_t)head * HD;
+    if (a.fused) {
+        if (warp == 0) {
+            constexpr int DPL = HD / 32;       // dims per lane: l, l + 32, ...
+            float x[DPL];
+            float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) {
+                x[j] = bf2f(qsrc[lane + 32 * j]);
+                sq[j] = fmaf(x[j], x[j], 0.0f);
+            }
+            float c = (sq[0] + sq[2]) + (sq[1] + sq[3]);      // the 256-slot halving tree, empty slots zero
+            c = warp_sum_down(c);
+            c = __shfl_sync(0xffffffffu, c, 0);
+            const float inv = rsqrtf(c / static_cast<float>(HD) + a.eps);
+            float y[DPL];
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) y[j] = rbf(rbf(x[j] * inv) * bf2f(a.q_norm_w[lane + 32 * j]));
+#pragma unroll
+            for (int j = 0; j < DPL / 2; ++j) {
+                const int d = lane + 32 * j;
+                float o1, o2;
+                if (a.rope_table != nullptr && pos < a.rope_positions) {
+                    const uint32_t cs = a.rope_table[(size_t)pos * (HD / 2) + d];
+                    rope_pair_cs(y[j], y[j + DPL / 2], bf_lo(cs), bf_hi(cs), o1, o2);
+                } else {
+                    rope_pair(y[j], y[j + DPL / 2], static_cast<float>(pos) * rope_inv_freq(d, HD, a.theta), o1, o2);
+                }
+                qs[d] = o1;
+                qs[d + HD / 2] = o2;
+            }
+        }
+    } else {
+        for (int d = tid; d < HD; d += kOrderedThreads) qs[d] = bf2f(qsrc[d]);
+    }
+    __syncthreads();
+
+    // ---- scores: one thread per position ----------------------------------------------------
+    // The reference takes the head dimension as a kernel argument, so its scale is the hardware's
+    // reciprocal square root evaluated at run time; a compile-time constant here would be folded to
+    // the correctly rounded value, which can differ from it in the last bit.
+    const float scale = rsqrtf(static_cast<float>(a.head_dim));
+    float local_maximum = -__int_as_float(0x7f800000);
+    for (int p = tid; p < len; p += kOrderedThreads) {
+        const bf16* key = kv_row(p, false);
+        float dot = 0.0f;
+        for (int d = 0; d < HD; ++d) dot = fmaf(qs[d], bf2f(key[d]), dot);
+        const float scored = dot * scale;
+        scores[p] = scored;
+        local_maximum = fmaxf(local_maximum, scored);
+    }
+    reduction[tid] = local_maximum;
+    __syncthreads();
+    for (int stride = kOrderedThreads / 2; stride > 0; stride /= 2) {
+        if (tid < stride) reduction[tid] = fmaxf(reduction[tid], reduction[tid + stride]);
+        __syncthreads();
+    }
+    const float maximum = reduction[0];
+    __syncthreads();
+
+    float local_sum = 0.0f;
+    for (int p = tid; p < len; p += kOrderedThreads) {
+        const float weight = expf(scores[p] - maximum);
+        scores[p] = weight;
+        local_sum += weight;
+    }
+    reduction[tid] = local_sum;
+    __syncthreads();
+    for (int stride = kOrderedThreads / 2; stride > 0; stride /= 2) {
+        if (tid < stride) reduction[tid] += reduction[tid + stride];
+        __syncthreads();
+    }
+    const float inverse = 1.0f / reduction[0];
+
+    // ---- values: one thread per dimension ---------------------------------------------------
+    for (int d = tid; d < HD; d += kOrderedThreads) {
+        float accumulated = 0.0f;
+        for (int p = 0; p < len; ++p) accumulated = fmaf(scores[p], bf2f(kv_row(p, true)[d]), accumulated);
+        const size_t o = ((size_t)row * a.q_heads + head) * HD + d;
+        const float value = accumulated * inverse;
+        if (a.out32 != nullptr) a.out32[o] = value;
+        a.out[o] = f2bf(value);
+    }
+}
 }  // namespace
 
 namespace {
@@ -669,6 +801,46 @@ cudaError_t launch_decode_attention(const AttentionArgs& a, cudaStream_t stream)
         case 32: return launch_hd<32>(b, stream);
         case 64: return launch_hd<64>(b, stream);
         case 128: return launch_hd<128>(b, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+namespace {
+int g_attention_mode = 1;
+}
+// 1 (default): the split-KV kernel.  0: sums in the reference's order (parity mode).
+int set_attention_mode(int mode) {
+    const int before = g_attention_mode;
+    g_attention_mode = mode == 0 ? 0 : 1;
+    return before;
+}
+int attention_mode() { return g_attention_mode; }
+
+// What the engine and the operator entry point call: append and attend in the mode in force.
+cudaError_t launch_attention(const AttentionArgs& a, cudaStream_t stream) {
+    if (g_attention_mode != 0) return launch_decode_attention(a, stream);
+    if (a.fused && a.append_mode != 2) {
+        AttentionArgs append = a;
+        append.append_mode = 1;
+        append.inputs_settled = 0;
+        const cudaError_t e = launch_decode_attention(append, stream);
+        if (e != cudaSuccess || a.append_mode == 1) return e;
+    }
+    return launch_attention_reference_order(a, stream);
+}
+
+cudaError_t launch_attention_reference_order(const AttentionArgs& a, cudaStream_t stream) {
+    if (a.rows < 1 || a.q_heads < 1 || a.kv_heads < 1 || a.q_heads % a.kv_heads != 0 || a.q == nullptr
+        || a.out == nullptr || a.positions == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    if (a.kv.page_table == nullptr && (a.kv.k_bases == nullptr || a.kv.v_bases == nullptr)) return cudaErrorInvalidValue;
+    if (a.kv.page_table != nullptr && a.kv.slabs == nullptr) return cudaErrorInvalidValue;
+    if (a.fused && a.q_norm_w == nullptr) return cudaErrorInvalidValue;
+    const dim3 grid(static_cast<unsigned int>(a.rows * a.q_heads));
+    switch (a.head_dim) {
+        case 64: return launch_pdl(attention_reference_order_kernel<64>, grid, dim3(kOrderedThreads), 0, stream, a);
+        case 128: return launch_pdl(attention_reference_order_kernel<128>, grid, dim3(kOrderedThreads), 0, stream, a);
         default: return cudaErrorInvalidValue;
     }
 }

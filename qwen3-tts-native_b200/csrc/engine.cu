@@ -135,6 +135,15 @@ KvLayout KvPool::layout(int layer, const int* page_table, int table_stride) cons
     return l;
 }
 
+const bf16* KvPool::page_rows(int page, int layer, bool value) const {
+    const int slab = page >> slab_shift_;
+    if (page < 0 || slab >= static_cast<int>(slabs_.size()) || layer < 0 || layer >= layers_) {
+        throw std::runtime_error("KV page or layer out of range");
+    }
+    return slabs_[slab].as<bf16>() + (long long)(page & ((1 << slab_shift_) - 1)) * page_elems_
+           + (long long)(layer * 2 + (value ? 1 : 0)) * plane_elems_;
+}
+
 uint64_t KvPool::page_bytes() const { return (uint64_t)layers_ * 2 * page_elems_ * sizeof(bf16); }
 
 // ------------------------------------------------------------------ Workspace
@@ -555,10 +564,10 @@ void enqueue_layers(Workspace& w, const ModelDims& d, const std::vector<LayerWei
             // the rows are consecutive positions of one session: every row's K/V goes into the
             // cache first, then every row attends up to its own position
             a.append_mode = 1;
-            check_launch(launch_decode_attention(a, s), "prompt KV append");
+            check_launch(launch_attention(a, s), "prompt KV append");
             a.append_mode = 2;
         }
-        check_launch(launch_decode_attention(a, s), "decode attention");
+        check_launch(launch_attention(a, s), "decode attention");
         observe("attention", w.attention.as<bf16>(), d.q_width, d.q_width);
 
         GemvArgs o;
@@ -1474,6 +1483,29 @@ void Session::read_state(uint16_t* last_hidden, int* frame_tokens, unsigned long
     if (rng != nullptr) {
         check_cuda(cudaMemcpy(rng, d_rng_, sizeof(unsigned long long), cudaMemcpyDeviceToHost),
                    "cudaMemcpy(rng)");
+    }
+}
+
+void Session::read_kv(int layer, int first, int count, uint16_t* keys, uint16_t* values) const {
+    check_cuda(cudaSetDevice(device_), "cudaSetDevice(read kv)");
+    if (first < 0 || count < 0 || first + count > position_) {
+        throw std::runtime_error("KV positions outside what the session has written");
+    }
+    check_cuda(cudaStreamSynchronize(stream_), "cudaStreamSynchronize(read kv)");
+    const KvPool& pool = *model_->talker_pool;
+    const int width = model_->talker.kv_width;
+    for (int token = first; token < first + count;) {
+        const int in_page = token % kPageTokens;
+        const int run = std::min(kPageTokens - in_page, first + count - token);
+        const int page = talker_pages_.at(token / kPageTokens);
+        for (int plane = 0; plane < 2; ++plane) {
+            uint16_t* out = plane == 0 ? keys : values;
+            if (out == nullptr) continue;
+            check_cuda(cudaMemcpy(out + (size_t)(token - first) * width,
+                                  pool.page_rows(page, layer, plane == 1) + (size_t)in_page * width,
+                                  (size_t)run * width * sizeof(bf16), cudaMemcpyDeviceToHost), "cudaMemcpy(read kv)");
+        }
+        token += run;
     }
 }
 

@@ -98,6 +98,8 @@ public:
     int layers() const { return layers_; }
     long long page_elems() const { return page_elems_; }
     long long plane_elems() const { return plane_elems_; }
+    // device address of token 0 of `page` in the K (value = false) or V plane of `layer`
+    const bf16* page_rows(int page, int layer, bool value) const;
     static constexpr int kMaxSlabs = 512;
 private:
     void add_slab();
@@ -296,6 +298,9 @@ public:
 
     // parity-test hook: copies of the device-side state (any pointer may be null)
     void read_state(uint16_t* last_hidden, int* frame_tokens, unsigned long long* rng) const;
+    // parity-test hook: the talker's K and V rows of positions [first, first + count) of one layer,
+    // as stored (K after its head norm and rotation), copied to host memory, [count][kv width] each
+    void read_kv(int layer, int first, int count, uint16_t* keys, uint16_t* values) const;
     // Benchmark harness: puts the session in the PREFILLED phase at `position` without running a
     // prompt: KV rows [0, position) and last_hidden are filled with seeded pseudo-random
     // N(0,1) values, the semantic history gets one token.

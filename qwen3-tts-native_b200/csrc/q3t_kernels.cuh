@@ -168,6 +168,17 @@ struct AttentionArgs {
 constexpr int kAttnChunk = 64;          // tokens per split
 size_t attention_scratch_floats(int rows, int q_heads, int head_dim, int max_splits);
 cudaError_t launch_decode_attention(const AttentionArgs& args, cudaStream_t stream);
+// Parity mode: the same attention with every fp32 sum formed in the order of the reference's
+// kernel (bit-identical bf16 output; slow).  Fused mode normalises and rotates the query heads;
+// the new token's K/V must already be in the cache (launch_decode_attention with append_mode 1).
+// Positions must be below 8192.
+cudaError_t launch_attention_reference_order(const AttentionArgs& args, cudaStream_t stream);
+// Process-wide choice between the two (1, default: split-KV kernel; 0: reference order) and the
+// launcher that honours it: in mode 0 a fused call appends with the split-KV kernel's prologue,
+// then attends in the reference's order.
+int set_attention_mode(int mode);
+int attention_mode();
+cudaError_t launch_attention(const AttentionArgs& args, cudaStream_t stream);
 // cos/sin of every (position, rotary pair), rounded to bf16 as the fused prologue rounds them;
 // computed by the same device expressions, so using the table changes no bit
 cudaError_t launch_build_rope_table(uint32_t* table, int positions, int head_dim, float theta,

@@ -111,7 +111,7 @@ EXPORTED_SYMBOLS = (
     "q3t_launch_int8_gemm_rows", "q3t_launch_int8_gemm_rows_add",
     "q3t_launch_int8_gate_up_silu_rows", "q3t_launch_int8_gemm_ex",
     "q3t_launch_quantize_weight_rows", "q3t_benchmark_int8_gemv", "q3t_launch_rms_norm_rows",
-    "q3t_set_gemv_mode", "q3t_test_fail_launch_after", "q3t_test_fail_allocation_after",
+    "q3t_set_gemv_mode", "q3t_set_attention_mode", "q3t_test_fail_launch_after", "q3t_test_fail_allocation_after",
     "q3t_test_report_device_wait_failure", "q3t_host_pump_frames",
     "q3t_pump_create", "q3t_pump_destroy", "q3t_pump_register", "q3t_pump_unregister",
     "q3t_pump_begin_frame", "q3t_pump_statistics", "q3t_pick_device",
@@ -120,7 +120,7 @@ EXPORTED_SYMBOLS = (
     "q3t_launch_gather_embedding_rows", "q3t_launch_add_embedding_rows",
     "q3t_attention_scratch_bytes", "q3t_launch_batch_causal_gqa_attention_fast",
     "q3t_launch_decode_attention_ex", "q3t_launch_sample_logits", "q3t_launch_sample_logits_at",
-    "q3t_model_set_option", "q3t_model_run_frames", "q3t_session_read_state",
+    "q3t_model_set_option", "q3t_model_run_frames", "q3t_session_read_state", "q3t_session_read_kv",
     "q3t_session_synthetic_prefill", "q3t_model_kernel_launches", "q3t_session_current_token",
     "q3t_launch_batch_causal_gqa_attention_fast_noalloc", "q3t_attention_static_scratch_capacity",
     "q3t_kernel_error_count", "q3t_model_tensor_image", "q3t_model_adopt_tensor",
@@ -192,6 +192,8 @@ def library() -> C.CDLL:
                 ("q3t_model_set_option", [C.c_void_p, C.c_char_p, C.c_int32, C.c_char_p, C.c_size_t]),
                 ("q3t_session_read_state", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p,
                                             C.c_size_t]),
+                ("q3t_session_read_kv", [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                         C.c_char_p, C.c_size_t]),
                 ("q3t_session_synthetic_prefill", [C.c_void_p, C.c_int32, C.c_uint64, C.c_char_p, C.c_size_t]),
                 ("q3t_model_kernel_launches", [C.c_void_p, C.POINTER(C.c_uint64), C.c_char_p, C.c_size_t])):
             if hasattr(lib, name):
@@ -573,6 +575,17 @@ class NativeTalkerSession:
                                                 rng.ctypes.data_as(C.c_void_p), err, _ERR_CAP), err)
         return hidden, tokens, int(rng[0])
 
+    def read_kv(self, layer: int, first: int, count: int):
+        """(keys, values) of talker positions [first, first + count) of one layer, bf16 bits
+        [count][1024] each, as the cache holds them -- test hook."""
+        keys = np.zeros((count, 1024), dtype=np.uint16)
+        values = np.zeros((count, 1024), dtype=np.uint16)
+        err = C.create_string_buffer(_ERR_CAP)
+        _check(library().q3t_session_read_kv(self._handle, layer, first, count,
+                                             keys.ctypes.data_as(C.c_void_p),
+                                             values.ctypes.data_as(C.c_void_p), err, _ERR_CAP), err)
+        return keys, values
+
     def close(self) -> None:
         if self._handle:
             library().qwen3_tts_session_destroy(self._handle)
@@ -602,8 +615,14 @@ def probe_device(device_index: int = 0) -> DeviceInfoC:
 
 def set_gemv_mode(mode: int) -> int:
     """Kernel for projections of 1..8 rows: 0 SIMT (bit-identical to the reference's summation order),
-    1 mma.sync where the shape allows (default), 2 bulk-copy SIMT.  Returns the previous mode."""
+    1 int8 tensor-core kernel where the shape allows (default), 2 bulk-copy SIMT.  Returns the previous mode."""
     return int(library().q3t_set_gemv_mode(int(mode)))
+
+
+def set_attention_mode(mode: int) -> int:
+    """Decode attention kernel: 1 split-KV on tensor cores (default), 0 sums in the reference's order
+    (parity mode, bit-identical to the reference's kernel, slow).  Returns the previous mode."""
+    return int(library().q3t_set_attention_mode(int(mode)))
 
 
 def benchmark_int8_gemv(device_index: int, in_features: int, out_features: int, rows: int = 1,

@@ -184,3 +184,50 @@ def test_vs_reference_fast_kernel(orc, ops, ref, length):
     d = orc.bf16_ulp_distance(out["out"], exact)
     print(f"L={length}: max ulp distance to the exact kernel {int(d.max())}, "
           f"{100 * float((d > 0).mean()):.1f}% of elements differ")
+
+
+# ---- parity mode: sums in the reference's order ----------------------------------------------
+
+@pytest.fixture
+def reference_order(q3t):
+    before = q3t.native.set_attention_mode(0)
+    yield
+    q3t.native.set_attention_mode(before)
+
+
+@pytest.mark.parametrize("length", [1, 2, 7, 64, 257, 513, 1100])
+def test_reference_order_is_bit_identical(orc, ops, ref, reference_order, length):
+    """Attention mode 0 against the reference's fast kernel run on the same GPU: equal bits."""
+    rows, qh, kvh, hd = 3, 16, 8, 128
+    q, k, v, pos = make(orc, 21, rows, qh, kvh, hd, length, [length - 1, length // 3, 0])
+    got = ops.attention_ex(q, pos, qh, kvh, hd, k=k, v=v)["out"]
+    want = ref.ref_attention(q, k, v, pos, qh, kvh, hd, fast=True)
+    assert np.array_equal(got.reshape(-1), want.reshape(-1))
+    slabs, table = paged_copy(k, v, kvh * hd, np.random.default_rng(6), per_slab=32)
+    paged = ops.attention_ex(q, pos, qh, kvh, hd, pages=slabs, page_table=table, slab_shift=5)["out"]
+    assert np.array_equal(paged.reshape(-1), want.reshape(-1))
+
+
+def test_reference_order_fused(orc, ops, ref, reference_order):
+    """Fused call in mode 0 == the stand-alone operators one after the other, then the reference's
+    fast kernel over the caches they produced."""
+    rows, qh, kvh, hd, cap = 4, 16, 8, 128, 150
+    rng = np.random.default_rng(22)
+    qw, kvw = qh * hd, kvh * hd
+    q, k, v, pos = make(orc, 23, rows, qh, kvh, hd, cap, [149, 0, 64, 17])
+    stride = qw + 2 * kvw
+    qkv = bf(orc, rng.standard_normal((rows, stride)) * 1.5)
+    qn = bf(orc, 1.0 + 0.05 * rng.standard_normal(hd))
+    kn = bf(orc, 1.0 + 0.05 * rng.standard_normal(hd))
+    fused = ops.attention_ex(qkv, pos, qh, kvh, hd, k=k, v=v, q_norm_w=qn, k_norm_w=kn, fused=True,
+                             q_stride=stride, new_stride=stride)
+    q2 = np.ascontiguousarray(qkv[:, :qw])
+    k2 = np.ascontiguousarray(qkv[:, qw:qw + kvw])
+    v2 = np.ascontiguousarray(qkv[:, qw + kvw:])
+    q2 = ops.rope_rows_at(ops.head_rms_norm_rows(q2, qn, rows, qh, hd), rows, qh, hd, pos).reshape(rows, qw)
+    k2 = ops.rope_rows_at(ops.head_rms_norm_rows(k2, kn, rows, kvh, hd), rows, kvh, hd, pos).reshape(rows, kvw)
+    kc = ops.kv_scatter_rows(k2, k, pos)
+    vc = ops.kv_scatter_rows(v2, v, pos)
+    assert np.array_equal(fused["k"], kc) and np.array_equal(fused["v"], vc)
+    want = ref.ref_attention(q2, kc, vc, pos, qh, kvh, hd, fast=True)
+    assert np.array_equal(fused["out"].reshape(-1), want.reshape(-1))

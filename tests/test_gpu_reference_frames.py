@@ -17,6 +17,13 @@ KV cache each library decodes from is therefore its own prompt's, and exact code
 frames is not implied.  The test asserts what the arithmetic guarantees (identical structure and
 counters, stage tensors within a bf16 rounding step, hidden-state statistics and logits that
 track) and records, in the file named by Q3T_PARITY_REPORT, how far the code sequences agree.
+
+The frames themselves are pinned exactly another way: oracle/_ref/libqwen3_tts_cuda_ref_state.so is
+the same reference library plus two accessors (oracle/ref_state_shim.cu) through which the worker
+overwrites each reference session's state after its prompt (K/V rows, last hidden row, first token,
+random state) with the state this library exported.  From equal state, and with this library in its
+parity modes (SIMT projections, attention sums in the reference's order), every code and every next
+token of every frame must be equal: test_frames_from_the_same_state.
 """
 import json
 import os
@@ -30,24 +37,27 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF_LIBRARY = os.path.join(ROOT, "oracle", "_ref", "libqwen3_tts_cuda_ref.so")
+REF_STATE_LIBRARY = os.path.join(ROOT, "oracle", "_ref", "libqwen3_tts_cuda_ref_state.so")
 WORKER = os.path.join(ROOT, "tests", "reference_frames_worker.py")
 
 
-def run_worker(tmp, name, library, extra_env):
+def run_worker(tmp, name, library, extra_env, extra_args=(), trace=True):
     out = os.path.join(tmp, name + ".json")
     stages = os.path.join(tmp, name + "_stages")
     env = dict(os.environ)
     env.update(extra_env)
-    env["QWEN3_TTS_PARITY_TRACE"] = "1"
+    if trace:
+        env["QWEN3_TTS_PARITY_TRACE"] = "1"
     if library is not None:
         env["QWEN3_TTS_TALKER_LIBRARY"] = library
     else:
         env.pop("QWEN3_TTS_TALKER_LIBRARY", None)
-    proc = subprocess.run([sys.executable, WORKER, out, stages], env=env, capture_output=True, text=True,
-                          timeout=900)
+    proc = subprocess.run([sys.executable, WORKER, out, stages, *extra_args], env=env, capture_output=True,
+                          text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
     with open(out) as f:
         report = json.load(f)
+    report["json_path"] = out
     # trace lines of the first prompt: everything up to and including the first "logits" line
     trace = []
     for line in proc.stderr.splitlines():
@@ -73,12 +83,27 @@ def both(tmp_path_factory):
         pytest.skip("oracle/_ref/libqwen3_tts_cuda_ref.so not built (needs a reference checkout)")
     tmp = str(tmp_path_factory.mktemp("reference_frames"))
     ref = run_worker(tmp, "reference", REF_LIBRARY, {"QWEN3_TTS_INT8_DECODE": "1", "QWEN3_TTS_STAGE_DUMP": "1"})
-    # mode 0: the projection kernel that keeps the reference's summation order, so that what differs
-    # is the composition and the prompt path, not the order of a dot product
+    # parity modes: the projection and attention kernels that keep the reference's summation order,
+    # so that what differs is the composition and the prompt path, not the order of a sum
     os.makedirs(os.path.join(tmp, "ours_dump"), exist_ok=True)
+    os.makedirs(os.path.join(tmp, "state"), exist_ok=True)
     ours = run_worker(tmp, "ours", None, {"QWEN3_TTS_STAGE_DUMP": os.path.join(tmp, "ours_dump/"),
-                                          "Q3T_WORKER_GEMV_MODE": "0", "Q3T_WORKER_TC_MIN_ROWS": "65"})
+                                          "Q3T_WORKER_GEMV_MODE": "0", "Q3T_WORKER_TC_MIN_ROWS": "65",
+                                          "Q3T_WORKER_ATTENTION_MODE": "0"},
+                      ("--export-state", os.path.join(tmp, "state")))
     return ref, ours
+
+
+@pytest.fixture(scope="module")
+def seeded(both, tmp_path_factory):
+    """The reference's library started from this library's state after every prompt."""
+    if not os.path.exists(REF_STATE_LIBRARY):
+        pytest.skip("oracle/_ref/libqwen3_tts_cuda_ref_state.so not built (needs a reference checkout)")
+    tmp = str(tmp_path_factory.mktemp("reference_seeded"))
+    state_dir = os.path.join(os.path.dirname(both[1][0]["json_path"]), "state")
+    ref = run_worker(tmp, "reference_seeded", REF_STATE_LIBRARY, {"QWEN3_TTS_INT8_DECODE": "1"},
+                     ("--import-state", state_dir), trace=False)
+    return ref[0], both[1][0]
 
 
 def f32(bits):
@@ -198,9 +223,42 @@ def test_frame_sequences_against_the_reference(both):
         if not run["sampled"]:
             for i in range(1, run["sessions"]):
                 assert run["frames"][i] == run["frames"][0] and run["next_tokens"][i] == run["next_tokens"][0]
-    # the short prompt leaves the least room for the prompt paths to differ: greedy decoding from it
-    # starts with the same semantic token and the same first frame in both libraries
-    short_greedy = [r for r in rows if r["prompt"] == "short" and not r["sampled"]]
-    for r in short_greedy:
-        assert r["same_first_token"] == r["sessions"], r
-        assert r["first_frame_code_agreement"] >= 0.75, r
+    # Across the two libraries nothing more is asserted here: each decodes from its own prompt's
+    # cache, and with random weights the gap between the two largest logits is often smaller than
+    # the rounding differences of the prompt paths, so first tokens and codes flip.  The frame
+    # composition itself is pinned bit for bit by test_frames_from_the_same_state below.
+
+def test_frames_from_the_same_state(seeded):
+    """Frame composition proper.  The reference's sessions are handed this library's state after the
+    prompt (K/V rows, last hidden row, first token, random state: oracle/ref_state_shim.cu), so the
+    prompt paths no longer matter; from there both libraries run lockstep batches of 2 and 8 sessions
+    through the same ABI calls, greedy and sampled.  In the parity modes (gemv mode 0, attention mode
+    0, no tensor-core GEMM) every operator of the frame is bit-identical to the reference's kernel, so
+    every code and every next token of every session must be equal."""
+    ref, ours = seeded
+    rows = []
+    total = identical = first_frames = first_equal = 0
+    for a, b in zip(ref["runs"], ours["runs"]):
+        assert a["first_tokens"] == b["first_tokens"]
+        n = a["sessions"]
+        diverged_at = []
+        for i in range(n):
+            fa, fb = a["frames"][i], b["frames"][i]
+            ta, tb = a["next_tokens"][i], b["next_tokens"][i]
+            frames = min(len(fa), len(fb))
+            at = next((f for f in range(frames) if fa[f] != fb[f] or ta[f] != tb[f]), None)
+            diverged_at.append(at)
+            total += 1
+            identical += int(at is None and len(fa) == len(fb))
+            if frames:
+                first_frames += 1
+                first_equal += int(fa[0] == fb[0] and ta[0] == tb[0])
+        rows.append({"prompt": a["prompt"], "sessions": n, "sampled": a["sampled"],
+                     "frames": [len(f) for f in b["frames"]], "first_divergent_frame": diverged_at,
+                     "session0_reference": [a["frames"][0][:2], a["next_tokens"][0][:2]],
+                     "session0_ours": [b["frames"][0][:2], b["next_tokens"][0][:2]]})
+    record(test="reference_frames_from_same_state", runs=rows, sessions=total, identical_sequences=identical,
+           first_frames=first_frames, first_frames_identical=first_equal)
+    assert first_frames > 0
+    assert first_equal == first_frames, rows
+    assert identical == total, rows
