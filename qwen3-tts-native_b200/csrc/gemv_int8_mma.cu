@@ -267,7 +267,40 @@ __global__ void __launch_bounds__(kThreads, NTMAX == 1 ? 2 : 1) gemv_mma_kernel(
         }
     }
 
-    // ---- activations: fetched by all lanes, converted, parked in shared memory as fp16 ------------
+    // ---- activations: fetched by all lanes, converted, parked in shared memory as byte limbs -------
+    // A lane's share of up to RB rows: 2 Q consecutive elements of each, in this warp's part of K.
+    const size_t my_offset = (size_t)warp * KW + 2 * Q * lane;      // elements
+    uint32_t raw[RB][Q];
+    auto load_rows = [&](int r0) {
+#pragma unroll
+        for (int b = 0; b < RB; ++b) {
+            if (r0 + b < R) {
+                const bf16* src = p.x + (size_t)(r0 + b) * K + my_offset;
+                if constexpr (Q % 4 == 0) {
+#pragma unroll
+                    for (int m = 0; m < Q / 4; ++m) {
+                        const int4 v = reinterpret_cast<const int4*>(src)[m];
+                        raw[b][4 * m + 0] = v.x; raw[b][4 * m + 1] = v.y;
+                        raw[b][4 * m + 2] = v.z; raw[b][4 * m + 3] = v.w;
+                    }
+                } else if constexpr (Q % 2 == 0) {
+#pragma unroll
+                    for (int m = 0; m < Q / 2; ++m) {
+                        const int2 v = reinterpret_cast<const int2*>(src)[m];
+                        raw[b][2 * m + 0] = v.x; raw[b][2 * m + 1] = v.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int m = 0; m < Q; ++m) raw[b][m] = reinterpret_cast<const uint32_t*>(src)[m];
+                }
+            }
+        }
+    };
+    // With a norm prologue all rows fit one batch (RB = 8): request them now, so that they travel
+    // together with the strided reads of the sum of squares instead of after its barrier.
+    static_assert(!NORM || RB >= 8, "the norm prologue expects every row in the first batch");
+    if (NORM) load_rows(0);
+
     float inv_mine = 0.0f;           // NORM: lane r keeps 1/rms of row r
     if (NORM) {
         // sum of squares in the order of the stand-alone RMSNorm (thread i takes elements i, i + 256,
@@ -312,33 +345,9 @@ __global__ void __launch_bounds__(kThreads, NTMAX == 1 ? 2 : 1) gemv_mma_kernel(
 
     float unscale_mine = 1.0f;       // lane r keeps 2^-e of row r in this warp's part
     {
-        const size_t my_offset = (size_t)warp * KW + 2 * Q * lane;      // elements
 #pragma unroll 1
         for (int r0 = 0; r0 < R; r0 += RB) {
-            uint32_t raw[RB][Q];
-#pragma unroll
-            for (int b = 0; b < RB; ++b) {
-                if (r0 + b < R) {
-                    const bf16* src = p.x + (size_t)(r0 + b) * K + my_offset;
-                    if constexpr (Q % 4 == 0) {
-#pragma unroll
-                        for (int m = 0; m < Q / 4; ++m) {
-                            const int4 v = reinterpret_cast<const int4*>(src)[m];
-                            raw[b][4 * m + 0] = v.x; raw[b][4 * m + 1] = v.y;
-                            raw[b][4 * m + 2] = v.z; raw[b][4 * m + 3] = v.w;
-                        }
-                    } else if constexpr (Q % 2 == 0) {
-#pragma unroll
-                        for (int m = 0; m < Q / 2; ++m) {
-                            const int2 v = reinterpret_cast<const int2*>(src)[m];
-                            raw[b][2 * m + 0] = v.x; raw[b][2 * m + 1] = v.y;
-                        }
-                    } else {
-#pragma unroll
-                        for (int m = 0; m < Q; ++m) raw[b][m] = reinterpret_cast<const uint32_t*>(src)[m];
-                    }
-                }
-            }
+            if (!NORM || r0 > 0) load_rows(r0);
             if (r0 == 0) await_group(min(Gf, T));      // the activations are in flight meanwhile
 #pragma unroll
             for (int b = 0; b < RB; ++b) {
