@@ -16,10 +16,16 @@ top-p 0.9.  Prints ONE JSON line:
              round trip per frame: frame table up, next tokens and codes down
   b1         the B=1 numbers (one session at KV length 512, the single-session configurations of the benchmark spec)
   roofline   the batch-1 int8 GEMV (configs[0], 2048 -> 6144) against the measured HBM peak
-  cpu_baseline  the oracle's CPU restatement timed on this host's cores on a bounded sample
+  cpu_baseline  the oracle's CPU restatement timed on this host's cores: whole B=1 frames, median
+  existing_kernels  the reference project's own CUDA code on this GPU (oracle/_ref, test
+             infrastructure, outside every timed region): its int8 GEMV kernel on configs[0] and its
+             whole library's B=1 / B=8 frames through its ABI, with this library's times for the same
+             calls beside them
 
---impl reference times that CPU restatement as its own arm (the reference has no CPU
-implementation of this path and its host is Rust, which this image cannot build).
+--impl reference times the CPU restatement as its own arm (the reference has no CPU implementation
+of this path and its host is Rust, which this image cannot build): whole B=1 frames, one per step.
+--leg b64 | b1 | gemv | attn | existing run one part alone (profiling wants few launches and a
+small footprint; `existing` drives whichever library QWEN3_TTS_TALKER_LIBRARY names).
 """
 from __future__ import annotations
 
@@ -40,6 +46,7 @@ if ROOT not in sys.path:
 
 SESSIONS = 64
 GEMV_BYTES = 6144 * 2048 + 6144 * 4 + 2048 * 2 + 6144 * 2          # W + scales + x + y
+GEMV_TRAFFIC_NCU = None                                               # bytes per launch, see roofline.traffic_source
 TALKER_WEIGHT_BYTES = 1_423_966_208 + 2_322_432                      # int8 rows + fp32 scales
 PREDICTOR_FRAME_BYTES = 1_323_302_912
 KV_BYTES_PER_TOKEN = 28 * 2 * 1024 * 2                               # all layers, K and V
@@ -134,90 +141,110 @@ class ClockSampler:
 
 # ------------------------------------------------------------------ CPU restatement, timed
 
-def cpu_frame_seconds(repeats: int = 1):
-    """Times the oracle (oracle/q3t_oracle.c, OpenMP over output rows) on a bounded sample of one
-    B=1 frame -- one talker layer at KV length 513, one predictor layer, the heads and the
-    sampler, with the real shapes -- and scales it to a whole frame (28 talker layers, 16 x 5
-    predictor layers, 16 small projections and heads).  Returns (seconds per frame, threads,
-    description)."""
-    from oracle import oracle as o
-    o.build()
-    # all the host threads this process may use, whatever OMP_NUM_THREADS says (torchrun sets it
-    # to 1 for its workers; only rank 0 runs the CPU arm)
-    try:
-        o.set_threads(len(os.sched_getaffinity(0)))
-    except (AttributeError, OSError):
-        o.set_threads(os.cpu_count() or 1)
-    rng = np.random.default_rng(0)
+CPU_WORKLOAD = ("B=1 frames, one after the other, on the host cores: 28 talker layers at KV length 513, "
+                "16 x 5 code-predictor layers, 16 input projections, 15 predictor heads + the codec head, "
+                "2 text projections, 16 samplers (T=0.9 top-k 50 top-p 0.9), every operator executed at its "
+                "real shape; a CPU runs sessions one at a time, so its frames/s is the single-session rate")
 
-    def layer(hidden, inter, qw, kvw):
-        def q(n, k):
-            return (rng.integers(-127, 128, size=(n, k), dtype=np.int8),
-                    (rng.uniform(0.5, 1.5, size=n) / (73.6 * np.sqrt(k))).astype(np.float32))
-        ones = o.to_bf16(np.ones(hidden, dtype=np.float32))
-        hd = o.to_bf16(np.ones(128, dtype=np.float32))
-        return dict(input_norm=ones, qkv=q(qw + 2 * kvw, hidden), o=q(hidden, qw), q_norm=hd,
-                    k_norm=hd, post_norm=ones, gate_up=q(2 * inter, hidden), down=q(hidden, inter))
 
-    talker = layer(2048, 6144, 2048, 1024)
-    predictor = layer(1024, 3072, 2048, 1024)
-    kc = o.to_bf16(rng.standard_normal((513, 1024)).astype(np.float32))
-    vc = o.to_bf16(rng.standard_normal((513, 1024)).astype(np.float32))
-    pk = np.zeros((16, 1024), dtype=np.uint16)
-    pv = np.zeros((16, 1024), dtype=np.uint16)
-    h = o.to_bf16(rng.standard_normal(2048).astype(np.float32))
-    ph = o.to_bf16(rng.standard_normal(1024).astype(np.float32))
-    head_w = rng.integers(-127, 128, size=(3072, 2048), dtype=np.int8)
-    head_s = np.full(3072, 1.0 / 3000.0, dtype=np.float32)
-    phead_w = rng.integers(-127, 128, size=(2048, 1024), dtype=np.int8)
-    mtp_w = rng.integers(-127, 128, size=(1024, 2048), dtype=np.int8)
-    pdims = o.predictor_dims(128)
+class CpuFrames:
+    """The oracle (oracle/q3t_oracle.c, OpenMP over output rows) set up to run whole B=1 frames."""
 
-    def timed(fn):
-        best = None
-        for _ in range(max(1, repeats)):
-            t0 = time.perf_counter()
-            fn()
-            dt = time.perf_counter() - t0
-            best = dt if best is None else min(best, dt)
-        return best
+    def __init__(self):
+        from oracle import oracle as o
+        o.build()
+        # all the host threads this process may use, whatever OMP_NUM_THREADS says (torchrun sets it
+        # to 1 for its workers; only rank 0 runs the CPU arm)
+        try:
+            o.set_threads(len(os.sched_getaffinity(0)))
+        except (AttributeError, OSError):
+            o.set_threads(os.cpu_count() or 1)
+        self.o = o
+        rng = np.random.default_rng(0)
 
-    t_talker = timed(lambda: o.decoder_layer(h, talker, o.TALKER_DIMS, kc, vc, 512))
-    t_pred = timed(lambda: o.decoder_layer(ph, predictor, pdims, pk, pv, 8))
-    t_head = timed(lambda: o.sample(o.int8_gemm_rows(head_w, head_s, h)[0], 1, suppress=True,
-                                    top_k=50, top_p=0.9))
-    t_phead = timed(lambda: o.sample(o.int8_gemm_rows(phead_w, head_s[:2048], ph)[0], 1, top_k=50))
-    t_mtp = timed(lambda: o.int8_gemm_rows(mtp_w, head_s[:1024], h))
-    t_text = 2 * timed(lambda: o.int8_gemm_rows(head_w[:2048], head_s[:2048], h))
-    frame = 28 * t_talker + 16 * 5 * t_pred + t_head + 15 * t_phead + 16 * t_mtp + t_text
-    sample = ("1 talker layer (L=513) + 1 predictor layer + heads + samplers of a B=1 frame, real "
-              "shapes, scaled x28 / x80 / x16 to one frame")
-    return frame, o.threads(), sample
+        def layer(hidden, inter, qw, kvw):
+            def q(n, k):
+                return (rng.integers(-127, 128, size=(n, k), dtype=np.int8),
+                        (rng.uniform(0.5, 1.5, size=n) / (73.6 * np.sqrt(k))).astype(np.float32))
+            ones = o.to_bf16(np.ones(hidden, dtype=np.float32))
+            hd = o.to_bf16(np.ones(128, dtype=np.float32))
+            return dict(input_norm=ones, qkv=q(qw + 2 * kvw, hidden), o=q(hidden, qw), q_norm=hd,
+                        k_norm=hd, post_norm=ones, gate_up=q(2 * inter, hidden), down=q(hidden, inter))
+
+        self.talker = layer(2048, 6144, 2048, 1024)
+        self.predictor = layer(1024, 3072, 2048, 1024)
+        self.kc = o.to_bf16(rng.standard_normal((513, 1024)).astype(np.float32))
+        self.vc = o.to_bf16(rng.standard_normal((513, 1024)).astype(np.float32))
+        self.pk = np.zeros((16, 1024), dtype=np.uint16)
+        self.pv = np.zeros((16, 1024), dtype=np.uint16)
+        self.h = o.to_bf16(rng.standard_normal(2048).astype(np.float32))
+        self.ph = o.to_bf16(rng.standard_normal(1024).astype(np.float32))
+        self.head_w = rng.integers(-127, 128, size=(3072, 2048), dtype=np.int8)
+        self.head_s = np.full(3072, 1.0 / 3000.0, dtype=np.float32)
+        self.phead_w = rng.integers(-127, 128, size=(2048, 1024), dtype=np.int8)
+        self.mtp_w = rng.integers(-127, 128, size=(1024, 2048), dtype=np.int8)
+        self.pdims = o.predictor_dims(128)
+        self.threads = o.threads()
+
+    def frame(self) -> float:
+        """Runs every operator of one B=1 frame (the same weights serve every layer: values do not
+        change the time) and returns the seconds it took."""
+        o = self
+        lib = self.o
+        t0 = time.perf_counter()
+        for position in range(16):                       # code predictor: 16 positions x 5 layers
+            lib.int8_gemm_rows(o.mtp_w, o.head_s[:1024], o.h)
+            for _ in range(5):
+                lib.decoder_layer(o.ph, o.predictor, o.pdims, o.pk, o.pv, position)
+            if position > 0:
+                lib.sample(lib.int8_gemm_rows(o.phead_w, o.head_s[:2048], o.ph)[0], 1, top_k=50, top_p=0.9)
+        for _ in range(2):                               # trailing text: two 2048 x 2048 projections
+            lib.int8_gemm_rows(o.head_w[:2048], o.head_s[:2048], o.h)
+        for _ in range(28):                              # talker step at position 512
+            lib.decoder_layer(o.h, o.talker, lib.TALKER_DIMS, o.kc, o.vc, 512)
+        lib.sample(lib.int8_gemm_rows(o.head_w, o.head_s, o.h)[0], 1, suppress=True, top_k=50, top_p=0.9)
+        return time.perf_counter() - t0
+
+
+def cpu_frames_timed(frames: int, warmup: int, budget_s: float):
+    """(per-frame seconds of the frames that ran, threads).  Stops early once `budget_s` is spent,
+    but runs at least one timed frame."""
+    cpu = CpuFrames()
+    for _ in range(warmup):
+        cpu.frame()
+    times = []
+    started = time.perf_counter()
+    for _ in range(max(1, frames)):
+        times.append(cpu.frame())
+        if time.perf_counter() - started > budget_s:
+            break
+    return times, cpu.threads
 
 
 def run_reference_arm(args, rank: int) -> None:
-    """CPU arm: the restatement of the reference's kernels on this host's cores."""
+    """CPU arm: the restatement of the reference's kernels on this host's cores, whole frames."""
     if rank != 0:
         return
-    for _ in range(max(0, min(args.warmup, 2))):
-        cpu_frame_seconds()
-    times = [cpu_frame_seconds()[0] for _ in range(max(1, min(args.steps, 5)))]
-    frame_s = float(np.mean(times))
-    _, threads, sample = cpu_frame_seconds()
+    times, threads = cpu_frames_timed(max(args.steps, 5), min(args.warmup, 2), budget_s=150.0)
+    frame_s = float(np.median(times))
     value = 1.0 / frame_s
+    config = workload_config(args.gpus)
+    config["workload"] = CPU_WORKLOAD
+    config["gpu_arm_workload"] = workload_config(args.gpus)["workload"]
     line = {
         "impl": "reference", "metric": "codec frames/s", "value": value, "unit": "frames/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 2),
         "ms_per_step": frame_s * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 weights x bf16 activations, fp32 accumulate",
         "data": "synthetic",
-        "config": workload_config(args.gpus),
+        "config": config,
         "cpu_baseline": {"value": value, "unit": "frames/s", "cores": threads, "kind": "port",
-                         "sample": sample},
+                         "sample": f"{len(times)} whole B=1 frames, median; " + CPU_WORKLOAD},
         "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "frame_seconds": {"min": float(np.min(times)), "median": frame_s, "max": float(np.max(times))},
         "note": "the reference has no CPU implementation of this path and no Rust toolchain is "
-                "available; this is the C restatement of its kernels (oracle/), frames are "
-                "sequential on the CPU so the rate does not grow with the session count",
+                "available; this is the C restatement of its kernels (oracle/).  steps = whole frames "
+                "actually run (the requested count, or fewer if 150 s were spent), value = 1 / median",
     }
     print(json.dumps(line), flush=True)
 
@@ -260,6 +287,88 @@ def api_frames(model, sessions, frames, trailing=11):
                 p.finish_without_consumer()
 
 
+def abi_frame_times(q3t, model, talker_cfg, predictor_cfg, frames: int = 30):
+    """B=1 and B=8 frame times through the reference's ABI calls only (session_create, prefill of a
+    512-id prompt, session_next_frame / model_batch_next_frame_begin_v2 + finish_v2), wall clock with
+    the host round trip every frame: works on any library that exports that ABI."""
+    ids = [int(t) for t in np.random.default_rng(4).integers(0, 151936, size=512)]
+    out = {"prompt_ids": 512, "frames_timed": frames}
+
+    def start(count, seed0):
+        group = []
+        for i in range(count):
+            s = model.create_session(1024, seed0 + i)
+            s.talker_sampling, s.predictor_sampling = talker_cfg, predictor_cfg
+            s.prefill(ids, [-1] * 512)
+            group.append(s)
+        return group
+
+    one = start(1, 300)[0]
+    gpu_ms, wall = [], []
+    for f in range(frames + 3):
+        if one.ended:
+            break
+        t0 = time.perf_counter()
+        fr = one.next_frame(11)
+        if f >= 3:
+            wall.append((time.perf_counter() - t0) * 1e3)
+            gpu_ms.append(fr.predictor_gpu_milliseconds + fr.talker_gpu_milliseconds)
+    one.close()
+    out["b1"] = {"api": "qwen3_tts_session_next_frame", "frames": len(wall),
+                 "ms_per_frame_wall": percentile(wall, 50), "ms_per_frame_gpu_events": percentile(gpu_ms, 50)}
+    group = start(8, 400)
+    wall = []
+    for f in range(frames + 3):
+        if any(s.ended for s in group):
+            break
+        t0 = time.perf_counter()
+        pending = model.batch_begin_device_frames(group, [11] * len(group))
+        for p in pending:
+            p.finish_without_consumer()
+        if f >= 3:
+            wall.append((time.perf_counter() - t0) * 1e3)
+    for s in group:
+        s.close()
+    out["b8"] = {"api": "qwen3_tts_model_batch_next_frame_begin_v2 + qwen3_tts_session_next_frame_finish_v2",
+                 "frames": len(wall), "ms_per_frame_wall": percentile(wall, 50),
+                 "frames_per_s": 8e3 / percentile(wall, 50) if wall else None}
+    return out
+
+
+def existing_kernels_block():
+    """The reference project's own CUDA code on this GPU, compiled for sm_100a into oracle/_ref (test
+    infrastructure): its int8 GEMV kernel on configs[0], and its whole library (int8 decode switched
+    on) driven through its ABI in a child process.  Outside every timed region of this line."""
+    from oracle import oracle as o
+    if not o.ref_available():
+        return {"unavailable": "oracle/_ref not built (needs a checkout of the reference where it was built)"}
+    o.build()
+    block = {}
+    us = o.ref_time_int8_gemm(2048, 6144, 1, 0, 16, 2000)
+    block["int8_gemm_rows_2048x6144"] = {
+        "kernel": "reference launch_int8_gemm_rows (int8_gemv.cu:318-334), rows = 1, 16 rotating weight images",
+        "us_per_launch": us, "GBps": GEMV_BYTES / us / 1e3 if us > 0 else None}
+    library = os.path.join(ROOT, "oracle", "_ref", "libqwen3_tts_cuda_ref.so")
+    if not os.path.exists(library):
+        block["library"] = {"unavailable": "oracle/_ref/libqwen3_tts_cuda_ref.so not built"}
+        return block
+    env = dict(os.environ)
+    env.update({"QWEN3_TTS_TALKER_LIBRARY": library, "QWEN3_TTS_INT8_DECODE": "1"})
+    for name in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        env.pop(name, None)
+    try:
+        proc = subprocess.run([sys.executable, os.path.abspath(__file__), "--leg", "existing"], env=env,
+                              capture_output=True, text=True, timeout=600)
+        last = [l for l in proc.stdout.splitlines() if l.startswith("{")]
+        if proc.returncode == 0 and last:
+            block["library"] = json.loads(last[-1])
+        else:
+            block["library"] = {"unavailable": (proc.stderr or "no output")[-300:]}
+    except (subprocess.TimeoutExpired, OSError) as e:
+        block["library"] = {"unavailable": str(e)[:300]}
+    return block
+
+
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     import torch
     import torch.distributed as dist
@@ -288,11 +397,25 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                           "GBps": (args.gemv_in * args.gemv_out) / g.mean_launch_microseconds / 1e3}),
               flush=True)
         return
+    if args.leg == "attn":
+        # operator microbenchmark: the 64-session ragged batch of one talker layer, contiguous caches
+        us, kv_bytes = native.benchmark_decode_attention(local_rank, rows=SESSIONS, min_length=64, max_length=2048,
+                                                         seed=3, iterations=max(args.steps, 1))
+        print(json.dumps({"leg": "attn", "rows": SESSIONS, "kv_lengths": "U[64, 2048], seed 3",
+                          "us_per_launch": us, "kv_bytes": kv_bytes, "GBps": kv_bytes / us / 1e3}), flush=True)
+        return
     model = q3t.NativeTalkerModel.load(local_rank, synth.checkpoint_cuda(local_rank, seed=0))
-    model.set_option("mask_eos", 1)
-    model.set_option("batch_host_codes", 1)
     talker_cfg = q3t.SamplingConfig(True, 50, 0.9, 0.9, 1.0)
     predictor_cfg = q3t.SamplingConfig(True, 50, 0.9, 0.9, 1.0)
+    if args.leg == "existing":
+        # whichever library QWEN3_TTS_TALKER_LIBRARY names, through the reference's ABI only
+        out = abi_frame_times(q3t, model, talker_cfg, predictor_cfg)
+        out["library"] = os.path.basename(os.environ.get("QWEN3_TTS_TALKER_LIBRARY", "libqwen3_tts_cuda.so"))
+        print(json.dumps(out), flush=True)
+        model.close()
+        return
+    model.set_option("mask_eos", 1)
+    model.set_option("batch_host_codes", 1)
     K, W = args.steps, args.warmup
     total_frames = 3 * (K + W) + 8
 
@@ -431,16 +554,24 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         # ---- batch-1 int8 GEMV, configs[0]: 16 weight images (201 MB > L2) round-robin --------------
         g = native.benchmark_int8_gemv(local_rank, 2048, 6144, rows=1, buffers=16, iterations=4000)
         gemv_s = g.mean_launch_microseconds * 1e-6
-        line["roofline"] = {"bound": "hbm", "kernel": "gemv_b1_kernel<4> 2048->6144 (configs[0])",
+        line["roofline"] = {"bound": "hbm", "kernel": "gemv_mma_kernel<4,false,false,1> 2048->6144 (configs[0]); the kernel the B=1 frame "
+                                      "dispatches for all its projections (gemv mode 1)",
                             "achieved": GEMV_BYTES / gemv_s / 1e9, "peak": hbm_peak, "unit": "GB/s",
                             "frac": GEMV_BYTES / gemv_s / 1e9 / hbm_peak, "peak_kind": peak_kind,
                             "frac_of_8TBs": GEMV_BYTES / gemv_s / 8.0e12,
-                            "us_per_launch": g.mean_launch_microseconds, "traffic": 12639488,  # dram__bytes_read+write per launch, ncu capture of this kernel (profiles/)
+                            "us_per_launch": g.mean_launch_microseconds,
+                            # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture
+                            # summarised in profiles/gemv_mma_kernel_2048x6144_rows1.md (not measured by this run)
+                            "traffic": GEMV_TRAFFIC_NCU, "traffic_source": "ncu capture, profiles/gemv_mma_kernel_2048x6144_rows1.md",
                             "bytes_per_launch": GEMV_BYTES}
+        if world == 1 and not args.no_existing:
+            line["existing_kernels"] = existing_kernels_block()
+            line["existing_kernels"]["ours_same_calls"] = abi_frame_times(q3t, model, talker_cfg, predictor_cfg)
         if world == 1 and not args.no_cpu_baseline:
-            frame_cpu, threads, sample = cpu_frame_seconds()
-            line["cpu_baseline"] = {"value": 1.0 / frame_cpu, "unit": "frames/s", "cores": threads,
-                                    "kind": "port", "sample": sample}
+            cpu_times, threads = cpu_frames_timed(5, 1, budget_s=30.0)
+            line["cpu_baseline"] = {"value": 1.0 / float(np.median(cpu_times)), "unit": "frames/s",
+                                    "cores": threads, "kind": "port",
+                                    "sample": f"{len(cpu_times)} whole B=1 frames, median; " + CPU_WORKLOAD}
         print(json.dumps(line), flush=True)
     model.close()
     if world > 1:
@@ -455,9 +586,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-existing", action="store_true",
+                    help="skip the existing_kernels block (the reference's kernels and library from oracle/_ref)")
     ap.add_argument("--gemv-mode", type=int, default=None,
                     help="kernel for 1..8 rows: 0 SIMT, 1 mma.sync (default), 2 bulk-copy SIMT")
-    ap.add_argument("--leg", choices=["all", "b64", "b1", "gemv"], default="all",
+    ap.add_argument("--leg", choices=["all", "b64", "b1", "gemv", "attn", "existing"], default="all",
                     help="profiling aid: run one leg only and print a short JSON line")
     ap.add_argument("--gemv-in", type=int, default=2048)
     ap.add_argument("--gemv-out", type=int, default=6144)

@@ -206,6 +206,15 @@ QWEN3_TTS_API int32_t q3t_set_gemv_mode(int32_t mode);
  * reference's.  Also reachable as model option "attention_mode". */
 QWEN3_TTS_API int32_t q3t_set_attention_mode(int32_t mode);
 
+/* Operator-level attention case for profiling: `rows` sessions with KV lengths uniform in
+ * [min_length, max_length] (seeded), 16 query / 8 KV heads of 128, contiguous bf16 caches of N(0,1);
+ * `iterations` launches in the attention mode in force, timed with CUDA events on their stream.
+ * *kv_bytes = the K and V bytes one launch reads (the algorithmic traffic). */
+QWEN3_TTS_API int32_t q3t_benchmark_decode_attention(int32_t device_index, int32_t rows, int32_t min_length,
+                                                     int32_t max_length, uint64_t seed, int32_t iterations,
+                                                     float* mean_launch_microseconds, uint64_t* kv_bytes,
+                                                     char* error, size_t error_capacity);
+
 /* ---- norms, RoPE, KV append, glue (talker_kernels.cu) --------------------------------- */
 
 QWEN3_TTS_API int32_t q3t_launch_rms_norm_rows(const uint16_t* input, const uint16_t* weight,
@@ -254,6 +263,13 @@ QWEN3_TTS_API int32_t q3t_launch_batch_causal_gqa_attention_fast(
     const int32_t* positions, uint16_t* output, int32_t rows, int32_t query_heads,
     int32_t key_value_heads, int32_t head_dimension, int32_t max_sequence_length, void* scratch,
     size_t scratch_bytes, void* stream);
+
+/* Positions are read from the caller's device memory and must lie in [0, max_sequence_length) (the
+ * scratch, the grid and the per-row ticket counts are sized from max_sequence_length).  A row whose
+ * position lies outside is computed over the clamped length instead of running past them, and is
+ * counted (process-wide) in q3t_attention_range_error_count(): a caller that cannot vouch for its
+ * positions compares that counter before and after. */
+QWEN3_TTS_API uint32_t q3t_attention_range_error_count(void);
 
 /* No counterpart in the reference.  The same operator for hosts that may not allocate device
  * memory where they run it (a real-time audio thread, a process with a fixed, policed memory

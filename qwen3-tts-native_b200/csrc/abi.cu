@@ -63,6 +63,7 @@ cudaError_t configure_device() {
             e = set_gemv_mma_error_sink(word);
             if (e == cudaSuccess) e = set_gemv_b1_error_sink(word);
             if (e == cudaSuccess) e = set_tc_error_sink(word);
+            if (e == cudaSuccess) e = set_attention_error_sink(word);
             if (e == cudaSuccess) g_error_words[device].store(word, std::memory_order_release);
         }
     }
@@ -132,14 +133,8 @@ int32_t ready() {
     return static_cast<int32_t>(e);
 }
 
-size_t counters_bytes(int rows, int kv_heads) {
-    return ((size_t)rows * kv_heads * sizeof(unsigned int) + 255) / 256 * 256;
-}
-
-int splits_for(int max_sequence_length) {
-    const int s = (max_sequence_length + kAttnChunk - 1) / kAttnChunk;
-    return s < 1 ? 1 : s;
-}
+size_t counters_bytes(int rows, int kv_heads) { return attention_counters_bytes(rows, kv_heads); }
+int splits_for(int max_sequence_length) { return attention_splits_for(max_sequence_length); }
 
 }  // namespace
 
@@ -739,6 +734,85 @@ int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t input_features,
     }, QWEN3_TTS_TALKER_STATUS_CUDA, error, error_capacity);
 }
 
+// Operator-level attention case: `rows` sessions with KV lengths drawn uniformly from
+// [min_length, max_length] (seeded), 16 query / 8 KV heads of 128, contiguous bf16 caches filled
+// with N(0,1); `iterations` launches of the decode attention in the mode in force, timed with
+// events.  One launch reads every row's K and V once: *kv_bytes.
+int32_t q3t_benchmark_decode_attention(int32_t device_index, int32_t rows, int32_t min_length,
+                                       int32_t max_length, uint64_t seed, int32_t iterations,
+                                       float* mean_launch_microseconds, uint64_t* kv_bytes, char* error,
+                                       size_t error_capacity) {
+    if (rows < 1 || rows > kMaxRows || min_length < 1 || max_length < min_length || max_length > 8192
+        || iterations < 1 || mean_launch_microseconds == nullptr || kv_bytes == nullptr) {
+        write_error(error, error_capacity, "attention benchmark arguments are out of range");
+        return QWEN3_TTS_TALKER_STATUS_INVALID_ARGUMENT;
+    }
+    return protect([&] {
+        check_cuda(cudaSetDevice(device_index), "cudaSetDevice");
+        check_cuda(configure_device(), "configure kernels");
+        constexpr int kQHeads = 16, kKvHeads = 8, kHeadDim = 128, kKvWidth = kKvHeads * kHeadDim;
+        std::vector<int> positions(rows);
+        std::vector<bf16*> k_bases(rows), v_bases(rows);
+        uint64_t state = seed * 0x9e3779b97f4a7c15ull + 0x2545f4914f6cdd1dull;
+        size_t tokens = 0;
+        for (int r = 0; r < rows; ++r) {
+            state ^= state >> 12; state ^= state << 25; state ^= state >> 27;
+            const int length = min_length + static_cast<int>((state * 0x2545f4914f6cdd1dull >> 33)
+                                                             % static_cast<uint64_t>(max_length - min_length + 1));
+            positions[r] = length - 1;
+            tokens += static_cast<size_t>(length);
+        }
+        DeviceBuffer k(tokens * kKvWidth * sizeof(bf16)), v(tokens * kKvWidth * sizeof(bf16));
+        DeviceBuffer q((size_t)rows * kQHeads * kHeadDim * sizeof(bf16)), out((size_t)rows * kQHeads * kHeadDim * sizeof(bf16));
+        DeviceBuffer dpos((size_t)rows * sizeof(int)), dk((size_t)rows * sizeof(bf16*)), dv((size_t)rows * sizeof(bf16*));
+        size_t at = 0;
+        for (int r = 0; r < rows; ++r) {
+            k_bases[r] = k.as<bf16>() + at * kKvWidth;
+            v_bases[r] = v.as<bf16>() + at * kKvWidth;
+            at += static_cast<size_t>(positions[r] + 1);
+        }
+        const int splits = splits_for(max_length);
+        DeviceBuffer scratch(attention_scratch_floats(rows, kQHeads, kHeadDim, splits) * sizeof(float));
+        DeviceBuffer counters(counters_bytes(rows, kKvHeads));
+        cudaStream_t stream = nullptr;
+        cudaEvent_t t0 = nullptr, t1 = nullptr;
+        check_cuda(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        float total_ms = 0.0f;
+        try {
+            check_cuda(cudaEventCreate(&t0), "cudaEventCreate");
+            check_cuda(cudaEventCreate(&t1), "cudaEventCreate");
+            check_cuda(launch_fill_normal(k.as<bf16>(), tokens * kKvWidth, seed * 3 + 1, stream), "fill K");
+            check_cuda(launch_fill_normal(v.as<bf16>(), tokens * kKvWidth, seed * 3 + 2, stream), "fill V");
+            check_cuda(launch_fill_normal(q.as<bf16>(), (size_t)rows * kQHeads * kHeadDim, seed * 3 + 3, stream), "fill q");
+            check_cuda(cudaMemsetAsync(counters.as<void>(), 0, counters.bytes(), stream), "cudaMemsetAsync");
+            check_cuda(cudaMemcpyAsync(dpos.as<void>(), positions.data(), dpos.bytes(), cudaMemcpyHostToDevice, stream), "upload positions");
+            check_cuda(cudaMemcpyAsync(dk.as<void>(), k_bases.data(), dk.bytes(), cudaMemcpyHostToDevice, stream), "upload K bases");
+            check_cuda(cudaMemcpyAsync(dv.as<void>(), v_bases.data(), dv.bytes(), cudaMemcpyHostToDevice, stream), "upload V bases");
+            AttentionArgs a;
+            a.q = q.as<bf16>(); a.out = out.as<bf16>(); a.positions = dpos.as<int>();
+            a.kv.k_bases = dk.as<bf16*>(); a.kv.v_bases = dv.as<bf16*>();
+            a.rows = rows; a.q_heads = kQHeads; a.kv_heads = kKvHeads; a.head_dim = kHeadDim;
+            a.max_splits = splits;
+            a.scratch = scratch.as<float>(); a.counters = counters.as<unsigned int>();
+            for (int i = 0; i < 3; ++i) check_cuda(launch_attention(a, stream), "decode attention");
+            check_cuda(cudaEventRecord(t0, stream), "cudaEventRecord");
+            for (int i = 0; i < iterations; ++i) check_cuda(launch_attention(a, stream), "decode attention");
+            check_cuda(cudaEventRecord(t1, stream), "cudaEventRecord");
+            check_cuda(cudaEventSynchronize(t1), "cudaEventSynchronize");
+            check_cuda(cudaEventElapsedTime(&total_ms, t0, t1), "cudaEventElapsedTime");
+        } catch (...) {
+            if (t0 != nullptr) cudaEventDestroy(t0);
+            if (t1 != nullptr) cudaEventDestroy(t1);
+            cudaStreamSynchronize(stream);
+            cudaStreamDestroy(stream);
+            throw;
+        }
+        cudaEventDestroy(t0); cudaEventDestroy(t1); cudaStreamDestroy(stream);
+        *mean_launch_microseconds = total_ms * 1000.0f / iterations;
+        *kv_bytes = static_cast<uint64_t>(tokens) * kKvWidth * sizeof(bf16) * 2;
+    }, QWEN3_TTS_TALKER_STATUS_CUDA, error, error_capacity);
+}
+
 }  // extern "C"
 
 extern "C" {
@@ -994,6 +1068,8 @@ int32_t q3t_test_report_device_wait_failure(int32_t device_index) {
 uint32_t q3t_kernel_error_count(void) {
     return gemv_b1_error_count() + gemm_tc_error_count() + gemv_mma_error_count();
 }
+
+uint32_t q3t_attention_range_error_count(void) { return attention_range_error_count(); }
 
 int32_t q3t_session_current_token(Qwen3TtsSessionHandle session, uint16_t* token, char* error,
                                   size_t error_capacity) {

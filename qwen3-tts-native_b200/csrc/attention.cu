@@ -23,6 +23,12 @@
 namespace q3t {
 namespace {
 
+// Rows whose position lay outside [0, max_splits * kAttnChunk): the kernel clamps the length to what
+// its scratch and grid were sized for, computes over that and counts the row here (and in the
+// engine's host-mapped error word, if one is registered), so that the host can refuse the result.
+__device__ unsigned int g_attention_range_errors = 0;
+__device__ unsigned int* g_attention_error_sink = nullptr;
+
 constexpr int kAttnThreads = 128;
 constexpr int kAttnWarps = kAttnThreads / kWarp;
 constexpr int kWarpTokens = kAttnChunk / kAttnWarps;   // 16 = one page
@@ -159,6 +165,18 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
     pdl_wait();        // q / k_new / v_new (and, unless settled, everything else) come from the kernel before
     pdl_trigger();
     if (!early) pos = a.positions[row];
+    {
+        // the position comes from device memory the caller filled; the grid, the scratch partials and
+        // the ticket count were sized for max_splits chunks
+        const int limit = a.max_splits * kAttnChunk - 1;
+        if (pos < 0 || pos > limit) {
+            if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+                atomicAdd(&g_attention_range_errors, 1u);
+                if (g_attention_error_sink != nullptr) atomicAdd_system(g_attention_error_sink, 1u);
+            }
+            pos = pos < 0 ? 0 : limit;
+        }
+    }
     const int len = pos + 1;
     const int nsplits = (len + kAttnChunk - 1) / kAttnChunk;
     // A CTA walks `units` consecutive 64-token splits.  Each split still produces its own
@@ -642,8 +660,15 @@ __global__ void __launch_bounds__(kOrderedThreads) attention_reference_order_ker
 
     pdl_wait();
     pdl_trigger();
-    const int pos = a.positions[row];
-    const int len = min(pos + 1, kOrderedMaxLength);     // the launcher's callers keep positions below the limit
+    int pos = a.positions[row];
+    if (pos < 0 || pos >= kOrderedMaxLength) {
+        if (tid == 0) {
+            atomicAdd(&g_attention_range_errors, 1u);
+            if (g_attention_error_sink != nullptr) atomicAdd_system(g_attention_error_sink, 1u);
+        }
+        pos = pos < 0 ? 0 : kOrderedMaxLength - 1;
+    }
+    const int len = pos + 1;
 
     auto kv_row = [&](int token, bool value) -> const bf16* {
         if (a.kv.page_table != nullptr) {
@@ -803,6 +828,16 @@ cudaError_t launch_decode_attention(const AttentionArgs& a, cudaStream_t stream)
         case 128: return launch_hd<128>(b, stream);
         default: return cudaErrorInvalidValue;
     }
+}
+
+unsigned int attention_range_error_count() {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attention_range_errors, sizeof(v)) != cudaSuccess) return ~0u;
+    return v;
+}
+
+cudaError_t set_attention_error_sink(unsigned int* device_visible_word) {
+    return cudaMemcpyToSymbol(g_attention_error_sink, &device_visible_word, sizeof(device_visible_word));
 }
 
 namespace {

@@ -25,7 +25,7 @@
 #include "q3t_ops.h"
 
 #include <cstdio>
-#include <mutex>
+#include <atomic>
 
 namespace {
 
@@ -34,8 +34,8 @@ constexpr int kMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_attention_scratch[kStaticScratchBytes];
 
-std::mutex g_guard;
-void* g_scratch_address[kMaxDevices] = {};
+// resolved once per device; a first call racing another resolves the same address twice, harmlessly
+std::atomic<void*> g_scratch_address[kMaxDevices] = {};
 
 void message(char* error, size_t capacity, const char* text) {
     if (error != nullptr && capacity != 0) std::snprintf(error, capacity, "%s", text);
@@ -47,15 +47,14 @@ cudaError_t scratch_for_current_device(void** out) {
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return e;
     if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
-    std::lock_guard<std::mutex> lock(g_guard);
-    if (g_scratch_address[device] == nullptr) {
-        void* address = nullptr;
+    void* address = g_scratch_address[device].load(std::memory_order_acquire);
+    if (address == nullptr) {
         e = cudaGetSymbolAddress(&address, g_attention_scratch);
         if (e != cudaSuccess) return e;
         if (address == nullptr) return cudaErrorInvalidSymbol;
-        g_scratch_address[device] = address;
+        g_scratch_address[device].store(address, std::memory_order_release);
     }
-    *out = g_scratch_address[device];
+    *out = address;
     return cudaSuccess;
 }
 
@@ -93,9 +92,8 @@ extern "C" int32_t q3t_launch_batch_causal_gqa_attention_fast_noalloc(
         return QWEN3_TTS_TALKER_STATUS_CUDA;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int splits = (max_sequence_length + kAttnChunk - 1) / kAttnChunk;
-    const size_t counter_bytes =
-        ((size_t)rows * key_value_heads * sizeof(unsigned int) + 255) / 256 * 256;
+    const int splits = attention_splits_for(max_sequence_length);
+    const size_t counter_bytes = attention_counters_bytes(rows, key_value_heads);
     AttentionArgs a;
     a.q = reinterpret_cast<const bf16*>(query);
     a.positions = positions;
@@ -106,7 +104,7 @@ extern "C" int32_t q3t_launch_batch_causal_gqa_attention_fast_noalloc(
     a.q_heads = query_heads;
     a.kv_heads = key_value_heads;
     a.head_dim = head_dimension;
-    a.max_splits = splits < 1 ? 1 : splits;
+    a.max_splits = splits;
     a.counters = static_cast<unsigned int*>(scratch);
     a.scratch = reinterpret_cast<float*>(static_cast<char*>(scratch) + counter_bytes);
     // the array holds the last call's contents: the ticket counters have to start at zero

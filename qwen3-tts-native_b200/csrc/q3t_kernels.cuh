@@ -168,6 +168,15 @@ struct AttentionArgs {
 constexpr int kAttnChunk = 64;          // tokens per split
 size_t attention_scratch_floats(int rows, int q_heads, int head_dim, int max_splits);
 cudaError_t launch_decode_attention(const AttentionArgs& args, cudaStream_t stream);
+// Layout of a caller's scratch buffer for the split-KV kernel, shared by every entry point that
+// carves one up: ticket counters first (rounded to 256 bytes), the chunk partials behind them.
+inline size_t attention_counters_bytes(int rows, int kv_heads) {
+    return ((size_t)rows * kv_heads * sizeof(unsigned int) + 255) / 256 * 256;
+}
+inline int attention_splits_for(int max_sequence_length) {
+    const int s = (max_sequence_length + kAttnChunk - 1) / kAttnChunk;
+    return s < 1 ? 1 : s;
+}
 // Parity mode: the same attention with every fp32 sum formed in the order of the reference's
 // kernel (bit-identical bf16 output; slow).  Fused mode normalises and rotates the query heads;
 // the new token's K/V must already be in the cache (launch_decode_attention with append_mode 1).
@@ -176,6 +185,9 @@ cudaError_t launch_attention_reference_order(const AttentionArgs& args, cudaStre
 // Process-wide choice between the two (1, default: split-KV kernel; 0: reference order) and the
 // launcher that honours it: in mode 0 a fused call appends with the split-KV kernel's prologue,
 // then attends in the reference's order.
+// rows seen so far whose position lay outside what the launch was sized for (clamped and counted)
+unsigned int attention_range_error_count();
+cudaError_t set_attention_error_sink(unsigned int* device_visible_word);
 int set_attention_mode(int mode);
 int attention_mode();
 cudaError_t launch_attention(const AttentionArgs& args, cudaStream_t stream);

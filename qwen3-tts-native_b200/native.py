@@ -111,7 +111,7 @@ EXPORTED_SYMBOLS = (
     "q3t_launch_int8_gemm_rows", "q3t_launch_int8_gemm_rows_add",
     "q3t_launch_int8_gate_up_silu_rows", "q3t_launch_int8_gemm_ex",
     "q3t_launch_quantize_weight_rows", "q3t_benchmark_int8_gemv", "q3t_launch_rms_norm_rows",
-    "q3t_set_gemv_mode", "q3t_set_attention_mode", "q3t_test_fail_launch_after", "q3t_test_fail_allocation_after",
+    "q3t_set_gemv_mode", "q3t_set_attention_mode", "q3t_benchmark_decode_attention", "q3t_attention_range_error_count", "q3t_test_fail_launch_after", "q3t_test_fail_allocation_after",
     "q3t_test_report_device_wait_failure", "q3t_host_pump_frames",
     "q3t_pump_create", "q3t_pump_destroy", "q3t_pump_register", "q3t_pump_unregister",
     "q3t_pump_begin_frame", "q3t_pump_statistics", "q3t_pick_device",
@@ -623,6 +623,21 @@ def set_attention_mode(mode: int) -> int:
     """Decode attention kernel: 1 split-KV on tensor cores (default), 0 sums in the reference's order
     (parity mode, bit-identical to the reference's kernel, slow).  Returns the previous mode."""
     return int(library().q3t_set_attention_mode(int(mode)))
+
+
+def benchmark_decode_attention(device_index: int, rows: int = 64, min_length: int = 64, max_length: int = 2048,
+                               seed: int = 3, iterations: int = 20):
+    """(mean microseconds per launch, K+V bytes one launch reads) of the decode attention on a seeded
+    ragged batch of contiguous caches -- the operator-level case profiles are taken on."""
+    us = C.c_float(0.0)
+    nbytes = C.c_uint64(0)
+    err = C.create_string_buffer(_ERR_CAP)
+    lib = library()
+    lib.q3t_benchmark_decode_attention.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_uint64, C.c_int32,
+                                                   C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.c_char_p, C.c_size_t]
+    _check(lib.q3t_benchmark_decode_attention(device_index, rows, min_length, max_length, seed, iterations,
+                                              C.byref(us), C.byref(nbytes), err, _ERR_CAP), err)
+    return float(us.value), int(nbytes.value)
 
 
 def benchmark_int8_gemv(device_index: int, in_features: int, out_features: int, rows: int = 1,

@@ -231,3 +231,22 @@ def test_reference_order_fused(orc, ops, ref, reference_order):
     assert np.array_equal(fused["k"], kc) and np.array_equal(fused["v"], vc)
     want = ref.ref_attention(q2, kc, vc, pos, qh, kvh, hd, fast=True)
     assert np.array_equal(fused["out"].reshape(-1), want.reshape(-1))
+
+
+def test_position_outside_the_launch_is_clamped_and_counted(q3t, orc, ops):
+    """A position at or past max_sequence_length (the caller's device memory said so) must not run the
+    kernel over scratch and tickets it was not sized for: the row is computed over the clamped length,
+    the library's range-error counter rises, and the next launch is unaffected."""
+    rows, qh, kvh, hd, cap = 2, 16, 8, 128, 128
+    q, k, v, pos = make(orc, 31, rows, qh, kvh, hd, cap, [127, 40])
+    lib = q3t.library()
+    before = int(lib.q3t_attention_range_error_count())
+    good = ops.attention_ex(q, pos, qh, kvh, hd, k=k, v=v)["out"]
+    assert int(lib.q3t_attention_range_error_count()) == before
+    bad_pos = np.array([5000, 40], dtype=np.int32)       # row 0 claims a length the launch was not sized for
+    out = ops.attention_ex(q, bad_pos, qh, kvh, hd, k=k, v=v)["out"]
+    assert int(lib.q3t_attention_range_error_count()) > before
+    assert np.array_equal(out.reshape(rows, -1)[0], good.reshape(rows, -1)[0])      # clamped to position 127
+    assert np.array_equal(out.reshape(rows, -1)[1], good.reshape(rows, -1)[1])
+    again = ops.attention_ex(q, pos, qh, kvh, hd, k=k, v=v)["out"]
+    assert np.array_equal(again, good)

@@ -43,7 +43,22 @@ def worker(rank: int, world: int, port: int, results):
         session = model.start_prompt([1501, 77, 151935, -1, 9000, 42, 31337, 8], [-1, 2148, 3, 2049, -1, 100, 7, 2000], 64, 777, t, p)
         frames = [tuple(session.next_frame(9).codes) for _ in range(3)]
         session.close()
-        results[rank] = dict(sent=sent, tensors=int(memory.tensor_count), frames=frames,
+        # placement independence: the sessions every rank owns under the data-parallel sharding
+        # (dp.shard_session_seeds), decoded here as lockstep batches whatever this rank is
+        by_owner = {}
+        for owner in range(world):
+            group = [model.start_prompt([1501, 77, 9000, 42], [-1, 2148, -1, 100], 64, seed, t, p)
+                     for seed in dp.shard_session_seeds(owner, 3)]
+            codes = [[] for _ in group]
+            for _ in range(3):
+                pending = model.batch_begin_device_frames(group, [9] * len(group))
+                for i, pf in enumerate(pending):
+                    frame = pf.finish_without_consumer()
+                    codes[i].append(int(frame.next_semantic_token))
+            by_owner[owner] = codes
+            for x in group:
+                x.close()
+        results[rank] = dict(sent=sent, tensors=int(memory.tensor_count), frames=frames, by_owner=by_owner,
                              errors=int(q3t.native.library().q3t_kernel_error_count()))
         dist.barrier()
     finally:
@@ -66,4 +81,7 @@ def test_broadcast_image_then_decode_on_two_gpus():
     assert r0["tensors"] == r1["tensors"] == 404
     assert r0["sent"] == r1["sent"] > 2_000_000_000
     assert r0["frames"] == r1["frames"]
+    # a session's tokens depend on its seed and prompt, not on the GPU or rank that decodes it
+    assert r0["by_owner"] == r1["by_owner"]
+    assert r0["by_owner"][0] != r0["by_owner"][1]          # different seeds do give different sessions
     assert r0["errors"] == r1["errors"] == 0

@@ -58,3 +58,39 @@ def test_oversized_shape_is_refused(q3t, orc, ops):
     status, message, _ = ops.attention_contiguous_noalloc(q, k, v, pos, qh, kvh, hd)
     assert status == q3t.native.STATUS_INVALID_ARGUMENT
     assert "scratch" in message and str(capacity) in message
+
+
+FRESH_PROCESS_SCRIPT = r"""
+import importlib, sys
+import numpy as np
+sys.path.insert(0, sys.argv[1])
+from oracle import oracle as orc
+orc.build()
+ops = importlib.import_module("qwen3-tts-native_b200.ops")
+rng = np.random.default_rng(5)
+rows, qh, kvh, hd, cap = 3, 16, 8, 128, 520
+q = orc.to_bf16(rng.standard_normal((rows, qh * hd)).astype(np.float32))
+k = orc.to_bf16(rng.standard_normal((rows, cap, kvh * hd)).astype(np.float32))
+v = orc.to_bf16(rng.standard_normal((rows, cap, kvh * hd)).astype(np.float32))
+pos = np.asarray([519, 77, 0], dtype=np.int32)
+# the very first call this process makes into the library: nothing has resolved the built-in
+# array's address or configured a kernel before it
+status, message, got = ops.attention_contiguous_noalloc(q, k, v, pos, qh, kvh, hd)
+assert status == 0 and message == "", (status, message)
+want = ops.attention_contiguous(q, k, v, pos, qh, kvh, hd)
+assert np.array_equal(got, want)
+print("fresh-process first call ok")
+"""
+
+
+def test_first_call_in_a_fresh_process(ops):
+    """The entry point as the first thing a new process asks of the library (address of the built-in
+    array not yet resolved, kernels not yet configured), which running after other tests cannot show."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run([sys.executable, "-c", FRESH_PROCESS_SCRIPT, root], capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert "fresh-process first call ok" in proc.stdout
