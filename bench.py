@@ -46,7 +46,7 @@ if ROOT not in sys.path:
 
 SESSIONS = 64
 GEMV_BYTES = 6144 * 2048 + 6144 * 4 + 2048 * 2 + 6144 * 2          # W + scales + x + y
-GEMV_TRAFFIC_NCU = None                                               # bytes per launch, see roofline.traffic_source
+GEMV_TRAFFIC_NCU = 12647936                                               # bytes per launch, see roofline.traffic_source
 TALKER_WEIGHT_BYTES = 1_423_966_208 + 2_322_432                      # int8 rows + fp32 scales
 PREDICTOR_FRAME_BYTES = 1_323_302_912
 KV_BYTES_PER_TOKEN = 28 * 2 * 1024 * 2                               # all layers, K and V
