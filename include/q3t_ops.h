@@ -291,7 +291,11 @@ QWEN3_TTS_API size_t q3t_attention_static_scratch_capacity(void);
 
 /* Full form: paged KV and/or the fused per-head RMSNorm + RoPE + KV append, which the reference
  * issues as launch_head_rms_norm_rows x2, launch_rope_rows_at x2, launch_kv_scatter_rows x2
- * (talker.cu:2101-2175) before the attention launch. */
+ * (talker.cu:2101-2175) before the attention launch.
+ * Paged caches: a page holds Q3T_KV_PAGE_TOKENS tokens of one plane (K or V) of one layer as
+ * [key_value_heads][Q3T_KV_PAGE_TOKENS][head_dimension] bf16, i.e. head-major: the tokens of one KV
+ * head are contiguous.  (The reference's caches are contiguous per session, [position][kv width];
+ * the paged layout has no counterpart there.) */
 typedef struct Q3tAttentionDesc {
     uint32_t struct_size;        /* sizeof(Q3tAttentionDesc) */
     int32_t fused;               /* 1: q/key_new are raw projections; normalize, rotate, append */

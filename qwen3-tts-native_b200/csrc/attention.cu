@@ -68,6 +68,9 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
     const int lane = tid % kWarp;
     const int warp = tid / kWarp;
     const int kvw = a.kv_heads * HD;
+    // elements between consecutive tokens of one KV head: pages are head-major ([kv head][16][HD], a
+    // head's 16 tokens are one contiguous block), contiguous caches token-major
+    const int tstride = PAGED ? HD : kvw;
     const int qw = a.q_heads * HD;
     const int q_stride = a.q_stride > 0 ? a.q_stride : qw;
     const int kn_stride = a.kv_new_stride > 0 ? a.kv_new_stride : kvw;
@@ -83,7 +86,7 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
             bf16* slab = a.kv.slabs[pid >> a.kv.slab_shift];
             const long long in_slab = (long long)(pid & ((1 << a.kv.slab_shift) - 1)) * a.kv.page_elems;
             return slab + in_slab + (value ? a.kv.v_offset : a.kv.k_offset)
-                   + (size_t)(token % kPageTokens) * kvw + (size_t)kvh * HD;
+                   + (size_t)kvh * (kPageTokens * HD) + (size_t)(token % kPageTokens) * HD;
         }
         bf16* base = value ? a.kv.v_bases[row] : a.kv.k_bases[row];
         return base + (size_t)token * kvw + (size_t)kvh * HD;
@@ -103,7 +106,7 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
             const bool valid = w0 + t < bound;
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
-                kr[nt][jj] = valid ? *reinterpret_cast<const int4*>(kpage + (size_t)t * kvw + 32 * jj + 8 * tig)
+                kr[nt][jj] = valid ? *reinterpret_cast<const int4*>(kpage + (size_t)t * tstride + 32 * jj + 8 * tig)
                                    : zero4;
             }
         }
@@ -117,7 +120,7 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
                 const bool valid = w0 + t < bound;
 #pragma unroll
                 for (int jb = 0; jb < 2; ++jb) {
-                    vr[h][pp][jb] = valid ? *reinterpret_cast<const int4*>(vpage + (size_t)t * kvw + 64 * jb + 8 * gid)
+                    vr[h][pp][jb] = valid ? *reinterpret_cast<const int4*>(vpage + (size_t)t * tstride + 64 * jb + 8 * gid)
                                           : zero4;
                 }
             }
@@ -441,12 +444,12 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
 #pragma unroll
         for (int it = 0; it < ITERS; ++it) {
             const int t = it * TPI + sub;
-            if (w0 + t < c1) raw[it] = *reinterpret_cast<const int4*>(kpage + (size_t)t * kvw + j8);
+            if (w0 + t < c1) raw[it] = *reinterpret_cast<const int4*>(kpage + (size_t)t * tstride + j8);
         }
 #pragma unroll
         for (int it = 0; it < ITERS; ++it) {
             const int t = it * TPI + sub;
-            if (w0 + t < c1) rawv[it] = *reinterpret_cast<const int4*>(vpage + (size_t)t * kvw + j8);
+            if (w0 + t < c1) rawv[it] = *reinterpret_cast<const int4*>(vpage + (size_t)t * tstride + j8);
         }
 
         float s[G][ITERS];
@@ -676,7 +679,7 @@ __global__ void __launch_bounds__(kOrderedThreads) attention_reference_order_ker
             const bf16* slab = a.kv.slabs[pid >> a.kv.slab_shift];
             const long long in_slab = (long long)(pid & ((1 << a.kv.slab_shift) - 1)) * a.kv.page_elems;
             return slab + in_slab + (value ? a.kv.v_offset : a.kv.k_offset)
-                   + (size_t)(token % kPageTokens) * kvw + (size_t)kvh * HD;
+                   + (size_t)kvh * (kPageTokens * HD) + (size_t)(token % kPageTokens) * HD;
         }
         const bf16* base = value ? a.kv.v_bases[row] : a.kv.k_bases[row];
         return base + (size_t)token * kvw + (size_t)kvh * HD;

@@ -1494,6 +1494,10 @@ void Session::read_kv(int layer, int first, int count, uint16_t* keys, uint16_t*
     check_cuda(cudaStreamSynchronize(stream_), "cudaStreamSynchronize(read kv)");
     const KvPool& pool = *model_->talker_pool;
     const int width = model_->talker.kv_width;
+    const int hd = model_->talker.head_dim;
+    const int heads = model_->talker.kv_heads;
+    // a page holds [kv head][16 tokens][head_dim]: fetch the page whole, hand out token-major rows
+    std::vector<uint16_t> page_copy((size_t)kPageTokens * width);
     for (int token = first; token < first + count;) {
         const int in_page = token % kPageTokens;
         const int run = std::min(kPageTokens - in_page, first + count - token);
@@ -1501,9 +1505,14 @@ void Session::read_kv(int layer, int first, int count, uint16_t* keys, uint16_t*
         for (int plane = 0; plane < 2; ++plane) {
             uint16_t* out = plane == 0 ? keys : values;
             if (out == nullptr) continue;
-            check_cuda(cudaMemcpy(out + (size_t)(token - first) * width,
-                                  pool.page_rows(page, layer, plane == 1) + (size_t)in_page * width,
-                                  (size_t)run * width * sizeof(bf16), cudaMemcpyDeviceToHost), "cudaMemcpy(read kv)");
+            check_cuda(cudaMemcpy(page_copy.data(), pool.page_rows(page, layer, plane == 1),
+                                  page_copy.size() * sizeof(uint16_t), cudaMemcpyDeviceToHost), "cudaMemcpy(read kv)");
+            for (int t = 0; t < run; ++t) {
+                for (int h = 0; h < heads; ++h) {
+                    std::memcpy(out + (size_t)(token - first + t) * width + (size_t)h * hd,
+                                page_copy.data() + ((size_t)h * kPageTokens + in_page + t) * hd, (size_t)hd * sizeof(uint16_t));
+                }
+            }
         }
         token += run;
     }

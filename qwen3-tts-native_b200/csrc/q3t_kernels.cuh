@@ -117,7 +117,9 @@ cudaError_t launch_gather_embedding_rows(const bf16* table, int vocabulary, int 
 // ---------------------------------------------------------------- decode attention
 // Where the K/V rows of one batch row live.  Contiguous: base[row] + token*kv_width.
 // Paged: pages of kPageTokens tokens; page id p of a row lives at
-// slabs[p >> slab_shift] + (p & slab_mask) * page_elems + layer_offset.
+// slabs[p >> slab_shift] + (p & slab_mask) * page_elems + layer_offset, and holds
+// [kv head][kPageTokens][head_dim]: the tokens of one KV head are one contiguous block (what a CTA
+// of the attention kernel reads), not interleaved with the other heads.
 struct KvLayout {
     bf16* const* k_bases = nullptr;     // contiguous mode: [rows]
     bf16* const* v_bases = nullptr;

@@ -268,7 +268,8 @@ def attention_ex(q, positions, q_heads, kv_heads, head_dim, *, k=None, v=None, p
                  k_norm_w=None, fused=False, q_stride=0, new_stride=0, max_seq=None,
                  want_f32=False, theta=1.0e6, eps=1.0e-6):
     """Full-form attention.  Contiguous: k, v [rows][capacity][kvw].  Paged: `pages` is a list
-    of slabs, each [2][pages_per_slab][16][kvw] (K plane then V plane), page_table
+    of slabs, each [2][pages_per_slab][kv_heads][16][head_dim] (K plane then V plane; a page is
+    head-major: the 16 tokens of one KV head are contiguous), page_table
     [rows][stride].  Returns dict(out, f32, k, v | pages) with caches after the append."""
     lib = native.library()
     rows = np.asarray(positions).size

@@ -82,12 +82,14 @@ def test_reference_shaped_entry_point(orc, ops):
     assert np.array_equal(got, full["out"])
 
 
-def paged_copy(k, v, kvw, rng, per_slab):
-    """Scatters contiguous caches [rows][cap][kvw] into shuffled 16-token pages of two slabs."""
+def paged_copy(k, v, kvw, rng, per_slab, hd=128):
+    """Scatters contiguous caches [rows][cap][kvw] into shuffled 16-token pages of two slabs.  A page is
+    head-major: [kv head][16 tokens][head_dim], so that a head's 16 tokens are one contiguous block."""
     rows, cap, _ = k.shape
+    heads = kvw // hd
     pages_per_row = (cap + 15) // 16
     total = rows * pages_per_row
-    slabs = [np.zeros((2, per_slab, 16, kvw), dtype=np.uint16) for _ in range((total + per_slab - 1) // per_slab + 1)]
+    slabs = [np.zeros((2, per_slab, heads, 16, hd), dtype=np.uint16) for _ in range((total + per_slab - 1) // per_slab + 1)]
     ids = rng.permutation(len(slabs) * per_slab)[:total]
     table = ids.reshape(rows, pages_per_row).astype(np.int32)
     for r in range(rows):
@@ -95,8 +97,8 @@ def paged_copy(k, v, kvw, rng, per_slab):
             pid = int(table[r, p])
             s, i = divmod(pid, per_slab)
             n = min(16, cap - p * 16)
-            slabs[s][0, i, :n] = k[r, p * 16:p * 16 + n]
-            slabs[s][1, i, :n] = v[r, p * 16:p * 16 + n]
+            slabs[s][0, i, :, :n] = k[r, p * 16:p * 16 + n].reshape(n, heads, hd).transpose(1, 0, 2)
+            slabs[s][1, i, :, :n] = v[r, p * 16:p * 16 + n].reshape(n, heads, hd).transpose(1, 0, 2)
     return slabs, table
 
 
@@ -154,8 +156,8 @@ def test_fused_paged_append(orc, ops):
     for r in range(rows):   # the appended row landed in the right page
         pid = int(table[r, pos[r] // 16])
         s, i = divmod(pid, 16)
-        assert np.array_equal(b["pages"][s][0, i, pos[r] % 16], a["k"][r, pos[r]])
-        assert np.array_equal(b["pages"][s][1, i, pos[r] % 16], a["v"][r, pos[r]])
+        assert np.array_equal(b["pages"][s][0, i, :, pos[r] % 16].reshape(-1), a["k"][r, pos[r]])
+        assert np.array_equal(b["pages"][s][1, i, :, pos[r] % 16].reshape(-1), a["v"][r, pos[r]])
 
 
 def test_repeated_launches_reuse_scratch(orc, ops):
