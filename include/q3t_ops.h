@@ -207,7 +207,7 @@ QWEN3_TTS_API int32_t q3t_set_gemv_mode(int32_t mode);
 QWEN3_TTS_API int32_t q3t_set_attention_mode(int32_t mode);
 
 /* Operator-level attention case for profiling: `rows` sessions with KV lengths uniform in
- * [min_length, max_length] (seeded), 16 query / 8 KV heads of 128, contiguous bf16 caches of N(0,1);
+ * [min_length, max_length] (seeded), 16 query / 8 KV heads of 128, paged bf16 caches of N(0,1);
  * `iterations` launches in the attention mode in force, timed with CUDA events on their stream.
  * *kv_bytes = the K and V bytes one launch reads (the algorithmic traffic). */
 QWEN3_TTS_API int32_t q3t_benchmark_decode_attention(int32_t device_index, int32_t rows, int32_t min_length,

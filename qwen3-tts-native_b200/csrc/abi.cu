@@ -735,8 +735,8 @@ int32_t q3t_benchmark_int8_gemv(int32_t device_index, int32_t input_features,
 }
 
 // Operator-level attention case: `rows` sessions with KV lengths drawn uniformly from
-// [min_length, max_length] (seeded), 16 query / 8 KV heads of 128, contiguous bf16 caches filled
-// with N(0,1); `iterations` launches of the decode attention in the mode in force, timed with
+// [min_length, max_length] (seeded), 16 query / 8 KV heads of 128, paged bf16 caches (16-token
+// head-major pages in one slab) filled with N(0,1); `iterations` launches of the decode attention in the mode in force, timed with
 // events.  One launch reads every row's K and V once: *kv_bytes.
 int32_t q3t_benchmark_decode_attention(int32_t device_index, int32_t rows, int32_t min_length,
                                        int32_t max_length, uint64_t seed, int32_t iterations,
@@ -752,25 +752,24 @@ int32_t q3t_benchmark_decode_attention(int32_t device_index, int32_t rows, int32
         check_cuda(configure_device(), "configure kernels");
         constexpr int kQHeads = 16, kKvHeads = 8, kHeadDim = 128, kKvWidth = kKvHeads * kHeadDim;
         std::vector<int> positions(rows);
-        std::vector<bf16*> k_bases(rows), v_bases(rows);
         uint64_t state = seed * 0x9e3779b97f4a7c15ull + 0x2545f4914f6cdd1dull;
         size_t tokens = 0;
+        const int stride = (max_length + kPageTokens - 1) / kPageTokens;      // page-table entries per row
+        std::vector<int> table((size_t)rows * stride, 0);
+        int pages = 0;
         for (int r = 0; r < rows; ++r) {
             state ^= state >> 12; state ^= state << 25; state ^= state >> 27;
             const int length = min_length + static_cast<int>((state * 0x2545f4914f6cdd1dull >> 33)
                                                              % static_cast<uint64_t>(max_length - min_length + 1));
             positions[r] = length - 1;
             tokens += static_cast<size_t>(length);
+            for (int p = 0; p < (length + kPageTokens - 1) / kPageTokens; ++p) table[(size_t)r * stride + p] = pages++;
         }
-        DeviceBuffer k(tokens * kKvWidth * sizeof(bf16)), v(tokens * kKvWidth * sizeof(bf16));
+        // one slab: the K planes of all pages, then the V planes (pages are head-major, see q3t_ops.h)
+        const size_t page_elems = (size_t)kPageTokens * kKvWidth;
+        DeviceBuffer slab((size_t)pages * page_elems * 2 * sizeof(bf16));
         DeviceBuffer q((size_t)rows * kQHeads * kHeadDim * sizeof(bf16)), out((size_t)rows * kQHeads * kHeadDim * sizeof(bf16));
-        DeviceBuffer dpos((size_t)rows * sizeof(int)), dk((size_t)rows * sizeof(bf16*)), dv((size_t)rows * sizeof(bf16*));
-        size_t at = 0;
-        for (int r = 0; r < rows; ++r) {
-            k_bases[r] = k.as<bf16>() + at * kKvWidth;
-            v_bases[r] = v.as<bf16>() + at * kKvWidth;
-            at += static_cast<size_t>(positions[r] + 1);
-        }
+        DeviceBuffer dpos((size_t)rows * sizeof(int)), dtable(table.size() * sizeof(int)), dslabs(sizeof(bf16*));
         const int splits = splits_for(max_length);
         DeviceBuffer scratch(attention_scratch_floats(rows, kQHeads, kHeadDim, splits) * sizeof(float));
         DeviceBuffer counters(counters_bytes(rows, kKvHeads));
@@ -781,16 +780,20 @@ int32_t q3t_benchmark_decode_attention(int32_t device_index, int32_t rows, int32
         try {
             check_cuda(cudaEventCreate(&t0), "cudaEventCreate");
             check_cuda(cudaEventCreate(&t1), "cudaEventCreate");
-            check_cuda(launch_fill_normal(k.as<bf16>(), tokens * kKvWidth, seed * 3 + 1, stream), "fill K");
-            check_cuda(launch_fill_normal(v.as<bf16>(), tokens * kKvWidth, seed * 3 + 2, stream), "fill V");
+            check_cuda(launch_fill_normal(slab.as<bf16>(), (size_t)pages * page_elems * 2, seed * 3 + 1, stream), "fill K and V");
             check_cuda(launch_fill_normal(q.as<bf16>(), (size_t)rows * kQHeads * kHeadDim, seed * 3 + 3, stream), "fill q");
             check_cuda(cudaMemsetAsync(counters.as<void>(), 0, counters.bytes(), stream), "cudaMemsetAsync");
             check_cuda(cudaMemcpyAsync(dpos.as<void>(), positions.data(), dpos.bytes(), cudaMemcpyHostToDevice, stream), "upload positions");
-            check_cuda(cudaMemcpyAsync(dk.as<void>(), k_bases.data(), dk.bytes(), cudaMemcpyHostToDevice, stream), "upload K bases");
-            check_cuda(cudaMemcpyAsync(dv.as<void>(), v_bases.data(), dv.bytes(), cudaMemcpyHostToDevice, stream), "upload V bases");
+            check_cuda(cudaMemcpyAsync(dtable.as<void>(), table.data(), dtable.bytes(), cudaMemcpyHostToDevice, stream), "upload page table");
+            bf16* slab_base = slab.as<bf16>();
+            check_cuda(cudaMemcpyAsync(dslabs.as<void>(), &slab_base, sizeof(slab_base), cudaMemcpyHostToDevice, stream), "upload slab table");
+            check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
             AttentionArgs a;
             a.q = q.as<bf16>(); a.out = out.as<bf16>(); a.positions = dpos.as<int>();
-            a.kv.k_bases = dk.as<bf16*>(); a.kv.v_bases = dv.as<bf16*>();
+            a.kv.page_table = dtable.as<int>(); a.kv.table_stride = stride;
+            a.kv.slabs = dslabs.as<bf16*>(); a.kv.slab_shift = 30;
+            a.kv.page_elems = static_cast<long long>(page_elems);
+            a.kv.k_offset = 0; a.kv.v_offset = static_cast<long long>((size_t)pages * page_elems);
             a.rows = rows; a.q_heads = kQHeads; a.kv_heads = kKvHeads; a.head_dim = kHeadDim;
             a.max_splits = splits;
             a.scratch = scratch.as<float>(); a.counters = counters.as<unsigned int>();
