@@ -29,6 +29,7 @@ namespace {
 __device__ unsigned int g_attention_range_errors = 0;
 __device__ unsigned int* g_attention_error_sink = nullptr;
 
+constexpr int kMaxUnits = 4;              // chunks one CTA may walk (shared-memory buffers are sized for it)
 constexpr int kAttnThreads = 128;
 constexpr int kAttnWarps = kAttnThreads / kWarp;
 constexpr int kWarpTokens = kAttnChunk / kAttnWarps;   // 16 = one page
@@ -188,9 +189,11 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
     const int split_end = min(nsplits, split_first + units);
 
     __shared__ float qs[G][HD];
-    __shared__ float wm[kAttnWarps][G];
-    __shared__ float wl[kAttnWarps][G];
-    __shared__ __align__(16) float wacc[kAttnWarps][G][HD];
+    // per 64-token chunk of this CTA's range and per warp: (max, sum, weighted V) of the warp's page.
+    // The warps walk the chunks without meeting; the chunks are merged after the last one.
+    __shared__ float wm[kMaxUnits][kAttnWarps][G];
+    __shared__ float wl[kMaxUnits][kAttnWarps][G];
+    __shared__ __align__(16) float wacc[kMaxUnits][kAttnWarps][G][HD];
     __shared__ int is_last;
     // this step's own K/V row, kept for the warp that attends to it (EARLY: saves re-reading
     // from global memory what this CTA has just written there)
@@ -303,6 +306,7 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
     }
 
     for (int split = split_first; split < split_end; ++split) {
+    const int unit = split - split_first;
     // ---- this warp's 16 tokens --------------------------------------------------------
     const int c1 = min(len, (split + 1) * kAttnChunk);
     const int w0 = split * kAttnChunk + warp * kWarpTokens;
@@ -414,15 +418,15 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
         }
         if (gid < G) {
             if (tig == 0) {
-                wm[warp][gid] = mx;
-                wl[warp][gid] = lsum;
+                wm[unit][warp][gid] = mx;
+                wl[unit][warp][gid] = lsum;
             }
 #pragma unroll
             for (int jb = 0; jb < 2; ++jb)
 #pragma unroll
                 for (int x = 0; x < 8; ++x) {
-                    wacc[warp][gid][64 * jb + 16 * tig + x] = o[jb][x][0];
-                    wacc[warp][gid][64 * jb + 16 * tig + 8 + x] = o[jb][x][1];
+                    wacc[unit][warp][gid][64 * jb + 16 * tig + x] = o[jb][x][0];
+                    wacc[unit][warp][gid][64 * jb + 16 * tig + 8 + x] = o[jb][x][1];
                 }
         }
     } else {
@@ -513,33 +517,36 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
     if (lane == 0) {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            wm[warp][g] = m_w[g];
-            wl[warp][g] = l_w[g];
+            wm[unit][warp][g] = m_w[g];
+            wl[unit][warp][g] = l_w[g];
         }
     }
     if (sub == 0) {
 #pragma unroll
         for (int g = 0; g < G; ++g)
 #pragma unroll
-            for (int e = 0; e < 8; ++e) wacc[warp][g][j8 + e] = acc[g][e];
+            for (int e = 0; e < 8; ++e) wacc[unit][warp][g][j8 + e] = acc[g][e];
     }
     }   // head_dim other than 128
+    }   // chunks of this CTA
     __syncthreads();
 
-    // ---- merge the four warps ------------------------------------------------------------
+    // ---- merge the four warps, chunk by chunk ----------------------------------------------
+    for (int split = split_first; split < split_end; ++split) {
+    const int unit = split - split_first;
     for (int i = tid; i < G * HD; i += kAttnThreads) {
         const int g = i / HD;
         const int d = i % HD;
-        float M = wm[0][g];
+        float M = wm[unit][0][g];
 #pragma unroll
-        for (int w = 1; w < kAttnWarps; ++w) M = fmaxf(M, wm[w][g]);
+        for (int w = 1; w < kAttnWarps; ++w) M = fmaxf(M, wm[unit][w][g]);
         float L = 0.0f, A = 0.0f;
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) {
-            if (wl[w][g] > 0.0f) {
-                const float f = expf(wm[w][g] - M);
-                L = fmaf(wl[w][g], f, L);
-                A = fmaf(wacc[w][g][d], f, A);
+            if (wl[unit][w][g] > 0.0f) {
+                const float f = expf(wm[unit][w][g] - M);
+                L = fmaf(wl[unit][w][g], f, L);
+                A = fmaf(wacc[unit][w][g][d], f, A);
             }
         }
         const int head = kvh * G + g;
@@ -558,8 +565,7 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
             part[2 + d] = A;
         }
     }
-    __syncthreads();   // the warp partials are reused by the next split
-    }   // splits of this CTA
+    }
     if (nsplits == 1) return;
 
     // ---- last CTA of this (row, kv head) merges the splits in order -------------------------
@@ -825,6 +831,7 @@ cudaError_t launch_decode_attention(const AttentionArgs& a, cudaStream_t stream)
         }();
         b.units_per_cta = forced > 0 ? forced : (ctas >= 8192 ? 4 : (ctas >= 2048 ? 2 : 1));
     }
+    if (b.units_per_cta > kMaxUnits) b.units_per_cta = kMaxUnits;     // the kernel's buffers hold that many chunks
     switch (b.head_dim) {
         case 32: return launch_hd<32>(b, stream);
         case 64: return launch_hd<64>(b, stream);
