@@ -532,19 +532,35 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
     __syncthreads();
 
     // ---- merge the four warps, chunk by chunk ----------------------------------------------
+    // The weight exp(max_w - max) of a warp's page is the same for every dimension: one thread per
+    // (chunk, warp, head) evaluates it, everybody applies it.
+    __shared__ float wf[kMaxUnits][kAttnWarps][G];
+    __shared__ float wmax[kMaxUnits][G];
+    {
+        const int units_here = split_end - split_first;
+        for (int i = tid; i < units_here * kAttnWarps * G; i += kAttnThreads) {
+            const int g = i % G;
+            const int w = (i / G) % kAttnWarps;
+            const int unit = i / (G * kAttnWarps);
+            float M = wm[unit][0][g];
+#pragma unroll
+            for (int ww = 1; ww < kAttnWarps; ++ww) M = fmaxf(M, wm[unit][ww][g]);
+            wf[unit][w][g] = wl[unit][w][g] > 0.0f ? expf(wm[unit][w][g] - M) : 0.0f;
+            if (w == 0) wmax[unit][g] = M;
+        }
+    }
+    __syncthreads();
     for (int split = split_first; split < split_end; ++split) {
     const int unit = split - split_first;
     for (int i = tid; i < G * HD; i += kAttnThreads) {
         const int g = i / HD;
         const int d = i % HD;
-        float M = wm[unit][0][g];
-#pragma unroll
-        for (int w = 1; w < kAttnWarps; ++w) M = fmaxf(M, wm[unit][w][g]);
+        const float M = wmax[unit][g];
         float L = 0.0f, A = 0.0f;
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) {
             if (wl[unit][w][g] > 0.0f) {
-                const float f = expf(wm[unit][w][g] - M);
+                const float f = wf[unit][w][g];
                 L = fmaf(wl[unit][w][g], f, L);
                 A = fmaf(wacc[unit][w][g][d], f, A);
             }
