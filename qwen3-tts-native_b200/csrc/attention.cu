@@ -313,13 +313,12 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
 
     if constexpr (HD == 128) {
         float mx = -INFINITY, lsum = 0.0f;
-        float o[2][8][4];
+        // out^T tile x: rows = dims (8 gid + x and 64 + 8 gid + x), columns = query heads
+        float o[8][4];
 #pragma unroll
-        for (int jb = 0; jb < 2; ++jb)
+        for (int x = 0; x < 8; ++x)
 #pragma unroll
-            for (int x = 0; x < 8; ++x)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) o[jb][x][e] = 0.0f;
+            for (int e = 0; e < 4; ++e) o[x][e] = 0.0f;
         if (w0 < c1) {
             if (early && split == split_first) {
                 // fetched ahead of the wait, except this step's own token (appended above by the
@@ -394,40 +393,53 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
                 const float r1 = pr[nt][1] - __uint_as_float(ph[nt] & 0xffff0000u);
                 pl[nt] = pack_bf16x2(r0, r1);
             }
-            // output tile (jb, x): column n of the MMA is dim 64 jb + 8 n + x, so that a lane can
-            // build its B fragment (two tokens, one dim) from the 16 bytes it loaded per token
+            // out^T = V^T P^T: V^T is the 16 x 16 A operand (rows = dims, contraction = the warp's 16
+            // tokens), P^T the 16 x 8 B operand, whose fragment is exactly what the score fragment holds
+            // (lane (gid, tig): head gid, tokens 2 tig, 2 tig + 1 and 8 + 2 tig, 9 + 2 tig).  Row gid of
+            // tile x is dim 8 gid + x, row gid + 8 is dim 64 + 8 gid + x, so that a lane builds its A
+            // fragment (two tokens, one dim) from the 16 bytes it loaded per token: eight tiles cover
+            // the 128 dims with half the MMAs and half the accumulators of the P V orientation.
+            uint32_t tv[2][2][2][4];      // [token group][token of the pair][dim half][word]
 #pragma unroll
-            for (int jb = 0; jb < 2; ++jb) {
-                const uint32_t t00[4] = {(uint32_t)vr[0][0][jb].x, (uint32_t)vr[0][0][jb].y,
-                                         (uint32_t)vr[0][0][jb].z, (uint32_t)vr[0][0][jb].w};
-                const uint32_t t01[4] = {(uint32_t)vr[0][1][jb].x, (uint32_t)vr[0][1][jb].y,
-                                         (uint32_t)vr[0][1][jb].z, (uint32_t)vr[0][1][jb].w};
-                const uint32_t t10[4] = {(uint32_t)vr[1][0][jb].x, (uint32_t)vr[1][0][jb].y,
-                                         (uint32_t)vr[1][0][jb].z, (uint32_t)vr[1][0][jb].w};
-                const uint32_t t11[4] = {(uint32_t)vr[1][1][jb].x, (uint32_t)vr[1][1][jb].y,
-                                         (uint32_t)vr[1][1][jb].z, (uint32_t)vr[1][1][jb].w};
+            for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                    const uint32_t sel = (x & 1) ? 0x7632u : 0x5410u;
-                    const uint32_t b0 = __byte_perm(t00[x >> 1], t01[x >> 1], sel);
-                    const uint32_t b1 = __byte_perm(t10[x >> 1], t11[x >> 1], sel);
-                    mma_bf16_16816(o[jb][x], ph[0], 0u, ph[1], 0u, b0, b1);
-                    mma_bf16_16816(o[jb][x], pl[0], 0u, pl[1], 0u, b0, b1);
-                }
+                for (int pp = 0; pp < 2; ++pp)
+#pragma unroll
+                    for (int jb = 0; jb < 2; ++jb) {
+                        tv[h][pp][jb][0] = (uint32_t)vr[h][pp][jb].x;
+                        tv[h][pp][jb][1] = (uint32_t)vr[h][pp][jb].y;
+                        tv[h][pp][jb][2] = (uint32_t)vr[h][pp][jb].z;
+                        tv[h][pp][jb][3] = (uint32_t)vr[h][pp][jb].w;
+                    }
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                const uint32_t sel = (x & 1) ? 0x7632u : 0x5410u;
+                const uint32_t a0 = __byte_perm(tv[0][0][0][x >> 1], tv[0][1][0][x >> 1], sel);
+                const uint32_t a1 = __byte_perm(tv[0][0][1][x >> 1], tv[0][1][1][x >> 1], sel);
+                const uint32_t a2 = __byte_perm(tv[1][0][0][x >> 1], tv[1][1][0][x >> 1], sel);
+                const uint32_t a3 = __byte_perm(tv[1][0][1][x >> 1], tv[1][1][1][x >> 1], sel);
+                mma_bf16_16816(o[x], a0, a1, a2, a3, ph[0], ph[1]);
+                mma_bf16_16816(o[x], a0, a1, a2, a3, pl[0], pl[1]);
             }
         }
-        if (gid < G) {
-            if (tig == 0) {
-                wm[unit][warp][gid] = mx;
-                wl[unit][warp][gid] = lsum;
+        if (gid < G && tig == 0) {
+            wm[unit][warp][gid] = mx;
+            wl[unit][warp][gid] = lsum;
+        }
+        // accumulator columns 2 tig and 2 tig + 1 are query heads; lanes past the group hold nothing
+        if (2 * tig < G) {
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                wacc[unit][warp][2 * tig][8 * gid + x] = o[x][0];
+                wacc[unit][warp][2 * tig][64 + 8 * gid + x] = o[x][2];
             }
+        }
+        if (2 * tig + 1 < G) {
 #pragma unroll
-            for (int jb = 0; jb < 2; ++jb)
-#pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                    wacc[unit][warp][gid][64 * jb + 16 * tig + x] = o[jb][x][0];
-                    wacc[unit][warp][gid][64 * jb + 16 * tig + 8 + x] = o[jb][x][1];
-                }
+            for (int x = 0; x < 8; ++x) {
+                wacc[unit][warp][(2 * tig + 1) % G][8 * gid + x] = o[x][1];
+                wacc[unit][warp][(2 * tig + 1) % G][64 + 8 * gid + x] = o[x][3];
+            }
         }
     } else {
 
