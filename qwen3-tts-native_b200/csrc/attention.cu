@@ -29,7 +29,8 @@ namespace {
 __device__ unsigned int g_attention_range_errors = 0;
 __device__ unsigned int* g_attention_error_sink = nullptr;
 
-constexpr int kMaxUnits = 4;              // chunks one CTA may walk (shared-memory buffers are sized for it)
+// chunks one CTA may walk (its shared-memory buffers are sized for it; 32 KB of partials at most)
+__host__ __device__ constexpr int max_units_for(int) { return 4; }
 constexpr int kAttnThreads = 128;
 constexpr int kAttnWarps = kAttnThreads / kWarp;
 constexpr int kWarpTokens = kAttnChunk / kAttnWarps;   // 16 = one page
@@ -58,7 +59,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // a grid that is resident at once); a separate instantiation, because holding the prefetched
 // fragments across the query prologue costs registers.
 template <int HD, int G, bool PAGED, bool EARLY>
-__global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_kernel(const AttentionArgs a) {
+__global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 6) decode_attention_kernel(const AttentionArgs a) {
     constexpr int LPT = HD / 8;            // lanes per token
     constexpr int TPI = kWarp / LPT;       // tokens per warp iteration
     constexpr int ITERS = kWarpTokens / TPI;
@@ -191,6 +192,7 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 5) decode_attention_
     __shared__ float qs[G][HD];
     // per 64-token chunk of this CTA's range and per warp: (max, sum, weighted V) of the warp's page.
     // The warps walk the chunks without meeting; the chunks are merged after the last one.
+    constexpr int kMaxUnits = max_units_for(G);
     __shared__ float wm[kMaxUnits][kAttnWarps][G];
     __shared__ float wl[kMaxUnits][kAttnWarps][G];
     __shared__ __align__(16) float wacc[kMaxUnits][kAttnWarps][G][HD];
@@ -859,7 +861,10 @@ cudaError_t launch_decode_attention(const AttentionArgs& a, cudaStream_t stream)
         }();
         b.units_per_cta = forced > 0 ? forced : (ctas >= 8192 ? 4 : (ctas >= 2048 ? 2 : 1));
     }
-    if (b.units_per_cta > kMaxUnits) b.units_per_cta = kMaxUnits;     // the kernel's buffers hold that many chunks
+    {
+        const int most = max_units_for(b.q_heads / b.kv_heads);     // the kernel's buffers hold that many chunks
+        if (b.units_per_cta > most) b.units_per_cta = most;
+    }
     switch (b.head_dim) {
         case 32: return launch_hd<32>(b, stream);
         case 64: return launch_hd<64>(b, stream);
