@@ -589,7 +589,7 @@ def main() -> None:
     ap.add_argument("--no-existing", action="store_true",
                     help="skip the existing_kernels block (the reference's kernels and library from oracle/_ref)")
     ap.add_argument("--gemv-mode", type=int, default=None,
-                    help="kernel for 1..8 rows: 0 SIMT, 1 mma.sync (default), 2 bulk-copy SIMT")
+                    help="kernel for 1..8 rows: 0 SIMT, 1 int8 mma.sync (default)")
     ap.add_argument("--leg", choices=["all", "b64", "b1", "gemv", "attn", "existing"], default="all",
                     help="profiling aid: run one leg only and print a short JSON line")
     ap.add_argument("--gemv-in", type=int, default=2048)

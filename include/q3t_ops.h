@@ -192,8 +192,7 @@ QWEN3_TTS_API int32_t q3t_model_adopt_tensor(Qwen3TtsModelHandle model, const ch
  *      fused RMSNorm K = 512 * {2, 4}): activations as three byte limbs of a per-row fixed-point
  *      value, exact integer products and sums (agreement ~1e-7 relative, a row's result bitwise
  *      independent of the rows beside it), weights bulk-copied ahead of the launch dependency;
- *   2  the bulk-copy SIMT kernel where the shape allows (rows == 1), else SIMT.
- * Also reachable as model option "gemv_mode" and as QWEN3_TTS_B1_GEMV=simt|bulk at load time.
+ * Also reachable as model option "gemv_mode" and as QWEN3_TTS_B1_GEMV=simt at load time.
  * No reference counterpart (one kernel there). */
 QWEN3_TTS_API int32_t q3t_set_gemv_mode(int32_t mode);
 

@@ -29,7 +29,6 @@ static_assert(Q3T_KV_PAGE_TOKENS == kPageTokens && Q3T_ATTENTION_CHUNK == kAttnC
 
 namespace q3t {
 cudaError_t set_gemv_mma_error_sink(unsigned int* device_visible_word);
-cudaError_t set_gemv_b1_error_sink(unsigned int* device_visible_word);
 cudaError_t set_tc_error_sink(unsigned int* device_visible_word);
 
 namespace {
@@ -49,7 +48,6 @@ cudaError_t configure_device() {
     std::lock_guard<std::mutex> lock(guard);
     if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
     e = configure_gemv_kernels();
-    if (e == cudaSuccess) e = configure_gemv_b1_kernels();
     if (e == cudaSuccess) e = configure_tc_kernels();
     if (e == cudaSuccess) e = configure_gemv_mma_kernels();
     if (e == cudaSuccess) e = configure_sampler_kernels();
@@ -61,7 +59,6 @@ cudaError_t configure_device() {
         if (e == cudaSuccess) {
             *word = 0;
             e = set_gemv_mma_error_sink(word);
-            if (e == cudaSuccess) e = set_gemv_b1_error_sink(word);
             if (e == cudaSuccess) e = set_tc_error_sink(word);
             if (e == cudaSuccess) e = set_attention_error_sink(word);
             if (e == cudaSuccess) g_error_words[device].store(word, std::memory_order_release);
@@ -1013,7 +1010,7 @@ int32_t q3t_model_set_option(Qwen3TtsModelHandle model, const char* key, int32_t
         } else if (std::strcmp(key, "tc_min_rows") == 0) {
             set_tc_min_rows(value);     // process-wide: rows at or above this use the tensor cores
         } else if (std::strcmp(key, "gemv_mode") == 0) {
-            if (value < 0 || value > 2) throw std::runtime_error("gemv_mode must be 0, 1 or 2");
+            if (value < 0 || value > 1) throw std::runtime_error("gemv_mode must be 0 or 1");
             set_gemv_mode(value);       // process-wide: kernel for projections of 1..8 rows
         } else if (std::strcmp(key, "attention_mode") == 0) {
             if (value < 0 || value > 1) throw std::runtime_error("attention_mode must be 0 or 1");
@@ -1069,7 +1066,7 @@ int32_t q3t_test_report_device_wait_failure(int32_t device_index) {
 }
 
 uint32_t q3t_kernel_error_count(void) {
-    return gemv_b1_error_count() + gemm_tc_error_count() + gemv_mma_error_count();
+    return gemm_tc_error_count() + gemv_mma_error_count();
 }
 
 uint32_t q3t_attention_range_error_count(void) { return attention_range_error_count(); }

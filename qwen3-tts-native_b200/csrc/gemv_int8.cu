@@ -356,32 +356,30 @@ bool pdl_enabled() {
 }
 
 namespace {
-// 0: SIMT only, 1: tensor-core GEMV where it applies (default), 2: the bulk-copy SIMT kernel where it applies
+// 0: SIMT only, 1: int8 tensor-core GEMV where it applies (default)
 int g_gemv_mode = [] {
     const char* v = std::getenv("QWEN3_TTS_B1_GEMV");
     if (v != nullptr && std::strcmp(v, "simt") == 0) return 0;
-    if (v != nullptr && std::strcmp(v, "bulk") == 0) return 2;
     return 1;
 }();
 }  // namespace
 
 int set_gemv_mode(int mode) {
     const int before = g_gemv_mode;
-    if (mode >= 0 && mode <= 2) g_gemv_mode = mode;
+    if (mode == 0 || mode == 1) g_gemv_mode = mode;
     return before;
 }
 int gemv_mode() { return g_gemv_mode; }
 
 // Which kernel takes a projection:
 //   9..64 rows, K a multiple of 128     tcgen05 kernel (gemm_int8_tc.cu)
-//   1..8 rows, K = 512 * {2,3,4,6,...}   mma.sync kernel (gemv_int8_mma.cu): weights bulk-copied ahead of the
-//                                       dependency wait, 1e-6-level agreement with the SIMT kernel
+//   1..8 rows, K = 512 * {2,4,6,12}     int8 mma.sync kernel (gemv_int8_mma.cu): weights bulk-copied ahead of
+//                                       the dependency wait, exact integer sums, 1e-7-level agreement with fp64
 //   everything else, or gemv mode 0     SIMT kernel below, which keeps the reference's summation order
 //                                       bit for bit (mode 0 is for callers that need exactly that)
 cudaError_t launch_int8_gemm(const GemvArgs& a, cudaStream_t stream) {
     if (gemm_tc_supports(a)) return launch_int8_gemm_tc(a, stream);
     if (g_gemv_mode == 1 && gemv_mma_supports(a)) return launch_int8_gemv_mma(a, stream);
-    if (g_gemv_mode == 2 && gemv_b1_supports(a)) return launch_int8_gemv_b1(a, stream);
     return launch_int8_gemm_simt(a, stream);
 }
 

@@ -67,10 +67,6 @@ cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
 // Dispatcher over the kernels below (see its definition for the rule)
 cudaError_t launch_int8_gemm(const GemvArgs& args, cudaStream_t stream);
 cudaError_t launch_int8_gemm_simt(const GemvArgs& args, cudaStream_t stream);
-// batch-1 kernel (bulk-copy rings, packed fp32x2 math): rows == 1 and K in {1024,2048,3072,6144}
-bool gemv_b1_supports(const GemvArgs& args);
-cudaError_t launch_int8_gemv_b1(const GemvArgs& args, cudaStream_t stream);
-cudaError_t configure_gemv_b1_kernels();
 // 1..8 rows on mma.sync with the weights bulk-copied ahead of the dependency wait (gemv_int8_mma.cu):
 // K = 512 * {2, 3, 4, 6, 8, 9, 12, ...}; same value as the SIMT kernel up to the order of summation
 bool gemv_mma_supports(const GemvArgs& args);
@@ -78,7 +74,7 @@ cudaError_t launch_int8_gemv_mma(const GemvArgs& args, cudaStream_t stream);
 cudaError_t configure_gemv_mma_kernels();
 unsigned int gemv_mma_error_count();
 // which kernel launch_int8_gemm picks for 1..8 rows: 0 SIMT (the reference's summation order, bit for
-// bit), 1 mma.sync where it applies (default), 2 the bulk-copy SIMT kernel where it applies.
+// bit), 1 the int8 mma.sync kernel where it applies (default).
 // Process-wide; returns the previous mode.
 int set_gemv_mode(int mode);
 int gemv_mode();
@@ -89,8 +85,6 @@ cudaError_t configure_tc_kernels();      // also allocates the per-device scratc
 void set_tc_min_rows(int rows);          // 65 or more: never use the tensor-core path
 int tc_min_rows();
 unsigned int gemm_tc_error_count();
-// number of bounded waits that ran out in gemv_b1 kernels since the library was loaded (0 = healthy)
-unsigned int gemv_b1_error_count();
 
 cudaError_t launch_quantize_weight_rows(const bf16* weight, int8_t* quantized, float* scales,
                                         int in_features, int out_features, cudaStream_t stream);

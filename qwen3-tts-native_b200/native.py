@@ -615,7 +615,7 @@ def probe_device(device_index: int = 0) -> DeviceInfoC:
 
 def set_gemv_mode(mode: int) -> int:
     """Kernel for projections of 1..8 rows: 0 SIMT (bit-identical to the reference's summation order),
-    1 int8 tensor-core kernel where the shape allows (default), 2 bulk-copy SIMT.  Returns the previous mode."""
+    1 int8 tensor-core kernel where the shape allows (default).  Returns the previous mode."""
     return int(library().q3t_set_gemv_mode(int(mode)))
 
 
