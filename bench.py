@@ -90,7 +90,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "--id=" + ",".join(str(d) for d in self.devices),
-                 f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                 f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "25"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None

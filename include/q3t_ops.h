@@ -196,6 +196,13 @@ QWEN3_TTS_API int32_t q3t_model_adopt_tensor(Qwen3TtsModelHandle model, const ch
  * No reference counterpart (one kernel there). */
 QWEN3_TTS_API int32_t q3t_set_gemv_mode(int32_t mode);
 
+/* Test hook, host arithmetic only (works without a GPU): the shared-memory plan the mode-1 kernel
+ * would give one launch of `rows` rows of this shape.  Returns 1 and fills fields[0..7] = grid, stages,
+ * tile group, tiles per CTA, rows one launch takes for this shape, bytes of a full stage, bytes of the
+ * weight ring, dynamic shared memory of the launch; returns 0 when the kernel does not take the shape. */
+QWEN3_TTS_API int32_t q3t_test_gemv_plan(int32_t in_features, int32_t out_features, int32_t rows,
+                                         int32_t gate_up, int32_t norm, int64_t* fields);
+
 /* Which kernel computes decode attention (process-wide; returns the previous mode):
  *   1  (default) the split-KV kernel: tensor-core products, chunked fp32 sums; within 1e-3 of the
  *      reference's batch_causal_gqa_attention_fast_kernel (talker_kernels.cu:506-595) on the fp32 value;

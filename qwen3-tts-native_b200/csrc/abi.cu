@@ -1054,6 +1054,16 @@ int32_t q3t_session_synthetic_prefill(Qwen3TtsSessionHandle session, int32_t pos
 }
 
 int32_t q3t_set_gemv_mode(int32_t mode) { return set_gemv_mode(mode); }
+
+int32_t q3t_test_gemv_plan(int32_t in_features, int32_t out_features, int32_t rows, int32_t gate_up,
+                           int32_t norm, int64_t* fields) {
+    GemvMmaPlan plan{};
+    if (fields == nullptr || !gemv_mma_plan(in_features, out_features, rows, gate_up != 0, norm != 0, &plan)) return 0;
+    fields[0] = plan.grid; fields[1] = plan.stages; fields[2] = plan.group; fields[3] = plan.tiles;
+    fields[4] = plan.rows_per_launch; fields[5] = plan.stage_bytes; fields[6] = plan.ring_bytes;
+    fields[7] = plan.shared_bytes;
+    return 1;
+}
 int32_t q3t_set_attention_mode(int32_t mode) { return set_attention_mode(mode); }
 
 void q3t_test_fail_launch_after(int32_t launches) { fail_launch_after(launches); }

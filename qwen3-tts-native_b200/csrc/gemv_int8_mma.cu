@@ -720,6 +720,32 @@ cudaError_t configure_gemv_mma_kernels() {
     return e;
 }
 
+// Host-side planning only (no CUDA call beyond the cached SM count, 148 without a device): what one
+// launch of `rows` activation rows would be given.  For tests of the plan arithmetic.
+bool gemv_mma_plan(int in_features, int out_features, int rows, bool gate_up, bool norm, GemvMmaPlan* out) {
+    if (out == nullptr) return false;
+    GemvArgs a;
+    a.in_features = in_features;
+    a.out_features = out_features;
+    a.rows = rows;
+    a.epilogue = gate_up ? EPI_GATE_UP_SILU : EPI_PLAIN;
+    static const bf16 some_weight = bf16();
+    a.norm_w = norm ? &some_weight : nullptr;        // only its presence matters to the plan
+    Plan plan;
+    if (!plan_for(a, rows, plan)) return false;
+    const int per_tile = gate_up ? 8 : 16;
+    const int channels = (out_features + plan.grid - 1) / plan.grid;
+    out->grid = plan.grid;
+    out->stages = plan.stages;
+    out->group = plan.group;
+    out->tiles = (channels + per_tile - 1) / per_tile;
+    out->stage_bytes = 2 * (8 * (long long)in_features + kHalfPad);
+    out->ring_bytes = static_cast<long long>(plan.ring);
+    out->shared_bytes = static_cast<long long>(plan.smem);
+    out->rows_per_launch = rows_per_launch(a);
+    return true;
+}
+
 bool gemv_mma_supports(const GemvArgs& a) {
     if (a.rows < 1 || a.rows > kMaxRows || rows_per_launch(a) == 0) return false;
     // bulk copies and vector loads need aligned sources; every row offset is a multiple of K

@@ -71,6 +71,12 @@ cudaError_t launch_int8_gemm_simt(const GemvArgs& args, cudaStream_t stream);
 // K = 512 * {2, 3, 4, 6, 8, 9, 12, ...}; same value as the SIMT kernel up to the order of summation
 bool gemv_mma_supports(const GemvArgs& args);
 cudaError_t launch_int8_gemv_mma(const GemvArgs& args, cudaStream_t stream);
+// the shared-memory plan of one launch (host arithmetic only; see gemv_int8_mma.cu)
+struct GemvMmaPlan {
+    int grid, stages, group, tiles, rows_per_launch;
+    long long stage_bytes, ring_bytes, shared_bytes;
+};
+bool gemv_mma_plan(int in_features, int out_features, int rows, bool gate_up, bool norm, GemvMmaPlan* out);
 cudaError_t configure_gemv_mma_kernels();
 unsigned int gemv_mma_error_count();
 // which kernel launch_int8_gemm picks for 1..8 rows: 0 SIMT (the reference's summation order, bit for

@@ -111,7 +111,7 @@ EXPORTED_SYMBOLS = (
     "q3t_launch_int8_gemm_rows", "q3t_launch_int8_gemm_rows_add",
     "q3t_launch_int8_gate_up_silu_rows", "q3t_launch_int8_gemm_ex",
     "q3t_launch_quantize_weight_rows", "q3t_benchmark_int8_gemv", "q3t_launch_rms_norm_rows",
-    "q3t_set_gemv_mode", "q3t_set_attention_mode", "q3t_benchmark_decode_attention", "q3t_attention_range_error_count", "q3t_test_fail_launch_after", "q3t_test_fail_allocation_after",
+    "q3t_set_gemv_mode", "q3t_test_gemv_plan", "q3t_set_attention_mode", "q3t_benchmark_decode_attention", "q3t_attention_range_error_count", "q3t_test_fail_launch_after", "q3t_test_fail_allocation_after",
     "q3t_test_report_device_wait_failure", "q3t_host_pump_frames",
     "q3t_pump_create", "q3t_pump_destroy", "q3t_pump_register", "q3t_pump_unregister",
     "q3t_pump_begin_frame", "q3t_pump_statistics", "q3t_pick_device",

@@ -107,3 +107,54 @@ def test_missing_library_fails_loudly(q3t, monkeypatch):
     monkeypatch.setattr(q3t.native, "_lib", None)
     with pytest.raises(ImportError):
         q3t.native.library()
+
+
+# ---- shared-memory plan of the 1..8-row projection kernel (host arithmetic, no GPU) ----------
+
+# (in_features, out_features, gate/up, norm prologue): every projection shape of the model
+PROJECTION_SHAPES = [
+    (2048, 4096, 0, 1), (2048, 2048, 0, 0), (2048, 6144, 1, 1), (6144, 2048, 0, 0),      # talker layer
+    (1024, 4096, 0, 1), (2048, 1024, 0, 0), (1024, 3072, 1, 1), (3072, 1024, 0, 0),      # predictor layer
+    (2048, 3072, 0, 1), (1024, 2048, 0, 1), (2048, 1024, 0, 0), (2048, 2048, 0, 0),      # heads, input and text projections
+    (2048, 6144, 0, 0),                                                                  # the benchmark's configs[0]
+]
+
+
+@pytest.mark.parametrize("k,n,gate_up,norm", PROJECTION_SHAPES)
+def test_projection_plan_keeps_every_stage_inside_the_allocation(q3t, k, n, gate_up, norm):
+    """The kernel's tile loop reads all sixteen rows of a weight stage whatever was copied into it, so
+    a launch is safe only if every stage, read at full height, lies inside its dynamic shared memory;
+    a tile group must not be larger than the ring (its tiles are all resident before it starts); and
+    the launch must fit what one SM has.  (A plan that let a short last stage stick out of the
+    allocation once ended in an illegal shared-memory access on a one-row launch.)"""
+    lib = q3t.library()
+    lib.q3t_test_gemv_plan.argtypes = [C.c_int32] * 5 + [C.POINTER(C.c_int64)]
+    taken = 0
+    for rows in range(1, 9):
+        f = (C.c_int64 * 8)()
+        if not lib.q3t_test_gemv_plan(k, n, rows, gate_up, norm, f):
+            continue
+        taken += 1
+        grid, stages, group, tiles, per_launch, stage_bytes, ring_bytes, shared_bytes = (int(v) for v in f)
+        assert 1 <= grid <= 148 and tiles >= 1
+        assert 1 <= group <= stages <= max(tiles, 1)
+        assert stage_bytes == 2 * (8 * k + 64)
+        assert stages * stage_bytes <= shared_bytes, (rows, stages, stage_bytes, shared_bytes)
+        assert ring_bytes % 16 == 0 and ring_bytes <= shared_bytes <= 200 * 1024
+        assert 1 <= per_launch <= 8
+        if rows <= 2 and shared_bytes <= 113 * 1024:
+            assert 2 * shared_bytes <= 227 * 1024          # room for the next launch's CTA beside this one
+    # every shape of the model is taken at one row (larger row counts may run as several launches)
+    f = (C.c_int64 * 8)()
+    assert lib.q3t_test_gemv_plan(k, n, 1, gate_up, norm, f) == 1
+    assert taken >= 1
+
+
+def test_projection_plan_refuses_what_the_kernel_does_not_take(q3t):
+    lib = q3t.library()
+    lib.q3t_test_gemv_plan.argtypes = [C.c_int32] * 5 + [C.POINTER(C.c_int64)]
+    f = (C.c_int64 * 8)()
+    assert lib.q3t_test_gemv_plan(1536, 300, 1, 0, 0, f) == 0        # K = 512 * 3 is not built
+    assert lib.q3t_test_gemv_plan(3072, 1024, 1, 0, 1, f) == 0       # norm prologue only for K = 1024, 2048
+    assert lib.q3t_test_gemv_plan(2048, 4096, 9, 0, 0, f) == 0       # more than eight rows per launch
+    assert lib.q3t_test_gemv_plan(2000, 4096, 1, 0, 0, f) == 0

@@ -1,14 +1,16 @@
 """GPU parity of the default kernel for projections of 1..8 rows (gemv_int8_mma.cu: weights
-bulk-copied ahead of the launch dependency, mma.sync arithmetic) through the operator-level C ABI.
+bulk-copied ahead of the launch dependency, int8 mma.sync arithmetic on byte limbs of the activations)
+through the operator-level C ABI.
 
-The products are the reference's (int8 weight x bf16 activation, exact) and the accumulation is
-fp32, but in another order than the reference's kernel, so the checks are the north-star tolerance
-stated two ways and a rounding-step bound on the bf16 output:
+The products are the reference's (int8 weight x bf16 activation) and they are summed exactly, as
+integers, per eighth of K; what differs from the reference's kernel is the order and rounding of the
+few fp32 steps that remain, so the checks are the north-star tolerance stated two ways and a
+rounding-step bound on the bf16 output:
 
   * fp32 value before the final round within 1e-3 of fp64 truth, element-wise relative error on
     every element whose magnitude is at least 0.1 x the row's RMS (smaller ones are cancellations,
     where a relative error has no meaning) and, for every element, relative to |truth| + RMS;
-    both figures are expected around 1e-6;
+    both figures are expected around 1e-7;
   * bf16 output == bf16(that fp32 value), and within one bf16 rounding step of the oracle's output
     with few mismatching elements;
   * a row's result does not depend on the rows beside it (batch of R == R solo calls, bit for bit),
@@ -154,22 +156,20 @@ def test_bias_epilogues(orc, ops, rows):
 
 
 @pytest.mark.parametrize("n,k", [(4096, 2048), (1024, 3072), (2048, 6144), (6144, 1024)])
-def test_rows_barely_depend_on_their_neighbours(orc, ops, n, k):
-    """Each activation row is its own column of the tensor-core operand with its own power of two, so
-    a row computed beside other rows equals the row computed alone -- up to the tensor cores
-    themselves: one element in several thousand was seen to round the other way when the columns
-    beside it were occupied.  Repeated calls agree bit for bit.  (Callers that need batch == solo bit
-    for bit select gemv mode 0.)"""
+def test_rows_do_not_depend_on_their_neighbours(orc, ops, n, k):
+    """Each activation row is its own pair of tensor-core columns with its own power of two, and every
+    product and partial sum is an exact integer, so a row computed beside other rows equals the row
+    computed alone, bit for bit, whatever the row count (1..2 rows and 3..8 rows run different
+    instantiations, K = 6144 takes several launches of fewer rows).  Repeated calls agree too."""
     w, s, x = case(orc, 8, n, k, 8)
     x[3] = orc.to_bf16(np.random.default_rng(9).standard_normal(k).astype(np.float32) * 1.0e4)   # another scale
     x[5] = orc.to_bf16(np.random.default_rng(10).standard_normal(k).astype(np.float32) * 1.0e-6)
     batch = ops.int8_gemm_rows(w, s, x)
     again = ops.int8_gemm_rows(w, s, x)
     assert np.array_equal(batch, again)
-    for rows in ([0], [3], [5], [7], [2, 3, 4], [1, 2, 3, 4, 5]):
+    for rows in ([0], [3], [5], [7], [2, 3], [2, 3, 4], [1, 2, 3, 4, 5], [0, 1, 2, 3, 4, 5, 6]):
         alone = ops.int8_gemm_rows(w, s, x[rows[0]:rows[-1] + 1])
-        d = orc.bf16_ulp_distance(alone, batch[rows[0]:rows[-1] + 1])
-        assert d.max() <= 1 and (d > 0).mean() <= 1.0e-3, (rows, int(d.max()), float((d > 0).mean()))
+        assert np.array_equal(alone, batch[rows[0]:rows[-1] + 1]), rows
 
 
 def test_activation_range(orc, ops):
