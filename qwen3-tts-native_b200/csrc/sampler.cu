@@ -169,6 +169,14 @@ __device__ __forceinline__ void sample_one(const SamplerRow& r, unsigned char* s
             const int shift = pass < 5 ? 36 - 8 * pass : 0;
             const int width = pass < 5 ? 8 : 4;
             if (s_done) break;
+            if (!penalise && (pass == 2 || pass == 3)) {
+                // bf16 logits: the low 16 bits of every value are zero, so those of the order key are
+                // all zeros (non-negative values) or all ones (negative ones), and every key still in
+                // the running has the sign of the prefix: the digit is known without counting
+                if (tid == 0 && ((s_prefix >> 43) & 1ull) == 0ull) s_prefix |= 0xffull << shift;
+                __syncthreads();
+                continue;
+            }
             for (int i = tid; i < 256; i += kSampleThreads) hist[i] = 0u;
             __syncthreads();
             const unsigned long long pref = s_prefix;
@@ -232,6 +240,7 @@ __device__ __forceinline__ void sample_one(const SamplerRow& r, unsigned char* s
         for (int i = tid; i < selections; i += kSampleThreads) {
             const unsigned long long k = cand[i];
             int rank = 0;
+#pragma unroll 8
             for (int j = 0; j < selections; ++j) rank += cand[j] > k ? 1 : 0;
             sval[rank] = key_value(k);
             sidx[rank] = key_index(k);
@@ -243,8 +252,20 @@ __device__ __forceinline__ void sample_one(const SamplerRow& r, unsigned char* s
         }
         __syncthreads();
         if (tid == 0) {
+            // one thread, the reference's order of additions; eight loads at a time ahead of the chain
             double running = 0.0;
-            for (int i = 0; i < selections; ++i) {
+            int i = 0;
+            for (; i + 8 <= selections; i += 8) {
+                double w8[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) w8[u] = weights[i + u];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    running += w8[u];
+                    prefix[i + u] = running;
+                }
+            }
+            for (; i < selections; ++i) {
                 running += weights[i];
                 prefix[i] = running;
             }
@@ -256,11 +277,27 @@ __device__ __forceinline__ void sample_one(const SamplerRow& r, unsigned char* s
         if (tid == 0) {
             double cumulative = 0.0;
             int keep = selections;
-            for (int i = 0; i < selections; ++i) {
+            const double limit = static_cast<double>(r.top_p);
+            int i = 0;
+            bool found = false;
+            for (; !found && i + 8 <= selections; i += 8) {
+                double w8[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) w8[u] = weights[i + u];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    cumulative += w8[u];
+                    if (!found && cumulative >= limit) {
+                        keep = i + u + 1;
+                        found = true;
+                    }
+                }
+            }
+            for (; !found && i < selections; ++i) {
                 cumulative += weights[i];
-                if (cumulative >= static_cast<double>(r.top_p)) {
+                if (cumulative >= limit) {
                     keep = i + 1;
-                    break;
+                    found = true;
                 }
             }
             s_retained = keep;
@@ -275,12 +312,17 @@ __device__ __forceinline__ void sample_one(const SamplerRow& r, unsigned char* s
         const double total = prefix[retained - 1];
         const double target = static_cast<double>(uniform_random(r.rng)) * total;
         int selected = fallback;
-        for (int i = 0; i < retained; ++i) {
-            if (prefix[i] >= target) {
-                selected = sidx[i];
-                break;
+        int first = retained;            // first prefix that reaches the target
+        for (int i = 0; i < retained && first == retained; i += 8) {
+            double p8[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) p8[u] = i + u < retained ? prefix[i + u] : 0.0;
+#pragma unroll
+            for (int u = 7; u >= 0; --u) {
+                if (i + u < retained && p8[u] >= target) first = i + u;
             }
         }
+        if (first < retained) selected = sidx[first];
         *r.selected = selected;
         if (r.store_a != nullptr) r.store_a[r.store_a_index] = selected;
         if (r.store_b != nullptr) r.store_b[count] = selected;
