@@ -424,6 +424,42 @@ __global__ void __launch_bounds__(kAttnThreads, EARLY ? 4 : 6) decode_attention_
                 mma_bf16_16816(o[x], a0, a1, a2, a3, pl[0], pl[1]);
             }
         }
+        if (len <= kWarpTokens) {
+            // The whole row is this one page (the code predictor's caches): warp 0 holds everything,
+            // the merges below would multiply by exp(0) = 1 and add zeros.  It writes the result from
+            // its registers, the same value bit for bit, and nobody meets at a barrier again.
+            if (warp == 0) {
+                // 1 / sum of the heads in this lane's accumulator columns, from the lanes that hold them
+                const float inv0 = 1.0f / __shfl_sync(0xffffffffu, lsum, (2 * tig) * 4 % kWarp);
+                const float inv1 = 1.0f / __shfl_sync(0xffffffffu, lsum, (2 * tig + 1) * 4 % kWarp);
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int g = 2 * tig + c;
+                    if (g < G) {
+                        const float inv = c == 0 ? inv0 : inv1;
+                        const size_t base = (size_t)row * qw + (size_t)(kvh * G + g) * HD;
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {     // dims 8 gid .. + 7 and 64 + 8 gid .. + 7
+                            float v8[8];
+#pragma unroll
+                            for (int x = 0; x < 8; ++x) v8[x] = o[x][2 * half + c] * inv;
+                            const size_t at = base + 64 * half + 8 * gid;
+                            if (a.out32 != nullptr) {
+#pragma unroll
+                                for (int x = 0; x < 8; ++x) a.out32[at + x] = v8[x];
+                            }
+                            int4 packed;
+                            packed.x = static_cast<int>(pack_bf16x2(v8[0], v8[1]));
+                            packed.y = static_cast<int>(pack_bf16x2(v8[2], v8[3]));
+                            packed.z = static_cast<int>(pack_bf16x2(v8[4], v8[5]));
+                            packed.w = static_cast<int>(pack_bf16x2(v8[6], v8[7]));
+                            *reinterpret_cast<int4*>(a.out + at) = packed;
+                        }
+                    }
+                }
+            }
+            return;
+        }
         if (gid < G && tig == 0) {
             wm[unit][warp][gid] = mx;
             wl[unit][warp][gid] = lsum;
