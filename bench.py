@@ -90,7 +90,10 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "--id=" + ",".join(str(d) for d in self.devices),
-                 f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "25"],
+                 f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms",
+                 # one GPU: a sample every 25 ms (the timed region is a fraction of a second); several
+                 # GPUs: every 100 ms, since each sample queries every GPU of the job
+                 "25" if len(self.devices) == 1 else "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
