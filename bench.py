@@ -407,6 +407,14 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         print(json.dumps({"leg": "attn", "rows": SESSIONS, "kv_lengths": "U[64, 2048], seed 3",
                           "us_per_launch": us, "kv_bytes": kv_bytes, "GBps": kv_bytes / us / 1e3}), flush=True)
         return
+    gemv_runs = None
+    if rank == 0 and args.leg == "all":
+        # The operator microbenchmark of the roofline block, taken before the model is loaded (the
+        # same state of the device as `--leg gemv`; with 12 GB of model and caches allocated first the
+        # figure moved by up to 8 % from run to run): five runs of 2000 launches, sorted; the median
+        # run is reported.
+        gemv_runs = sorted((native.benchmark_int8_gemv(local_rank, 2048, 6144, rows=1, buffers=16, iterations=2000)
+                            for _ in range(5)), key=lambda r: r.mean_launch_microseconds)
     model = q3t.NativeTalkerModel.load(local_rank, synth.checkpoint_cuda(local_rank, seed=0))
     talker_cfg = q3t.SamplingConfig(True, 50, 0.9, 0.9, 1.0)
     predictor_cfg = q3t.SamplingConfig(True, 50, 0.9, 0.9, 1.0)
@@ -555,9 +563,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                 ps.close()
         line["stream_375_frames"] = stream
         # ---- batch-1 int8 GEMV, configs[0]: 16 weight images (201 MB > L2) round-robin --------------
-        # five runs of 2000 launches, the median run (the figure moves by a few per cent between runs)
-        runs = sorted((native.benchmark_int8_gemv(local_rank, 2048, 6144, rows=1, buffers=16, iterations=2000)
-                       for _ in range(5)), key=lambda r: r.mean_launch_microseconds)
+        runs = gemv_runs
         g = runs[len(runs) // 2]
         gemv_s = g.mean_launch_microseconds * 1e-6
         line["roofline"] = {"bound": "hbm", "kernel": "gemv_mma_kernel<4,false,false,1> 2048->6144 (configs[0]); the kernel the B=1 frame "
