@@ -85,7 +85,7 @@ struct LayerWeights {
 };
 
 // Pool of 16-token KV pages.  A slab holds, for every layer, a K plane and a V plane of
-// `pages_per_slab` pages: slab[layer][k|v][page][16][kv_width].
+// `pages_per_slab` pages: slab[layer][k|v][page][kv_head][16][head_dim] (head-major pages).
 class KvPool {
 public:
     KvPool(int layers, int kv_width, int slab_shift);
