@@ -252,3 +252,10 @@ def test_position_outside_the_launch_is_clamped_and_counted(q3t, orc, ops):
     assert np.array_equal(out.reshape(rows, -1)[1], good.reshape(rows, -1)[1])
     again = ops.attention_ex(q, pos, qh, kvh, hd, k=k, v=v)["out"]
     assert np.array_equal(again, good)
+
+
+def test_operator_benchmark_case_runs(q3t):
+    """The paged, ragged case `bench.py --leg attn` profiles: runs, reports the bytes it read."""
+    us, kv_bytes = q3t.native.benchmark_decode_attention(0, rows=4, min_length=10, max_length=300, seed=5, iterations=2)
+    assert us > 0.0
+    assert kv_bytes % (1024 * 2 * 2) == 0 and 4 * 10 <= kv_bytes // 4096 <= 4 * 300      # tokens x 1024 x bf16 x (K, V)
